@@ -1,0 +1,172 @@
+/*
+ * b2c -- C ABI of the B200 convolution / FC back end.
+ *
+ * Every entry point takes raw device pointers, plain integers and a CUDA stream handle
+ * (passed as void*, i.e. a cudaStream_t; NULL = the default stream).  Calls only enqueue
+ * work on that stream: no allocation, no implicit device synchronisation, no ownership of
+ * caller memory.  The return value is B2C_OK (0) or a negative b2c_status; nothing aborts,
+ * throws across the boundary or traps the device.  b2c_status_string() names a status.
+ *
+ * The citations name the interface of the reference project each entry replaces
+ * (paths relative to that project's root).
+ */
+#ifndef B2C_H
+#define B2C_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum b2c_status {
+    B2C_OK = 0,
+    B2C_ERR_NULL_POINTER = -1,
+    B2C_ERR_BAD_GEOMETRY = -2,     /* non-positive size, empty output, stride/dilation < 1 */
+    B2C_ERR_BAD_ENUM = -3,         /* layout / dtype / weight layout / pass out of range */
+    B2C_ERR_WORKSPACE_TOO_SMALL = -4,
+    B2C_ERR_MISALIGNED = -5,
+    B2C_ERR_UNSUPPORTED = -6,      /* shape outside what the requested engine handles */
+    B2C_ERR_CUDA = -7,             /* launch failed; see b2c_last_cuda_error() */
+    B2C_ERR_TOO_LARGE = -8,        /* size exceeds a fixed capacity of the entry point */
+    B2C_ERR_DEVICE_TIMEOUT = -9    /* a bounded in-kernel wait ran out (status word set) */
+} b2c_status;
+
+enum { B2C_LAYOUT_NHWC = 0, B2C_LAYOUT_NCHW = 1 };
+enum { B2C_F32 = 0, B2C_F64 = 1 };
+/* Filter tensor layouts:
+ *   CRSK (ci,kh,kw,co)  reference CPU back end, NHWC   pydtnn/layers/conv_2d.py:73-74
+ *   KCRS (co,ci,kh,kw)  both back ends, NCHW            pydtnn/layers/conv_2d.py:71-72
+ *   KRSC (co,kh,kw,ci)  reference GPU back end, NHWC    pydtnn/backends/gpu/layers/conv_2d_gpu.py:49-51 */
+enum { B2C_W_CRSK = 0, B2C_W_KCRS = 1, B2C_W_KRSC = 2 };
+enum { B2C_PASS_FPROP = 0, B2C_PASS_DGRAD = 1, B2C_PASS_WGRAD = 2 };
+/* Engine selection: AUTO picks the tensor-core kernels when the shape qualifies and the
+ * generic FMA kernels otherwise; the other two force one engine (UNSUPPORTED if it cannot). */
+enum { B2C_ENGINE_AUTO = 0, B2C_ENGINE_FMA = 1, B2C_ENGINE_TENSOR = 2 };
+
+/* Geometry of one Conv2D layer: the fields of pydtnn/layers/conv_2d.py:31-78, i.e. the
+ * argument list of the reference's convolution FFI (b,h,w,c,kn,kh,kw,vpad,hpad,vstr,hstr,
+ * vdil,hdil -- pydtnn/backends/cpu/libs/conv_gemm.py:234-248) plus layout/dtype. */
+typedef struct b2c_conv_desc {
+    int32_t layout;      /* B2C_LAYOUT_* of x, y, dx, dy */
+    int32_t dtype;       /* B2C_F32 / B2C_F64 */
+    int32_t w_layout;    /* B2C_W_* of w and dw */
+    int32_t engine;      /* B2C_ENGINE_* */
+    int32_t n, h, w, ci; /* input batch, height, width, channels */
+    int32_t co, kh, kw;  /* filters, filter height, width */
+    int32_t vpad, hpad, vstr, hstr, vdil, hdil;
+} b2c_conv_desc;
+
+/* Per-channel vectors (length co) of the fused inference epilogue
+ *   y = relu?( ((conv + bias) - mean) * inv_std * gamma + beta )
+ * argument order and arithmetic of pydtnn/backends/cpu/libs/conv_gemm.py:234-248 (bn_mean,
+ * bn_inv_std, bn_gamma, bn_beta, relu) and pydtnn/cython_modules/bn_inference_cython.pyx:71-72. */
+typedef struct b2c_bn_params {
+    const void *mean, *inv_std, *gamma, *beta;
+} b2c_bn_params;
+
+const char *b2c_status_string(int status);
+const char *b2c_last_cuda_error(void);
+int b2c_version(void);
+
+/* Scratch bytes a pass needs for this geometry (0 = none).
+ * Replaces the process-global cuDNN workspace sizing, pydtnn/backends/gpu/layers/memory_allocation.py:28-49
+ * and ConvGemm's pack buffers, pydtnn/backends/cpu/libs/conv_gemm.py:88-94. */
+size_t b2c_conv_workspace_bytes(const b2c_conv_desc *desc, int pass);
+/* Which engine (B2C_ENGINE_FMA / B2C_ENGINE_TENSOR) a pass would run on; negative = error. */
+int b2c_conv_engine_for(const b2c_conv_desc *desc, int pass);
+
+/* y = relu?(bn?(conv(x, w) + bias)); bias, bn may be NULL.
+ * Replaces cudnnConvolutionForward + cudnnAddTensor, pydtnn/backends/gpu/layers/conv_2d_gpu.py:170-190,
+ * and sconvGemmNHWC/NCHW with trans='N', pydtnn/backends/cpu/libs/conv_gemm.py:234-248. */
+int b2c_conv_fprop(const b2c_conv_desc *desc, const void *x, const void *w, const void *bias,
+                   const b2c_bn_params *bn, int relu, void *y,
+                   void *workspace, size_t workspace_bytes, void *stream);
+
+/* dx = conv_transpose(dy, w) (the scatter-add of row2im / col2im written as a gather).
+ * Replaces cudnnConvolutionBackwardData, conv_2d_gpu.py:224-229, and sconvGemm*_back,
+ * pydtnn/backends/cpu/libs/conv_gemm.py:311-330. */
+int b2c_conv_dgrad(const b2c_conv_desc *desc, const void *dy, const void *w, void *dx,
+                   void *workspace, size_t workspace_bytes, void *stream);
+
+/* dw = lower(x)^T dy and, when db != NULL, db = sum over n,h,w of dy.
+ * Replaces cudnnConvolutionBackwardFilter + cudnnConvolutionBackwardBias, conv_2d_gpu.py:192-213,
+ * and sconvGemm* with trans='Y', conv_gemm.py:225-230. */
+int b2c_conv_wgrad(const b2c_conv_desc *desc, const void *x, const void *dy, void *dw, void *db,
+                   void *workspace, size_t workspace_bytes, void *stream);
+
+/* The integer index map of the lowering, written to DEVICE memory as int64:
+ *   NHWC: map[M][K], NCHW: map[K][M]; entry = flat offset into x or -1 at a padding tap,
+ * numbered exactly as pydtnn/cython_modules/im2row_nhwc_cython.pyx:85-97 and
+ * im2col_nchw_cython.pyx:112-124.  Uses the same tap arithmetic as the convolution kernels. */
+int b2c_conv_index_map(const b2c_conv_desc *desc, int64_t *map, void *stream);
+
+/* FC layer, row-major: y(b,out) = x(b,in) @ w(in,out) + bias; dw = x^T dy; db = sum_b dy;
+ * dx = dy @ w^T.  Any of dw, db, dx may be NULL to skip it.
+ * Replaces cublasSgemm/Dgemm + cudnnAddTensor + cublas gemv, pydtnn/backends/gpu/layers/fc_gpu.py:105-181. */
+size_t b2c_fc_workspace_bytes(int dtype, int batch, int in_features, int out_features, int engine);
+int b2c_fc_forward(int dtype, int engine, int batch, int in_features, int out_features,
+                   const void *x, const void *w, const void *bias, void *y,
+                   void *workspace, size_t workspace_bytes, void *stream);
+int b2c_fc_backward(int dtype, int engine, int batch, int in_features, int out_features,
+                    const void *x, const void *dy, const void *w, void *dw, void *db, void *dx,
+                    void *workspace, size_t workspace_bytes, void *stream);
+
+/* ---- layers either side of the convolution in a training step ------------------------
+ * "rows" = n*h*w, channel axis last for NHWC; for NCHW pass layout and (n, c, hw). */
+
+/* Training-mode batch norm. save_mean / save_inv_std (length c) are kept for backward.
+ * running_* are updated in place with r = momentum*r + (1-momentum)*batch_stat.
+ * Replaces cudnnBatchNormalizationForwardTraining, pydtnn/backends/gpu/layers/batch_normalization_gpu.py:121-131;
+ * arithmetic of pydtnn/backends/cpu/layers/batch_normalization_cpu.py:59-76. scratch: 2*c doubles. */
+int b2c_bn_train_forward(int dtype, int layout, int n, int c, int hw, const void *x, const void *gamma,
+                         const void *beta, void *running_mean, void *running_var, double momentum,
+                         double eps, int fuse_relu, void *y, void *save_mean, void *save_inv_std,
+                         void *scratch, size_t scratch_bytes, void *stream);
+/* dgamma, dbeta, dx (dx may be NULL). If fuse_relu, dy is first masked by y > 0.
+ * Replaces cudnnBatchNormalizationBackward, batch_normalization_gpu.py:146-156. scratch: 2*c doubles. */
+int b2c_bn_train_backward(int dtype, int layout, int n, int c, int hw, const void *x, const void *dy,
+                          const void *y_for_relu_mask, const void *gamma, const void *save_mean,
+                          const void *save_inv_std, void *dgamma, void *dbeta, void *dx,
+                          void *scratch, size_t scratch_bytes, void *stream);
+/* y = relu?(((x-mean)*inv_std)*gamma+beta); pydtnn/cython_modules/bn_inference_cython.pyx:71-72. */
+int b2c_bn_inference(int dtype, int layout, int n, int c, int hw, const void *x, const void *mean,
+                     const void *inv_std, const void *gamma, const void *beta, int relu, void *y, void *stream);
+
+/* y = max(x,0); dx = dy * (y > 0)   pydtnn/backends/gpu/activations/relu_gpu.py:58,66 */
+int b2c_relu_forward(int dtype, int64_t count, const void *x, void *y, void *stream);
+int b2c_relu_backward(int dtype, int64_t count, const void *dy, const void *y, void *dx, void *stream);
+/* acc += other  (residual sum; pydtnn/backends/gpu/layers/addition_block_gpu.py:63,82) */
+int b2c_add_inplace(int dtype, int64_t count, void *acc, const void *other, void *stream);
+
+/* Pooling over in-bounds taps only (pydtnn/cython_modules/max_pool_2d_nhwc_cython.pyx:96-113,
+ * average_pool_2d_nhwc_cython.pyx:93-111); idx_max is int32 tap number ii*kw+jj.
+ * Replaces cudnnPoolingForward/Backward, pydtnn/backends/gpu/layers/abstract_pool_2d_layer_gpu.py:82-102. */
+int b2c_pool_forward(int dtype, int layout, int is_max, int n, int h, int w, int c, int kh, int kw,
+                     int vpad, int hpad, int vstr, int hstr, int vdil, int hdil,
+                     const void *x, void *y, int32_t *idx_max, void *stream);
+int b2c_pool_backward(int dtype, int layout, int is_max, int n, int h, int w, int c, int kh, int kw,
+                      int vpad, int hpad, int vstr, int hstr, int vdil, int hdil,
+                      const void *dy, const int32_t *idx_max, void *dx, void *stream);
+
+/* Row-wise softmax and its backward (pydtnn/backends/cpu/activations/softmax_cpu.py:32-39). */
+int b2c_softmax_forward(int dtype, int rows, int cols, const void *x, void *y, void *stream);
+int b2c_softmax_backward(int dtype, int rows, int cols, const void *dy, const void *y, void *dx, void *stream);
+/* Categorical cross-entropy on probabilities with integer labels: per-row log-likelihood into
+ * row_loss (loss = -mean(row_loss)), hit[row] = 1 if arg-max equals the label, and
+ * dx = onehot / (-clip(p) * global_batch)
+ * (pydtnn/backends/gpu/losses/categorical_cross_entropy_gpu.py:33-58;
+ *  pydtnn/backends/gpu/metrics/categorical_accuracy_gpu.py:33-51). */
+int b2c_cce_forward_backward(int dtype, int rows, int cols, const void *probs, const int32_t *labels,
+                             int global_batch, double eps, void *row_loss, int32_t *hit, void *dx, void *stream);
+
+/* SGD with momentum over one flat tensor: v = m*v + dw; w -= lr*(decay*w + v)
+ * (Nesterov: w -= lr*(decay*w + dw + m*v)); pydtnn/backends/gpu/optimizers/sgd_gpu.py:40-47. */
+int b2c_sgd_update(int dtype, int64_t count, void *w, const void *dw, void *velocity,
+                   double lr, double momentum, double decay, int nesterov, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B2C_H */

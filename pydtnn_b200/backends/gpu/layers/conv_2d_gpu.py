@@ -1,0 +1,126 @@
+"""Conv2D on the b2c library: same attributes, buffer ownership and hook behaviour as the
+reference's cuDNN layer (pydtnn/backends/gpu/layers/conv_2d_gpu.py:37-231), with every cuDNN
+call replaced by one call through the C ABI."""
+import ctypes
+
+import numpy as np
+
+from .... import _lib
+from ....layers import Conv2D, Conv2DBatchNormalization, Conv2DBatchNormalizationRelu, Conv2DRelu
+from ....tensor_gpu import TensorGPU, empty, to_gpu
+from ....utils import PYDTNN_TENSOR_FORMAT_NCHW, PYDTNN_TENSOR_FORMAT_NHWC
+from .. import memory_allocation as wsp
+from .layer_gpu import LayerGPU
+
+
+class Conv2DGPU(LayerGPU, Conv2D):
+
+    def __init__(self, *args, **kwargs):
+        super().__init__(*args, **kwargs)
+        self.desc = None
+        self.engine = _lib.ENGINE_AUTO
+
+    def _make_desc(self):
+        m = self.model
+        nchw = m.tensor_format == PYDTNN_TENSOR_FORMAT_NCHW
+        return _lib.ConvDesc(
+            layout=_lib.LAYOUT_NCHW if nchw else _lib.LAYOUT_NHWC, dtype=_lib.dtype_code(m.dtype),
+            w_layout=_lib.W_KCRS if nchw else _lib.W_KRSC, engine=getattr(m, "conv_engine", self.engine),
+            n=m.batch_size, h=self.hi, w=self.wi, ci=self.ci, co=self.co, kh=self.kh, kw=self.kw,
+            vpad=self.vpadding, hpad=self.hpadding, vstr=self.vstride, hstr=self.hstride,
+            vdil=self.vdilation, hdil=self.hdilation)
+
+    def initialize(self, prev_shape, need_dx, x):
+        super().initialize(prev_shape, need_dx, x)
+        m = self.model
+        # filters are (co, kh, kw, ci) in NHWC, as in the reference's GPU layer (:49-51)
+        if m.tensor_format == PYDTNN_TENSOR_FORMAT_NHWC:
+            self.weights_shape = (self.co, *self.filter_shape, self.ci)
+        self.weights_cpu = self.weights_initializer(self.weights_shape, m.dtype)
+        w_arr, dw_arr = m.arena.alloc_param(self.weights_cpu)
+        self.weights = TensorGPU(w_arr, m.tensor_format, tensor_type="filter")
+        self.dw = TensorGPU(dw_arr, m.tensor_format, tensor_type="filter")
+        if self.use_bias:
+            bshape = (1, self.co, 1, 1) if m.tensor_format == PYDTNN_TENSOR_FORMAT_NCHW else (1, 1, 1, self.co)
+            self.biases_cpu = self.biases_initializer(bshape, m.dtype)
+            b_arr, db_arr = m.arena.alloc_param(self.biases_cpu)
+            self.biases = TensorGPU(b_arr, m.tensor_format)
+            self.db = TensorGPU(db_arr, m.tensor_format)
+        self.y = TensorGPU(empty((m.batch_size, *self.shape), m.dtype), m.tensor_format)
+        if self.need_dx:
+            self.dx = TensorGPU(empty(self.x.ary.shape, m.dtype), m.tensor_format)
+        self.desc = self._make_desc()
+        L = _lib.lib()
+        need = max(L.b2c_conv_workspace_bytes(ctypes.byref(self.desc), p) for p in
+                   (_lib.PASS_FPROP, _lib.PASS_DGRAD, _lib.PASS_WGRAD))
+        wsp.require(need)
+
+    def forward(self, x):
+        L = _lib.lib()
+        _lib.check(L.b2c_conv_fprop(ctypes.byref(self.desc), x.ptr, self.weights.ptr,
+                                    self.biases.ptr if self.use_bias else None, None, 0, self.y.ptr,
+                                    wsp.ptr(), wsp.size(), self.model.stream_handle))
+        return self.y
+
+    def backward(self, dy):
+        L = _lib.lib()
+        _lib.check(L.b2c_conv_wgrad(ctypes.byref(self.desc), self.x.ptr, dy.ptr, self.dw.ptr,
+                                    self.db.ptr if self.use_bias else None,
+                                    wsp.ptr(), wsp.size(), self.model.stream_handle))
+        if self.need_dx:
+            _lib.check(L.b2c_conv_dgrad(ctypes.byref(self.desc), dy.ptr, self.weights.ptr, self.dx.ptr,
+                                        wsp.ptr(), wsp.size(), self.model.stream_handle))
+            return self.dx
+
+
+class _FusedConvInference(Conv2DGPU):
+    """Inference-only Conv2D with the BN-scale / ReLU epilogue fused into the convolution.
+    Backward is refused, as in the reference's fused layers
+    (pydtnn/backends/cpu/layers/conv_2d_batch_normalization_relu_cpu.py:47-48, 96-97)."""
+    _with_bn = False
+    _with_relu = False
+
+    def __init__(self, *args, from_parent=None, from_parent_2=None, **kwargs):
+        if from_parent is None:
+            super().__init__(*args, **kwargs)
+        else:
+            # built by the fusion pass from initialised layers: share their buffers and parameters
+            self.__dict__.update(from_parent.__dict__)
+            self.bn_layer = from_parent_2
+
+    def _refresh_bn(self):
+        bn = self.bn_layer
+        var = bn.running_var.ary.get().astype(np.float64)
+        inv_std = (1.0 / np.sqrt(var + bn.epsilon)).astype(self.model.dtype)
+        self._inv_std = to_gpu(inv_std.reshape(-1))
+        self._bn = _lib.BnParams(bn.running_mean.ary.gpudata, self._inv_std.gpudata, bn.gamma.ary.gpudata,
+                                 bn.beta.ary.gpudata)
+
+    def forward(self, x):
+        from ....utils import TRAIN_MODE
+        if self.model.mode == TRAIN_MODE:
+            raise RuntimeError("Fused layers cannot be used in training mode!")
+        if self._with_bn:
+            self._refresh_bn()
+        L = _lib.lib()
+        _lib.check(L.b2c_conv_fprop(ctypes.byref(self.desc), x.ptr, self.weights.ptr,
+                                    self.biases.ptr if self.use_bias else None,
+                                    ctypes.byref(self._bn) if self._with_bn else None, int(self._with_relu),
+                                    self.y.ptr, wsp.ptr(), wsp.size(), self.model.stream_handle))
+        return self.y
+
+    def backward(self, dy):
+        raise RuntimeError("Backward method of a fused layer should not be called")
+
+
+class Conv2DReluGPU(_FusedConvInference, Conv2DRelu):
+    _with_relu = True
+
+
+class Conv2DBatchNormalizationGPU(_FusedConvInference, Conv2DBatchNormalization):
+    _with_bn = True
+
+
+class Conv2DBatchNormalizationReluGPU(_FusedConvInference, Conv2DBatchNormalizationRelu):
+    _with_bn = True
+    _with_relu = True

@@ -1,0 +1,25 @@
+"""One process-wide scratch buffer shared by every convolution/FC call, grown on demand while
+layers are being initialised -- the role of the reference's shared cuDNN workspace
+(pydtnn/backends/gpu/layers/memory_allocation.py:28-49).  All kernels of a process run on one
+stream, so sharing is safe; the library itself never allocates."""
+import torch
+
+_buf = None
+
+
+def require(nbytes, device=None):
+    """Make sure the shared workspace holds at least ``nbytes`` (call at initialise time)."""
+    global _buf
+    nbytes = int(nbytes)
+    if _buf is None or _buf.numel() < nbytes or (device is not None and _buf.device != torch.device(device)):
+        device = device or (_buf.device if _buf is not None else torch.device("cuda", torch.cuda.current_device()))
+        _buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+    return _buf
+
+
+def ptr():
+    return _buf.data_ptr() if _buf is not None else 0
+
+
+def size():
+    return _buf.numel() if _buf is not None else 0

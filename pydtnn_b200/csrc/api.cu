@@ -1,0 +1,139 @@
+// C ABI of the convolution / FC path: argument checking, engine selection, dispatch.
+#include "b2c_common.cuh"
+#include <string.h>
+
+namespace b2c {
+static thread_local char g_cuda_err[256] = "";
+void set_cuda_error(cudaError_t e, const char* where) {
+    snprintf(g_cuda_err, sizeof(g_cuda_err), "%s: %s", where, cudaGetErrorString(e));
+}
+
+// FMA for everything unless the tensor-core engine takes the shape (AUTO) or is forced.
+static int pick_engine(const Geo& g, int pass, int& engine) {
+    bool tc = tc_supported(g, pass);
+    if (g.engine == B2C_ENGINE_TENSOR) { if (!tc) return B2C_ERR_UNSUPPORTED; engine = B2C_ENGINE_TENSOR; }
+    else if (g.engine == B2C_ENGINE_FMA) engine = B2C_ENGINE_FMA;
+    else engine = tc ? B2C_ENGINE_TENSOR : B2C_ENGINE_FMA;
+    return B2C_OK;
+}
+
+// An FC layer is a 1x1 convolution over a (batch, 1, 1, in) NHWC tensor with a (in,1,1,out) filter.
+static int fc_geo(int dtype, int engine, int batch, int in_f, int out_f, Geo& g) {
+    b2c_conv_desc d{};
+    d.layout = B2C_LAYOUT_NHWC; d.dtype = dtype; d.w_layout = B2C_W_CRSK; d.engine = engine;
+    d.n = batch; d.h = 1; d.w = 1; d.ci = in_f; d.co = out_f; d.kh = 1; d.kw = 1;
+    d.vstr = d.hstr = d.vdil = d.hdil = 1;
+    return make_geo(&d, g);
+}
+}  // namespace b2c
+
+using namespace b2c;
+
+extern "C" const char* b2c_status_string(int status) {
+    switch (status) {
+        case B2C_OK: return "ok";
+        case B2C_ERR_NULL_POINTER: return "null pointer argument";
+        case B2C_ERR_BAD_GEOMETRY: return "invalid geometry (non-positive size, empty output, or stride/dilation < 1)";
+        case B2C_ERR_BAD_ENUM: return "layout / dtype / weight layout / engine / pass out of range";
+        case B2C_ERR_WORKSPACE_TOO_SMALL: return "workspace too small or missing";
+        case B2C_ERR_MISALIGNED: return "pointer not aligned as required";
+        case B2C_ERR_UNSUPPORTED: return "shape not supported by the requested engine";
+        case B2C_ERR_CUDA: return "CUDA launch error";
+        case B2C_ERR_TOO_LARGE: return "size exceeds a fixed capacity";
+        case B2C_ERR_DEVICE_TIMEOUT: return "a bounded in-kernel wait ran out";
+        default: return "unknown status";
+    }
+}
+extern "C" const char* b2c_last_cuda_error(void) { return g_cuda_err; }
+extern "C" int b2c_version(void) { return 100; }
+
+extern "C" int b2c_conv_engine_for(const b2c_conv_desc* desc, int pass) {
+    Geo g; int rc = make_geo(desc, g); if (rc) return rc;
+    if (pass < 0 || pass > 2) return B2C_ERR_BAD_ENUM;
+    int e; rc = pick_engine(g, pass, e); if (rc) return rc;
+    return e;
+}
+
+extern "C" size_t b2c_conv_workspace_bytes(const b2c_conv_desc* desc, int pass) {
+    Geo g; if (make_geo(desc, g)) return 0;
+    if (pass < 0 || pass > 2) return 0;
+    int e; if (pick_engine(g, pass, e)) return 0;
+    return e == B2C_ENGINE_TENSOR ? tc_workspace_bytes(g, pass) : fma_workspace_bytes(g, pass);
+}
+
+extern "C" int b2c_conv_fprop(const b2c_conv_desc* desc, const void* x, const void* w, const void* bias,
+                              const b2c_bn_params* bn, int relu, void* y, void* ws, size_t ws_bytes, void* stream) {
+    Geo g; int rc = make_geo(desc, g); if (rc) return rc;
+    if (!x || !w || !y) return B2C_ERR_NULL_POINTER;
+    if (bn && (!bn->mean || !bn->inv_std || !bn->gamma || !bn->beta)) return B2C_ERR_NULL_POINTER;
+    int e; rc = pick_engine(g, B2C_PASS_FPROP, e); if (rc) return rc;
+    if (e == B2C_ENGINE_TENSOR) return tc_fprop(g, x, w, bias, bn, relu, y, ws, ws_bytes, (cudaStream_t)stream);
+    return fma_fprop(g, x, w, bias, bn, relu, y, ws, ws_bytes, (cudaStream_t)stream);
+}
+
+extern "C" int b2c_conv_dgrad(const b2c_conv_desc* desc, const void* dy, const void* w, void* dx,
+                              void* ws, size_t ws_bytes, void* stream) {
+    Geo g; int rc = make_geo(desc, g); if (rc) return rc;
+    if (!dy || !w || !dx) return B2C_ERR_NULL_POINTER;
+    int e; rc = pick_engine(g, B2C_PASS_DGRAD, e); if (rc) return rc;
+    if (e == B2C_ENGINE_TENSOR) return tc_dgrad(g, dy, w, dx, ws, ws_bytes, (cudaStream_t)stream);
+    return fma_dgrad(g, dy, w, dx, ws, ws_bytes, (cudaStream_t)stream);
+}
+
+extern "C" int b2c_conv_wgrad(const b2c_conv_desc* desc, const void* x, const void* dy, void* dw, void* db,
+                              void* ws, size_t ws_bytes, void* stream) {
+    Geo g; int rc = make_geo(desc, g); if (rc) return rc;
+    if (!x || !dy || !dw) return B2C_ERR_NULL_POINTER;
+    int e; rc = pick_engine(g, B2C_PASS_WGRAD, e); if (rc) return rc;
+    if (e == B2C_ENGINE_TENSOR) return tc_wgrad(g, x, dy, dw, db, ws, ws_bytes, (cudaStream_t)stream);
+    return fma_wgrad(g, x, dy, dw, db, ws, ws_bytes, (cudaStream_t)stream);
+}
+
+extern "C" int b2c_conv_index_map(const b2c_conv_desc* desc, int64_t* map, void* stream) {
+    Geo g; int rc = make_geo(desc, g); if (rc) return rc;
+    if (!map) return B2C_ERR_NULL_POINTER;
+    return fma_index_map(g, map, (cudaStream_t)stream);
+}
+
+extern "C" size_t b2c_fc_workspace_bytes(int dtype, int batch, int in_f, int out_f, int engine) {
+    Geo g; if (fc_geo(dtype, engine, batch, in_f, out_f, g)) return 0;
+    size_t m = 0;
+    for (int pass = 0; pass < 3; pass++) {
+        int e; if (pick_engine(g, pass, e)) return 0;
+        size_t b = e == B2C_ENGINE_TENSOR ? tc_workspace_bytes(g, pass) : fma_workspace_bytes(g, pass);
+        if (b > m) m = b;
+    }
+    return m;
+}
+
+extern "C" int b2c_fc_forward(int dtype, int engine, int batch, int in_f, int out_f, const void* x, const void* w,
+                              const void* bias, void* y, void* ws, size_t ws_bytes, void* stream) {
+    Geo g; int rc = fc_geo(dtype, engine, batch, in_f, out_f, g); if (rc) return rc;
+    if (!x || !w || !y) return B2C_ERR_NULL_POINTER;
+    int e; rc = pick_engine(g, B2C_PASS_FPROP, e); if (rc) return rc;
+    if (e == B2C_ENGINE_TENSOR) return tc_fprop(g, x, w, bias, nullptr, 0, y, ws, ws_bytes, (cudaStream_t)stream);
+    return fma_fprop(g, x, w, bias, nullptr, 0, y, ws, ws_bytes, (cudaStream_t)stream);
+}
+
+extern "C" int b2c_fc_backward(int dtype, int engine, int batch, int in_f, int out_f, const void* x, const void* dy,
+                               const void* w, void* dw, void* db, void* dx, void* ws, size_t ws_bytes, void* stream) {
+    Geo g; int rc = fc_geo(dtype, engine, batch, in_f, out_f, g); if (rc) return rc;
+    if (!dy) return B2C_ERR_NULL_POINTER;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dw) {
+        if (!x) return B2C_ERR_NULL_POINTER;
+        int e; rc = pick_engine(g, B2C_PASS_WGRAD, e); if (rc) return rc;
+        rc = e == B2C_ENGINE_TENSOR ? tc_wgrad(g, x, dy, dw, db, ws, ws_bytes, st) : fma_wgrad(g, x, dy, dw, db, ws, ws_bytes, st);
+        if (rc) return rc;
+    } else if (db) {
+        size_t need = channel_sum_workspace_bytes(batch, out_f, 1);
+        if (!ws || ws_bytes < need) return B2C_ERR_WORKSPACE_TOO_SMALL;
+        rc = channel_sum(dtype, B2C_LAYOUT_NHWC, batch, out_f, 1, dy, db, ws, ws_bytes, st); if (rc) return rc;
+    }
+    if (dx) {
+        if (!w) return B2C_ERR_NULL_POINTER;
+        int e; rc = pick_engine(g, B2C_PASS_DGRAD, e); if (rc) return rc;
+        rc = e == B2C_ENGINE_TENSOR ? tc_dgrad(g, dy, w, dx, ws, ws_bytes, st) : fma_dgrad(g, dy, w, dx, ws, ws_bytes, st);
+    }
+    return rc;
+}

@@ -1,0 +1,236 @@
+"""Model: the layer list and the train / evaluate step of the reference
+(pydtnn/model.py: ``add`` :268-283, ``__train_batch`` :450-527, ``__evaluate_batch`` :623-644, the
+inference fusion pass :294-349), driving the GPU layers of this package.
+
+Differences that are deliberate:
+* the gradient exchange is a bucketed, event-ordered NCCL all-reduce (see comm.py) instead of one
+  host-synchronised call per tensor;
+* the optimiser runs once over the flat parameter arena instead of once per tensor;
+* ``non_blocking_mpi`` keeps its meaning (overlap the exchange with backward) and is the default.
+"""
+import itertools
+
+import numpy as np
+import torch
+
+from . import _lib
+from .arena import ParamArena
+from .comm import GradientBucketer
+from .layers import (BatchNormalization, Conv2D, Conv2DBatchNormalization, Conv2DBatchNormalizationRelu, Conv2DRelu,
+                     Relu)
+from .losses import CategoricalCrossEntropy
+from .tensor_gpu import empty
+from .utils import (EVALUATE_MODE, PYDTNN_TENSOR_FORMAT_NCHW, PYDTNN_TENSOR_FORMAT_NHWC, TRAIN_MODE,
+                    UNSPECIFIED_MODE, np_dtype)
+
+
+class Model:
+    def __init__(self, comm=None, non_blocking_mpi=True, dtype=np.float32, batch_size=64, tensor_format="NHWC",
+                 enable_fused_bn_relu=False, enable_fused_conv_relu=False, enable_fused_conv_bn=False,
+                 enable_fused_conv_bn_relu=False, conv_engine=_lib.ENGINE_AUTO, device=None, model_name=None,
+                 bucket_elems=6 * 1024 * 1024, **kwargs):
+        _lib.lib()  # fail loudly right away if the CUDA extension is missing
+        if not torch.cuda.is_available():
+            raise RuntimeError("pydtnn_b200 needs a CUDA device; there is no CPU back end")
+        self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        torch.cuda.set_device(self.device)
+        self.dtype = np_dtype(dtype).type
+        self.batch_size = int(batch_size)
+        if tensor_format in ("NCHW", "AUTO", PYDTNN_TENSOR_FORMAT_NCHW) and tensor_format != PYDTNN_TENSOR_FORMAT_NHWC:
+            # AUTO means NCHW on the GPU in the reference (pydtnn/model.py:207-215)
+            self.tensor_format = PYDTNN_TENSOR_FORMAT_NCHW
+        else:
+            self.tensor_format = PYDTNN_TENSOR_FORMAT_NHWC
+        self.enable_fused_bn_relu = enable_fused_bn_relu
+        self.enable_fused_conv_relu = enable_fused_conv_relu
+        self.enable_fused_conv_bn = enable_fused_conv_bn
+        self.enable_fused_conv_bn_relu = enable_fused_conv_bn_relu
+        self.conv_engine = conv_engine
+        self.kwargs = kwargs
+        self.blocking_mpi = not non_blocking_mpi
+        # comm: a torch.distributed process group, True (= default group) or None (single process)
+        self.comm = None
+        self.rank, self.nprocs = 0, 1
+        if comm is not None and comm is not False:
+            import torch.distributed as dist
+            if dist.is_initialized() and dist.get_world_size() > 1:
+                self.comm = dist.group.WORLD if comm is True else comm
+                self.rank, self.nprocs = dist.get_rank(), dist.get_world_size()
+        self.layers = []
+        self.layer_id = itertools.count()
+        self.nparams = 0
+        self.mode = UNSPECIFIED_MODE
+        self.arena = ParamArena(self.dtype, self.device)
+        self.bucketer = GradientBucketer(self.arena, self.comm, bucket_elems)
+        self.y_batch = None
+        self.loss_func = None
+        self._train_fused = False
+        self._eval_layers = None
+        self.fast_update = True
+        if model_name:
+            from . import nets
+            getattr(nets, f"create_{model_name}")(self)
+
+    # ------------------------------------------------------------------------------------------
+    @property
+    def stream_handle(self):
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    def add(self, layer):
+        layer.set_model(self)
+        need_dx = layer.id > 1
+        prev_shape = self.layers[-1].shape if layer.id > 0 else ()
+        y = self.layers[-1].y if layer.id > 0 else None
+        layer.initialize(prev_shape, need_dx, y)
+        self.nparams += layer.nparams
+        self.layers.append(layer)
+        if layer.act:
+            self.add(layer.act())
+
+    def get_all_layers(self, from_layers=None):
+        if from_layers is None:
+            from_layers = self.layers
+        out = []
+        for layer in from_layers:
+            out.append(layer)
+            out += self.get_all_layers(layer.children)
+        return out
+
+    # -- fusion ------------------------------------------------------------------------------------
+    def _fuse_training(self):
+        """BatchNormalization followed by Relu: the normalisation kernel applies the ReLU and the
+        backward kernel applies its mask, so the activation tensor makes one HBM round trip fewer."""
+        if self._train_fused or not self.enable_fused_bn_relu:
+            return
+        def walk(seq):
+            for a, b in zip(seq, seq[1:]):
+                if isinstance(a, BatchNormalization) and isinstance(b, Relu):
+                    a.fuse_relu, b.absorbed = True, True
+            for layer in seq:
+                for p in layer.paths:
+                    walk(p)
+        walk(self.layers)
+        self._train_fused = True
+
+    def _fuse_inference(self, seq):
+        """Conv2D [+ BatchNormalization] [+ Relu] -> one convolution with a fused epilogue
+        (the pass of pydtnn/model.py:294-349, applied to a copy of the layer list)."""
+        out, i = [], 0
+        while i < len(seq):
+            cur = seq[i]
+            nxt = seq[i + 1] if i + 1 < len(seq) else None
+            nxt2 = seq[i + 2] if i + 2 < len(seq) else None
+            plain_conv = isinstance(cur, Conv2D) and type(cur).__name__ == "Conv2DGPU"
+            if plain_conv and self.enable_fused_conv_bn_relu and isinstance(nxt, BatchNormalization) and isinstance(nxt2, Relu):
+                f = Conv2DBatchNormalizationRelu(from_parent=cur, from_parent_2=nxt)
+                f.y = nxt2.y
+                out.append(f); i += 3; continue
+            if plain_conv and self.enable_fused_conv_bn and isinstance(nxt, BatchNormalization):
+                f = Conv2DBatchNormalization(from_parent=cur, from_parent_2=nxt)
+                f.y = nxt.y
+                out.append(f); i += 2; continue
+            if plain_conv and self.enable_fused_conv_relu and isinstance(nxt, Relu):
+                f = Conv2DRelu(from_parent=cur)
+                f.y = nxt.y
+                out.append(f); i += 2; continue
+            if cur.paths:
+                import copy
+                blk = copy.copy(cur)
+                blk.paths = [self._fuse_inference(p) for p in cur.paths]
+                out.append(blk); i += 1; continue
+            out.append(cur); i += 1
+        return out
+
+    # -- steps ---------------------------------------------------------------------------------------
+    def _ensure_loss(self):
+        if self.loss_func is None:
+            ncls = int(np.prod(self.layers[-1].shape))
+            self.loss_func = CategoricalCrossEntropy((self.batch_size, ncls), self)
+            self.y_batch = empty((self.batch_size,), np.int32)
+
+    @staticmethod
+    def _labels(y_batch):
+        if isinstance(y_batch, torch.Tensor):
+            return y_batch if y_batch.dim() == 1 else y_batch.argmax(dim=1)
+        y_batch = np.asarray(y_batch)
+        return y_batch if y_batch.ndim == 1 else np.argmax(y_batch, axis=1)
+
+    def _upload(self, x_batch, y_batch):
+        """Host -> device copy of one batch (pydtnn/model.py:457-462). Accepts NumPy arrays or
+        (pinned) torch CPU tensors; labels may be integer class ids or one-hot rows."""
+        xin = self.layers[0].y.ary
+        if isinstance(x_batch, torch.Tensor):
+            xin.t.copy_(x_batch.view(xin.t.shape), non_blocking=True)
+        else:
+            xin.set(x_batch)
+        lab = self._labels(y_batch)
+        if isinstance(lab, torch.Tensor):
+            self.y_batch.t.copy_(lab.to(torch.int32), non_blocking=True)
+        else:
+            self.y_batch.set(lab.astype(np.int32))
+
+    def forward_backward(self, global_batch_size=None):
+        """Forward, loss, backward and gradient exchange on the batch already on the device."""
+        self.mode = TRAIN_MODE
+        self._fuse_training()
+        if global_batch_size is None:
+            global_batch_size = self.batch_size * self.nprocs
+        x = self.layers[0].y
+        for layer in self.layers[1:]:
+            x = layer.forward(x)
+        loss, dx = self.loss_func(x, self.y_batch, global_batch_size)
+        if self.comm is not None:
+            self.bucketer.reset()
+        for layer in reversed(self.layers[1:]):
+            dx = layer.backward(dx)
+            if not self.blocking_mpi:
+                layer.reduce_weights_async()
+        if self.blocking_mpi:
+            for layer in reversed(self.layers[1:]):
+                layer.reduce_weights_sync()
+        return loss
+
+    def apply_update(self, optimizer):
+        if self.comm is not None:
+            self.bucketer.wait_all()
+        if self.fast_update and hasattr(optimizer, "update_arena"):
+            optimizer.update_arena(self)
+        else:
+            for layer in reversed(self.layers[1:]):
+                layer.wait_allreduce_async()
+                layer.update_weights(optimizer)
+
+    def train_batch(self, x_batch, y_batch, optimizer, global_batch_size=None):
+        """One training step on a host batch; returns the loss object (``.loss()``, ``.accuracy()``
+        read the numbers back)."""
+        self._ensure_loss()
+        self._upload(x_batch, y_batch)
+        loss = self.forward_backward(global_batch_size)
+        self.apply_update(optimizer)
+        return loss
+
+    def evaluate_batch(self, x_batch, y_batch=None):
+        """Forward only, with the inference fusions that are switched on; returns the output handle
+        (and the loss object when labels are given)."""
+        self.mode = EVALUATE_MODE
+        if self._eval_layers is None:
+            self._eval_layers = self._fuse_inference(self.layers)
+        if x_batch is not None:
+            xin = self.layers[0].y.ary
+            if isinstance(x_batch, torch.Tensor):
+                xin.t.copy_(x_batch.view(xin.t.shape), non_blocking=True)
+            else:
+                xin.set(x_batch)
+        x = self.layers[0].y
+        for layer in self._eval_layers[1:]:
+            x = layer.forward(x)
+        if y_batch is None:
+            return x
+        self._ensure_loss()
+        lab = self._labels(y_batch)
+        self.y_batch.set(lab.astype(np.int32) if not isinstance(lab, torch.Tensor) else lab.cpu().numpy().astype(np.int32))
+        loss, _ = self.loss_func(x, self.y_batch, self.batch_size * self.nprocs)
+        return x, loss
+
+    def synchronize(self):
+        torch.cuda.synchronize(self.device)

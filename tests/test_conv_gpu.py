@@ -1,0 +1,243 @@
+"""Parity of the CUDA convolution / FC path with the CPU oracle and the reference's golden
+vectors, through the C ABI.  Needs a GPU."""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import conv_oracle as co
+from pydtnn_b200 import _lib
+from tests.gpu_util import (DEV, assert_parity, dev, make_desc, rel_l2, run_conv, stream, workspace)
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+ENGINES = {"auto": _lib.ENGINE_AUTO, "fma": _lib.ENGINE_FMA}
+
+
+def _geom(arr):
+    return co.Geom(*[int(v) for v in arr])
+
+
+@pytest.mark.parametrize("engine", ["auto", "fma"])
+@pytest.mark.parametrize("layout", ["NHWC", "NCHW"])
+@pytest.mark.parametrize("dtype", ["float32", "float64"])
+def test_golden_vectors_from_the_reference(layout, dtype, engine):
+    ref = np.load(os.path.join(GOLD, "conv_ref.npz"))
+    for i in range(8):
+        key = f"c{i}_{layout}_{dtype}"
+        g = _geom(ref[key + "_geom"])
+        x, w, b, dy = (ref[f"{key}_{n}"] for n in ("x", "w", "b", "dy"))
+        for w_layout in (("CRSK", "KRSC") if layout == "NHWC" else ("KCRS",)):
+            out = run_conv(g, layout, np.dtype(dtype), x, w, b, dy, w_layout=w_layout, engine=ENGINES[engine])
+            for name in ("y", "dw", "db", "dx"):
+                assert_parity(out[name], ref[f"{key}_{name}"], dtype, f"{key} {w_layout} {name}")
+
+
+def test_known_answer_cases_are_exact():
+    ka = np.load(os.path.join(GOLD, "conv_known_answer.npz"))
+    for i in range(int(ka["count"])):
+        x, w = ka[f"k{i}_x"], ka[f"k{i}_w"]
+        vs, hs = [int(v) for v in ka[f"k{i}_stride"]]
+        g = co.Geom(x.shape[0], x.shape[2], x.shape[3], x.shape[1], w.shape[0], w.shape[2], w.shape[3], 0, 0, vs, hs)
+        y_ref = ka[f"k{i}_y"]
+        out = run_conv(g, "NCHW", np.float32, x, w, np.zeros(1, np.float32), np.ones_like(y_ref))
+        assert np.array_equal(out["y"], y_ref)
+        assert np.array_equal(out["dw"], ka[f"k{i}_dw"])
+        assert np.array_equal(out["dx"], ka[f"k{i}_dx"])
+
+
+@pytest.mark.parametrize("layout", ["NHWC", "NCHW"])
+def test_index_map_is_bit_exact(layout):
+    ref = np.load(os.path.join(GOLD, "conv_ref.npz"))
+    geoms = [_geom(ref[f"c{i}_{layout}_float32_geom"]) for i in range(8)]
+    geoms.append(co.Geom(3, 17, 13, 5, 2, 3, 5, 2, 1, 2, 3, 2, 1))
+    geoms.append(co.Geom(2, 32, 32, 16, 8, 3, 3, 1, 1, 1, 1, 1, 1))
+    L = _lib.lib()
+    for g in geoms:
+        want = co.index_map_nhwc(g) if layout == "NHWC" else co.index_map_nchw(g)
+        got = torch.full(want.shape, -7, dtype=torch.int64, device=DEV)
+        desc = make_desc(g, layout, np.float32, "CRSK" if layout == "NHWC" else "KCRS")
+        _lib.check(L.b2c_conv_index_map(ctypes.byref(desc), got.data_ptr(), stream()))
+        torch.cuda.synchronize()
+        assert np.array_equal(got.cpu().numpy(), want), g
+
+
+# shapes of the benchmark configurations at oracle-friendly batch sizes
+PARITY_SHAPES = {
+    "cfg1_3x3_64_64_n64": co.Geom(64, 32, 32, 64, 64, 3, 3, 1, 1, 1, 1),
+    "resnet_stem_7x7s2": co.Geom(2, 224, 224, 3, 64, 7, 7, 3, 3, 2, 2),
+    "resnet_1x1_64_256": co.Geom(4, 56, 56, 64, 256, 1, 1, 0, 0, 1, 1),
+    "resnet_1x1_256_64": co.Geom(4, 56, 56, 256, 64, 1, 1, 0, 0, 1, 1),
+    "resnet_3x3s2_128": co.Geom(4, 56, 56, 128, 128, 3, 3, 1, 1, 2, 2),
+    "resnet_1x1s2_256_512": co.Geom(4, 56, 56, 256, 512, 1, 1, 0, 0, 2, 2),
+    "resnet_3x3_512_7": co.Geom(8, 7, 7, 512, 512, 3, 3, 1, 1, 1, 1),
+    "alexnet_conv1_11x11s4": co.Geom(2, 227, 227, 3, 96, 11, 11, 0, 0, 4, 4),
+    "alexnet_conv2_5x5": co.Geom(2, 27, 27, 96, 256, 5, 5, 2, 2, 1, 1),
+    "sweep_5x5s2_14": co.Geom(4, 14, 14, 64, 128, 5, 5, 2, 2, 2, 2),
+    "sweep_7x7_28": co.Geom(2, 28, 28, 64, 64, 7, 7, 3, 3, 1, 1),
+    "dilated_3x3": co.Geom(2, 20, 20, 16, 24, 3, 3, 2, 2, 1, 1, 2, 2),
+    "ragged_everything": co.Geom(3, 13, 11, 7, 5, 3, 2, 1, 0, 2, 1, 1, 1),
+    "single_pixel": co.Geom(1, 1, 1, 1, 1, 1, 1, 0, 0, 1, 1),
+    "pad_larger_than_input": co.Geom(1, 2, 2, 3, 2, 3, 3, 2, 2, 1, 1),
+}
+
+
+def _inputs(g, dtype, seed=0):
+    rng = np.random.Generator(np.random.PCG64(seed))
+    x = rng.standard_normal((g.n, g.h, g.w, g.ci)).astype(dtype)
+    w = (rng.standard_normal((g.ci, g.kh, g.kw, g.co)) * np.sqrt(2.0 / g.k)).astype(dtype)
+    b = rng.standard_normal((g.co,)).astype(dtype)
+    dy = rng.standard_normal((g.n, g.ho, g.wo, g.co)).astype(dtype)
+    return x, w, b, dy
+
+
+def _to_layout(x, w, dy, layout):
+    if layout == "NHWC":
+        return x, w, dy
+    t = lambda a: np.ascontiguousarray(a.transpose(0, 3, 1, 2))
+    return t(x), np.ascontiguousarray(w.transpose(3, 0, 1, 2)), t(dy)
+
+
+@pytest.mark.parametrize("engine", ["auto", "fma"])
+@pytest.mark.parametrize("name", list(PARITY_SHAPES))
+def test_float32_nhwc_against_oracle(name, engine):
+    g = PARITY_SHAPES[name]
+    x, w, b, dy = _inputs(g, np.float32)
+    keep = {}
+    y = co.conv2d_forward(x, w, b, g, "NHWC", keep=keep)
+    dw, db, dx = co.conv2d_backward(x, dy, w, g, "NHWC", keep=keep)
+    out = run_conv(g, "NHWC", np.float32, x, w, b, dy, w_layout="KRSC", engine=ENGINES[engine])
+    for nm, ref in (("y", y), ("dw", dw), ("db", db), ("dx", dx)):
+        assert_parity(out[nm], ref, np.float32, f"{name} {nm}")
+
+
+@pytest.mark.parametrize("layout,dtype", [("NCHW", "float32"), ("NHWC", "float64"), ("NCHW", "float64")])
+@pytest.mark.parametrize("name", ["cfg1_3x3_64_64_n64", "resnet_3x3s2_128", "resnet_1x1_64_256", "sweep_5x5s2_14",
+                                  "dilated_3x3", "ragged_everything", "alexnet_conv1_11x11s4"])
+def test_other_layouts_and_float64_against_oracle(name, layout, dtype):
+    g = PARITY_SHAPES[name]
+    if name == "cfg1_3x3_64_64_n64":
+        g = co.Geom(16, *[getattr(g, f) for f in ("h", "w", "ci", "co", "kh", "kw", "vpad", "hpad", "vstr", "hstr")])
+    x, w, b, dy = _inputs(g, np.dtype(dtype), seed=1)
+    xl, wl, dyl = _to_layout(x, w, dy, layout)
+    keep = {}
+    y = co.conv2d_forward(xl, wl, b, g, layout, keep=keep)
+    dw, db, dx = co.conv2d_backward(xl, dyl, wl, g, layout, keep=keep)
+    out = run_conv(g, layout, np.dtype(dtype), xl, wl, b, dyl)
+    for nm, ref in (("y", y), ("dw", dw), ("db", db), ("dx", dx)):
+        assert_parity(out[nm], ref, dtype, f"{name} {layout} {dtype} {nm}")
+
+
+@pytest.mark.parametrize("layout", ["NHWC", "NCHW"])
+@pytest.mark.parametrize("mode", ["relu", "bn", "bn_relu", "nobias_bn_relu"])
+def test_fused_inference_epilogue(layout, mode):
+    g = co.Geom(4, 14, 14, 32, 48, 3, 3, 1, 1, 1, 1)
+    x, w, b, dy = _inputs(g, np.float32, seed=2)
+    xl, wl, _ = _to_layout(x, w, dy, layout)
+    rng = np.random.Generator(np.random.PCG64(5))
+    bn = dict(running_mean=rng.standard_normal(g.co).astype(np.float32),
+              inv_std=(1.0 / np.sqrt(rng.uniform(0.5, 2.0, g.co) + 1e-5)).astype(np.float32),
+              gamma=rng.standard_normal(g.co).astype(np.float32), beta=rng.standard_normal(g.co).astype(np.float32))
+    use_bn = "bn" in mode
+    use_relu = "relu" in mode
+    bias = None if mode.startswith("nobias") else b
+    ref = co.conv2d_fused_inference(xl, wl, bias, g, layout, bn if use_bn else None, use_relu)
+    out = run_conv(g, layout, np.float32, xl, wl, bias, None, bn=bn if use_bn else None, relu=use_relu,
+                   passes=("fprop",))
+    assert_parity(out["y"], ref, np.float32, f"fused {mode} {layout}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float64"])
+def test_fc_against_reference_golden_and_oracle(dtype):
+    L = _lib.lib()
+    ref = np.load(os.path.join(GOLD, "fc_ref.npz"))
+    cases = [tuple(ref[f"f{i}_{dtype}_{n}"] for n in ("x", "w", "b", "dy", "y", "dw", "db", "dx")) for i in range(3)]
+    rng = np.random.Generator(np.random.PCG64(3))
+    for (bsz, fin, fout) in ((64, 2048, 1000), (32, 1000, 4096), (5, 7, 3)):
+        x = rng.standard_normal((bsz, fin)).astype(dtype)
+        w = (rng.standard_normal((fin, fout)) / np.sqrt(fin)).astype(dtype)
+        b = rng.standard_normal((fout,)).astype(dtype)
+        dy = rng.standard_normal((bsz, fout)).astype(dtype)
+        y = co.fc_forward(x, w, b)
+        dw, db, dx = co.fc_backward(x, dy, w)
+        cases.append((x, w, b, dy, y, dw, db, dx))
+    dt = _lib.dtype_code(dtype)
+    for x, w, b, dy, y, dw, db, dx in cases:
+        bsz, fin = x.shape
+        fout = w.shape[1]
+        nbytes = L.b2c_fc_workspace_bytes(dt, bsz, fin, fout, 0)
+        ws = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=DEV)
+        xd, wd, bd, dyd = dev(x), dev(w), dev(b), dev(dy)
+        yd, dwd, dbd, dxd = torch.empty_like(dyd), torch.empty_like(wd), torch.empty_like(bd), torch.empty_like(xd)
+        _lib.check(L.b2c_fc_forward(dt, 0, bsz, fin, fout, xd.data_ptr(), wd.data_ptr(), bd.data_ptr(), yd.data_ptr(),
+                                    ws.data_ptr(), ws.numel(), stream()))
+        _lib.check(L.b2c_fc_backward(dt, 0, bsz, fin, fout, xd.data_ptr(), dyd.data_ptr(), wd.data_ptr(), dwd.data_ptr(),
+                                     dbd.data_ptr(), dxd.data_ptr(), ws.data_ptr(), ws.numel(), stream()))
+        torch.cuda.synchronize()
+        for nm, got, want in (("y", yd, y), ("dw", dwd, dw), ("db", dbd, db), ("dx", dxd, dx)):
+            assert_parity(got.cpu().numpy(), want, dtype, f"fc {x.shape}x{w.shape} {nm}")
+
+
+@pytest.mark.parametrize("engine", ["auto", "fma"])
+@pytest.mark.parametrize("shape", [(64, 56, 56, 64, 64, 3, 1, 1), (64, 56, 56, 256, 64, 1, 0, 1),
+                                   (64, 28, 28, 128, 128, 3, 1, 2), (64, 14, 14, 256, 1024, 1, 0, 1)])
+def test_full_batch_properties(shape, engine):
+    """At the benchmark's batch size the oracle is too slow, so check what holds at any size:
+    the three passes are mutually adjoint, <fprop(x,w),dy> = <x,dgrad(dy,w)> = <w,wgrad(x,dy)>,
+    the forward pass is linear in x, and a second run is bitwise identical (fixed summation order)."""
+    n, h, w_, ci, cout, k, pad, stride = shape
+    g = co.Geom(n, h, w_, ci, cout, k, k, pad, pad, stride, stride)
+    L = _lib.lib()
+    gen = torch.Generator(device=DEV).manual_seed(7)
+    x = torch.randn((g.n, g.h, g.w, g.ci), device=DEV, generator=gen)
+    x2 = torch.randn((g.n, g.h, g.w, g.ci), device=DEV, generator=gen)
+    wt = torch.randn((g.co, g.kh, g.kw, g.ci), device=DEV, generator=gen) * (2.0 / g.k) ** 0.5
+    dy = torch.randn((g.n, g.ho, g.wo, g.co), device=DEV, generator=gen)
+    desc = make_desc(g, "NHWC", np.float32, "KRSC", ENGINES[engine])
+    ws = workspace(desc)
+
+    def fprop(inp):
+        y = torch.empty((g.n, g.ho, g.wo, g.co), device=DEV)
+        _lib.check(L.b2c_conv_fprop(ctypes.byref(desc), inp.data_ptr(), wt.data_ptr(), None, None, 0, y.data_ptr(),
+                                    ws.data_ptr(), ws.numel(), stream()))
+        return y
+
+    y = fprop(x)
+    dx = torch.empty_like(x)
+    dw = torch.empty_like(wt)
+    db = torch.empty((g.co,), device=DEV)
+    _lib.check(L.b2c_conv_dgrad(ctypes.byref(desc), dy.data_ptr(), wt.data_ptr(), dx.data_ptr(), ws.data_ptr(),
+                                ws.numel(), stream()))
+    _lib.check(L.b2c_conv_wgrad(ctypes.byref(desc), x.data_ptr(), dy.data_ptr(), dw.data_ptr(), db.data_ptr(),
+                                ws.data_ptr(), ws.numel(), stream()))
+    dot = lambda a, b: float((a.double() * b.double()).sum())
+    a, b_, c = dot(y, dy), dot(x, dx), dot(wt, dw)
+    scale = float(y.double().norm() * dy.double().norm())
+    assert abs(a - b_) <= 1e-5 * scale and abs(a - c) <= 1e-5 * scale, (a, b_, c, scale)
+    assert rel_l2(db.cpu().numpy(), dy.double().sum(dim=(0, 1, 2)).cpu().numpy()) <= 1e-6
+    y_lin = fprop(2.5 * x + x2)
+    want = 2.5 * y.double() + fprop(x2).double()
+    assert float((y_lin.double() - want).norm() / want.norm()) <= 1e-5
+    assert torch.equal(fprop(x), y)
+    dw2 = torch.empty_like(wt)
+    _lib.check(L.b2c_conv_wgrad(ctypes.byref(desc), x.data_ptr(), dy.data_ptr(), dw2.data_ptr(), None,
+                                ws.data_ptr(), ws.numel(), stream()))
+    assert torch.equal(dw, dw2)
+
+
+def test_errors_are_status_codes_not_faults():
+    L = _lib.lib()
+    g = co.Geom(64, 32, 32, 64, 64, 3, 3, 1, 1, 1, 1)
+    desc = make_desc(g, "NHWC", np.float32, "KRSC", _lib.ENGINE_FMA)
+    x = torch.zeros((g.n, g.h, g.w, g.ci), device=DEV)
+    wt = torch.zeros((g.co, 3, 3, g.ci), device=DEV)
+    dy = torch.zeros((g.n, g.ho, g.wo, g.co), device=DEV)
+    dw = torch.zeros_like(wt)
+    # wgrad needs split-K scratch for this shape: refusing a missing / short workspace is a status
+    assert L.b2c_conv_wgrad(ctypes.byref(desc), x.data_ptr(), dy.data_ptr(), dw.data_ptr(), None, None, 0, stream()) == -4
+    tiny = torch.empty(64, dtype=torch.uint8, device=DEV)
+    assert L.b2c_conv_wgrad(ctypes.byref(desc), x.data_ptr(), dy.data_ptr(), dw.data_ptr(), None, tiny.data_ptr(), 64,
+                            stream()) == -4
+    torch.cuda.synchronize()
