@@ -69,6 +69,15 @@ typedef struct b2c_bn_params {
 const char *b2c_status_string(int status);
 const char *b2c_last_cuda_error(void);
 int b2c_version(void);
+/* Number of kernels this library has launched in the process so far (diagnostic; lets a caller
+ * state how many of its launches fall inside a timed region). No counterpart in the reference. */
+uint64_t b2c_launch_count(void);
+
+/* Reads and clears the status word the tensor-core kernels set when one of their bounded in-kernel
+ * waits runs out (the kernel then skips its remaining work and returns; the context stays usable).
+ * Synchronises with the device. Returns B2C_OK or B2C_ERR_DEVICE_TIMEOUT; *detail (may be NULL)
+ * receives the raw code. The reference has no counterpart (cuDNN reports through its status). */
+int b2c_check_device_status(int *detail);
 
 /* Scratch bytes a pass needs for this geometry (0 = none).
  * Replaces the process-global cuDNN workspace sizing, pydtnn/backends/gpu/layers/memory_allocation.py:28-49

@@ -38,6 +38,8 @@ PROTOTYPES = {
     "b2c_status_string": (c_char_p, [c_int]),
     "b2c_last_cuda_error": (c_char_p, []),
     "b2c_version": (c_int, []),
+    "b2c_launch_count": (ctypes.c_uint64, []),
+    "b2c_check_device_status": (c_int, [POINTER(c_int)]),
     "b2c_conv_workspace_bytes": (c_size_t, [POINTER(ConvDesc), c_int]),
     "b2c_conv_engine_for": (c_int, [POINTER(ConvDesc), c_int]),
     "b2c_conv_fprop": (c_int, [POINTER(ConvDesc), c_void_p, c_void_p, c_void_p, POINTER(BnParams), c_int, c_void_p,

@@ -55,21 +55,41 @@ class Conv2DGPU(LayerGPU, Conv2D):
                    (_lib.PASS_FPROP, _lib.PASS_DGRAD, _lib.PASS_WGRAD))
         wsp.require(need)
 
+    @property
+    def flops_per_pass(self):
+        """2*M*K*Co, padding taps counted (the reference's model, pydtnn/performance_models.py:68-70)."""
+        return 2 * self.model.batch_size * self.ho * self.wo * self.co * self.ci * self.kh * self.kw
+
+    def _timed(self, name, call):
+        """Run one pass; when the model carries a ``conv_profile`` list, bracket it with CUDA events
+        on the launching stream (read back by the benchmark after the timed region)."""
+        prof = getattr(self.model, "conv_profile", None)
+        if prof is None:
+            _lib.check(call())
+            return
+        import torch
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        _lib.check(call())
+        e1.record()
+        prof.append((name, self, e0, e1))
+
     def forward(self, x):
         L = _lib.lib()
-        _lib.check(L.b2c_conv_fprop(ctypes.byref(self.desc), x.ptr, self.weights.ptr,
-                                    self.biases.ptr if self.use_bias else None, None, 0, self.y.ptr,
-                                    wsp.ptr(), wsp.size(), self.model.stream_handle))
+        self._timed("fprop", lambda: L.b2c_conv_fprop(
+            ctypes.byref(self.desc), x.ptr, self.weights.ptr, self.biases.ptr if self.use_bias else None, None, 0,
+            self.y.ptr, wsp.ptr(), wsp.size(), self.model.stream_handle))
         return self.y
 
     def backward(self, dy):
         L = _lib.lib()
-        _lib.check(L.b2c_conv_wgrad(ctypes.byref(self.desc), self.x.ptr, dy.ptr, self.dw.ptr,
-                                    self.db.ptr if self.use_bias else None,
-                                    wsp.ptr(), wsp.size(), self.model.stream_handle))
+        self._timed("wgrad", lambda: L.b2c_conv_wgrad(
+            ctypes.byref(self.desc), self.x.ptr, dy.ptr, self.dw.ptr, self.db.ptr if self.use_bias else None,
+            wsp.ptr(), wsp.size(), self.model.stream_handle))
         if self.need_dx:
-            _lib.check(L.b2c_conv_dgrad(ctypes.byref(self.desc), dy.ptr, self.weights.ptr, self.dx.ptr,
-                                        wsp.ptr(), wsp.size(), self.model.stream_handle))
+            self._timed("dgrad", lambda: L.b2c_conv_dgrad(
+                ctypes.byref(self.desc), dy.ptr, self.weights.ptr, self.dx.ptr, wsp.ptr(), wsp.size(),
+                self.model.stream_handle))
             return self.dx
 
 

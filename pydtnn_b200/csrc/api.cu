@@ -4,6 +4,8 @@
 
 namespace b2c {
 static thread_local char g_cuda_err[256] = "";
+static unsigned long long g_launches = 0;
+void count_launch() { __atomic_add_fetch(&g_launches, 1ULL, __ATOMIC_RELAXED); }
 void set_cuda_error(cudaError_t e, const char* where) {
     snprintf(g_cuda_err, sizeof(g_cuda_err), "%s: %s", where, cudaGetErrorString(e));
 }
@@ -46,6 +48,15 @@ extern "C" const char* b2c_status_string(int status) {
 }
 extern "C" const char* b2c_last_cuda_error(void) { return g_cuda_err; }
 extern "C" int b2c_version(void) { return 100; }
+extern "C" uint64_t b2c_launch_count(void) { return (uint64_t)__atomic_load_n(&b2c::g_launches, __ATOMIC_RELAXED); }
+
+extern "C" int b2c_check_device_status(int* detail) {
+    int v = 0;
+    int rc = tc_read_status(&v);
+    if (detail) *detail = v;
+    if (rc) return rc;
+    return v ? B2C_ERR_DEVICE_TIMEOUT : B2C_OK;
+}
 
 extern "C" int b2c_conv_engine_for(const b2c_conv_desc* desc, int pass) {
     Geo g; int rc = make_geo(desc, g); if (rc) return rc;

@@ -9,7 +9,9 @@ namespace b2c {
 
 // ---- error plumbing ---------------------------------------------------------------------
 void set_cuda_error(cudaError_t e, const char* where);
+void count_launch();
 inline int check_launch(const char* where) {
+    count_launch();
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { set_cuda_error(e, where); return B2C_ERR_CUDA; }
     return B2C_OK;
@@ -88,5 +90,6 @@ int tc_fprop(const Geo& g, const void* x, const void* w, const void* bias, const
 int tc_dgrad(const Geo& g, const void* dy, const void* w, void* dx, void* ws, size_t ws_bytes, cudaStream_t st);
 int tc_wgrad(const Geo& g, const void* x, const void* dy, void* dw, void* db, void* ws, size_t ws_bytes,
              cudaStream_t st);
+int tc_read_status(int* out);
 
 }  // namespace b2c

@@ -1,0 +1,120 @@
+"""Whole-step parity through the Layer / Model API: a small ResNet (conv, BN, ReLU, pooling,
+addition blocks, FC, softmax, cross-entropy, SGD) against its CPU-oracle twin, layer by layer --
+the pattern of the reference's CheckGPUModels (pydtnn/tests/check_gpu_models.py:109-146). GPU."""
+import numpy as np
+import pytest
+
+from tests.gpu_util import rel_l2 as _rel_l2
+from tests.model_util import cpu_twin, grads_of, params_of, walk_pairs
+
+pytestmark = pytest.mark.gpu
+
+
+def rel_l2(got, ref):
+    """Relative L2 error with an absolute floor: gradients that are analytically zero (the bias of a
+    convolution that feeds a batch normalisation) are rounding noise on both sides."""
+    got, ref = np.asarray(got, np.float64), np.asarray(ref, np.float64)
+    floor = (1e-13 if got.dtype == np.float64 and np.asarray(ref).dtype == np.float64 else 1e-13)
+    err = np.linalg.norm(got - ref)
+    scale = np.linalg.norm(ref)
+    noise = np.sqrt(ref.size) * (1e-6 if _NOISE["f32"] else 1e-14)
+    return err / max(scale, noise * 1e2)
+
+
+_NOISE = {"f32": False}
+
+
+def _small_resnet(layout, dtype, batch=4, **kw):
+    from pydtnn_b200 import nets
+    from pydtnn_b200.model import Model
+    np.random.seed(0)
+    model = Model(batch_size=batch, tensor_format=layout, dtype=dtype, **kw)
+    nets.create_resnet50_imagenet(model, input_hw=32, nclasses=10, layout=[[8, 2, 1], [16, 2, 2]])
+    return model
+
+
+def _batch(model, seed=0):
+    rng = np.random.Generator(np.random.PCG64(seed))
+    x = rng.standard_normal((model.batch_size, *model.layers[0].shape)).astype(model.dtype)
+    labels = rng.integers(0, 10, model.batch_size)
+    return x, labels
+
+
+@pytest.mark.parametrize("layout,dtype,fused", [("NHWC", "float64", False), ("NCHW", "float64", False),
+                                                ("NHWC", "float32", False), ("NCHW", "float32", False),
+                                                ("NHWC", "float64", True), ("NHWC", "float32", True)])
+def test_train_step_matches_cpu_twin(layout, dtype, fused):
+    from pydtnn_b200.optimizers import SGD
+    model = _small_resnet(layout, np.dtype(dtype).type, enable_fused_bn_relu=fused)
+    net = cpu_twin(model)
+    nchw = layout == "NCHW"
+    tol = 1e-10 if dtype == "float64" else 2e-4
+    _NOISE["f32"] = dtype == "float32"
+    opt = SGD(learning_rate=0.05, momentum=0.9)
+    for step in range(2):
+        x, labels = _batch(model, step)
+        loss_obj = model.train_batch(x, labels, opt)
+        model.synchronize()
+        probs = net.forward(x, True)
+        loss_ref, d = net.loss_and_grad(probs, labels, model.batch_size)
+        net.backward(d)
+        assert abs(loss_obj.loss() - loss_ref) <= tol * max(1.0, abs(loss_ref))
+        # activations of the top-level layers (absorbed ReLUs return their input's buffer)
+        for i, layer in enumerate(model.layers[1:]):
+            if layer.canonical_name in ("Flatten",) or getattr(layer, "absorbed", False):
+                continue
+            got = layer.y.ary.get().reshape(net.acts[i + 1].shape)
+            assert rel_l2(got, net.acts[i + 1]) <= tol, f"step {step} y of {layer}"
+        for layer, node in walk_pairs(model.layers[1:], net.nodes):
+            for k, g in grads_of(layer, nchw).items():
+                ref = getattr(node, k)
+                assert rel_l2(g.reshape(ref.shape), ref) <= tol, f"step {step} {k} of {layer}"
+        net.sgd(0.05, 0.9)
+        for layer, node in walk_pairs(model.layers[1:], net.nodes):
+            for k, p in params_of(layer, nchw).items():
+                ref = getattr(node, k)
+                assert rel_l2(p.reshape(ref.shape), ref) <= tol, f"step {step} param {k} of {layer}"
+
+
+def test_per_layer_update_equals_arena_update():
+    from pydtnn_b200.optimizers import SGD
+    a = _small_resnet("NHWC", np.float32)
+    b = _small_resnet("NHWC", np.float32)
+    b.fast_update = False
+    oa, ob = SGD(0.05, 0.9, decay=1e-4), SGD(0.05, 0.9, decay=1e-4)
+    for step in range(2):
+        x, labels = _batch(a, step)
+        a.train_batch(x, labels, oa)
+        b.train_batch(x, labels, ob)
+    for la, lb in zip(a.get_all_layers(), b.get_all_layers()):
+        for k in la.grad_vars:
+            assert np.array_equal(getattr(la, k).ary.get(), getattr(lb, k).ary.get()), (la, k)
+
+
+@pytest.mark.parametrize("layout", ["NHWC", "NCHW"])
+def test_inference_fusion_matches_unfused_chain(layout):
+    """Conv+BN+ReLU / Conv+BN folded into the convolution epilogue for evaluation: same output as
+    the un-fused chain on the CPU oracle, after a training step has moved the running statistics."""
+    from pydtnn_b200.optimizers import SGD
+    model = _small_resnet(layout, np.float32, enable_fused_conv_bn_relu=True, enable_fused_conv_bn=True,
+                          enable_fused_conv_relu=True)
+    net = cpu_twin(model)
+    opt = SGD(learning_rate=0.0, momentum=0.0)
+    x, labels = _batch(model, 3)
+    model.train_batch(x, labels, opt)          # lr 0: only the running statistics change
+    net.forward(x, True)
+    y = model.evaluate_batch(x)
+    model.synchronize()
+    fused_names = [type(l).__name__ for l in model._eval_layers] + \
+                  [type(l).__name__ for blk in model._eval_layers for p in blk.paths for l in p]
+    assert "Conv2DBatchNormalizationReluGPU" in fused_names and "Conv2DBatchNormalizationGPU" in fused_names
+    ref = net.forward(x, False)
+    assert rel_l2(y.ary.get(), ref) <= 2e-4
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    from pydtnn_b200 import _lib
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "absent.so"))
+    with pytest.raises(_lib.B2CError):
+        _lib.lib()
