@@ -128,13 +128,15 @@ int b2c_fc_backward(int dtype, int engine, int batch, int in_features, int out_f
 /* Training-mode batch norm. save_mean / save_inv_std (length c) are kept for backward.
  * running_* are updated in place with r = momentum*r + (1-momentum)*batch_stat.
  * Replaces cudnnBatchNormalizationForwardTraining, pydtnn/backends/gpu/layers/batch_normalization_gpu.py:121-131;
- * arithmetic of pydtnn/backends/cpu/layers/batch_normalization_cpu.py:59-76. scratch: 2*c doubles. */
+ * arithmetic of pydtnn/backends/cpu/layers/batch_normalization_cpu.py:59-76.
+ * scratch: at least 128*c doubles; up to about 1200*c doubles lets layers with few channels spread
+ * their reduction over more CTAs (the kernels adapt to what they are given). */
 int b2c_bn_train_forward(int dtype, int layout, int n, int c, int hw, const void *x, const void *gamma,
                          const void *beta, void *running_mean, void *running_var, double momentum,
                          double eps, int fuse_relu, void *y, void *save_mean, void *save_inv_std,
                          void *scratch, size_t scratch_bytes, void *stream);
 /* dgamma, dbeta, dx (dx may be NULL). If fuse_relu, dy is first masked by y > 0.
- * Replaces cudnnBatchNormalizationBackward, batch_normalization_gpu.py:146-156. scratch: 2*c doubles. */
+ * Replaces cudnnBatchNormalizationBackward, batch_normalization_gpu.py:146-156. scratch: as for the forward pass. */
 int b2c_bn_train_backward(int dtype, int layout, int n, int c, int hw, const void *x, const void *dy,
                           const void *y_for_relu_mask, const void *gamma, const void *save_mean,
                           const void *save_inv_std, void *dgamma, void *dbeta, void *dx,
@@ -148,6 +150,9 @@ int b2c_relu_forward(int dtype, int64_t count, const void *x, void *y, void *str
 int b2c_relu_backward(int dtype, int64_t count, const void *dy, const void *y, void *dx, void *stream);
 /* acc += other  (residual sum; pydtnn/backends/gpu/layers/addition_block_gpu.py:63,82) */
 int b2c_add_inplace(int dtype, int64_t count, void *acc, const void *other, void *stream);
+
+/* out = max(a + b, 0): the residual sum and the ReLU that follows an addition block, in one pass. */
+int b2c_add_relu(int dtype, int64_t count, const void *a, const void *b, void *out, void *stream);
 
 /* Pooling over in-bounds taps only (pydtnn/cython_modules/max_pool_2d_nhwc_cython.pyx:96-113,
  * average_pool_2d_nhwc_cython.pyx:93-111); idx_max is int32 tap number ii*kw+jj.

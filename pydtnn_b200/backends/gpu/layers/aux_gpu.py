@@ -9,6 +9,7 @@ from ....layers import (AdditionBlock, AveragePool2D, BatchNormalization, Dropou
                         Softmax)
 from ....tensor_gpu import TensorGPU, empty, to_gpu, zeros
 from ....utils import EVALUATE_MODE, PYDTNN_TENSOR_FORMAT_NCHW, TRAIN_MODE
+from .. import memory_allocation as wsp
 from .layer_gpu import LayerGPU
 
 
@@ -47,7 +48,7 @@ class BatchNormalizationGPU(LayerGPU, BatchNormalization):
         self.save_mean = TensorGPU(empty((c,), m.dtype), m.tensor_format)
         self.save_inv_var = TensorGPU(empty((c,), m.dtype), m.tensor_format)
         self._inv_std = empty((c,), m.dtype)
-        self._scratch = empty((64 * 2 * c,), np.float64)
+        wsp.require_reduction_scratch(c)
         self.y = TensorGPU(empty(x.ary.shape, m.dtype), m.tensor_format)
         if self.need_dx:
             self.dx = TensorGPU(empty(x.ary.shape, m.dtype), m.tensor_format)
@@ -59,13 +60,14 @@ class BatchNormalizationGPU(LayerGPU, BatchNormalization):
     def forward(self, x):
         m = self.model
         L = _lib.lib()
+        self.x = x
         if m.mode == TRAIN_MODE:
             _lib.check(L.b2c_bn_train_forward(self._dt, _layout(m), m.batch_size, self.ci, self._hw, x.ptr,
                                               self.gamma.ptr, self.beta.ptr, self.running_mean.ptr,
                                               self.running_var.ptr, float(self.momentum), float(self.epsilon),
                                               int(self.fuse_relu), self.y.ptr, self.save_mean.ptr,
-                                              self.save_inv_var.ptr, self._scratch.gpudata,
-                                              self._scratch.size * 8, m.stream_handle))
+                                              self.save_inv_var.ptr, wsp.reduction_scratch().data_ptr(),
+                                              wsp.reduction_scratch().numel() * 8, m.stream_handle))
             self.updated_running_var = True
         elif m.mode == EVALUATE_MODE:
             if self.updated_running_var:
@@ -84,8 +86,8 @@ class BatchNormalizationGPU(LayerGPU, BatchNormalization):
         _lib.check(_lib.lib().b2c_bn_train_backward(
             self._dt, _layout(m), m.batch_size, self.ci, self._hw, self.x.ptr, dy.ptr,
             self.y.ptr if self.fuse_relu else None, self.gamma.ptr, self.save_mean.ptr, self.save_inv_var.ptr,
-            self.dgamma.ptr, self.dbeta.ptr, self.dx.ptr if self.need_dx else None, self._scratch.gpudata,
-            self._scratch.size * 8, m.stream_handle))
+            self.dgamma.ptr, self.dbeta.ptr, self.dx.ptr if self.need_dx else None,
+            wsp.reduction_scratch().data_ptr(), wsp.reduction_scratch().numel() * 8, m.stream_handle))
         if self.need_dx:
             return self.dx
 
@@ -101,10 +103,13 @@ class ReluGPU(LayerGPU, Relu):
             self.dx = TensorGPU(empty(x.ary.shape, m.dtype), m.tensor_format)
         self._dt = _lib.dtype_code(m.dtype)
         self.absorbed = False            # True when the preceding BatchNormalization applies the ReLU itself
+        self.fed_by_block = False        # True when the preceding AdditionBlock writes max(sum, 0) into self.y
 
     def forward(self, x):
         if self.absorbed:
             return x
+        if self.fed_by_block:
+            return self.y
         _lib.check(_lib.lib().b2c_relu_forward(self._dt, self.y.size, x.ptr, self.y.ptr, self.model.stream_handle))
         return self.y
 
@@ -240,15 +245,21 @@ class AdditionBlockGPU(LayerGPU, AdditionBlock):
             raise NotImplementedError("the first path of an AdditionBlock must not be empty")
         self.y = self.paths[0][-1].y
         self._dt = _lib.dtype_code(m.dtype)
+        self.relu_after = None           # set by the model: the Relu layer that directly follows this block
 
     def forward(self, x):
         L = _lib.lib()
+        last = len(self.paths) - 1
         for i, p in enumerate(self.paths):
             y_i = x
             for layer in p:
                 y_i = layer.forward(y_i)
             if i == 0:
                 self.y = y_i
+            elif i == last and self.relu_after is not None:
+                # residual sum and the ReLU that follows in one pass: relu.y = max(y + y_i, 0)
+                _lib.check(L.b2c_add_relu(self._dt, self.y.size, self.y.ptr, y_i.ptr, self.relu_after.y.ptr,
+                                          self.model.stream_handle))
             else:
                 _lib.check(L.b2c_add_inplace(self._dt, self.y.size, self.y.ptr, y_i.ptr, self.model.stream_handle))
         return self.y

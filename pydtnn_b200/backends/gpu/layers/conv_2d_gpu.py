@@ -76,6 +76,7 @@ class Conv2DGPU(LayerGPU, Conv2D):
 
     def forward(self, x):
         L = _lib.lib()
+        self.x = x          # backward reads the tensor this call saw (a fused predecessor may hand over its own buffer)
         self._timed("fprop", lambda: L.b2c_conv_fprop(
             ctypes.byref(self.desc), x.ptr, self.weights.ptr, self.biases.ptr if self.use_bias else None, None, 0,
             self.y.ptr, wsp.ptr(), wsp.size(), self.model.stream_handle))

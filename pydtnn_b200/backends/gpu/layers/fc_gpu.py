@@ -34,6 +34,7 @@ class FCGPU(LayerGPU, FC):
 
     def forward(self, x):
         m = self.model
+        self.x = x
         _lib.check(_lib.lib().b2c_fc_forward(self._dt, self._engine, m.batch_size, self._in, self._out, x.ptr,
                                              self.weights.ptr, self.biases.ptr if self.use_bias else None,
                                              self.y.ptr, wsp.ptr(), wsp.size(), m.stream_handle))

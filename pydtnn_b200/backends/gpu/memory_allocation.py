@@ -23,3 +23,23 @@ def ptr():
 
 def size():
     return _buf.numel() if _buf is not None else 0
+
+
+_red = None
+
+
+def require_reduction_scratch(channels, device=None):
+    """Shared scratch (doubles) for per-channel reductions (batch norm statistics and gradients):
+    two doubles per channel and row chunk, enough chunks for about four CTAs per SM."""
+    global _red
+    gx = max(1, channels // 256)
+    chunks = max(64, (592 + gx - 1) // gx)
+    need = 2 * channels * chunks
+    if _red is None or _red.numel() < need:
+        device = device or (_red.device if _red is not None else torch.device("cuda", torch.cuda.current_device()))
+        _red = torch.empty(need, dtype=torch.float64, device=device)
+    return _red
+
+
+def reduction_scratch():
+    return _red

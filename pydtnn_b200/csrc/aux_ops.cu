@@ -156,13 +156,211 @@ __global__ void bn_bwd_dx_kernel(const T* __restrict__ x, const T* __restrict__ 
     }
 }
 
+
+// ---- float32 NHWC fast path (c % 4 == 0): float4 loads, per-thread fixed channel group ----------
+// The tensor is (rows, c4) float4 with c4 = c/4. A block is RX x CX threads (CX = min(c4, 64) channel
+// groups, RX = 256 / CX row lanes); grid.x walks channel-group blocks, grid.y row chunks. Every
+// thread keeps its 4 channels, so per-channel parameters are loaded once and reductions need no
+// index arithmetic per element.
+struct V4Geo { int c4, cx, rx, gx, chunks; int64_t rows; };
+
+static bool v4_ok(int dtype, int layout, int c, const void* a, const void* b, const void* d)
+{
+    if (dtype != B2C_F32 || layout != B2C_LAYOUT_NHWC || c % 4) return false;
+    int c4 = c / 4;
+    int cx = c4 < 64 ? c4 : 64;
+    if (256 % cx || c4 % cx) return false;
+    return (((uintptr_t)a | (uintptr_t)b | (uintptr_t)d) & 15) == 0;
+}
+static V4Geo v4_geo(int64_t rows, int c, int max_chunks)
+{
+    V4Geo g; g.c4 = c / 4; g.cx = g.c4 < 64 ? g.c4 : 64; g.rx = 256 / g.cx; g.gx = g.c4 / g.cx; g.rows = rows;
+    int64_t want = (148 * 4 + g.gx - 1) / g.gx;
+    int64_t by_rows = (rows + g.rx * 4 - 1) / (g.rx * 4);          // at least 4 rows per thread
+    int64_t ch = want < by_rows ? want : by_rows;
+    if (ch > max_chunks) ch = max_chunks;
+    if (ch < 1) ch = 1;
+    g.chunks = (int)ch;
+    return g;
+}
+
+// F(float4 index, channel-group index, v0[4], v1[4]) ; partial[chunk][2][c] doubles
+template <typename F>
+__global__ void __launch_bounds__(256) reduce2_v4_kernel(F f, double* __restrict__ partial, V4Geo g)
+{
+    __shared__ float sm[256][9];
+    const int cxi = threadIdx.x % g.cx, rxi = threadIdx.x / g.cx;
+    const int grp = blockIdx.x * g.cx + cxi;
+    const int64_t per = (g.rows + gridDim.y - 1) / gridDim.y;
+    const int64_t r0 = (int64_t)blockIdx.y * per, r1 = r0 + per < g.rows ? r0 + per : g.rows;
+    float a0[4] = {0.f, 0.f, 0.f, 0.f}, a1[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int64_t r = r0 + rxi; r < r1; r += g.rx) {
+        float v0[4], v1[4];
+        f(r * g.c4 + grp, grp, v0, v1);
+#pragma unroll
+        for (int e = 0; e < 4; e++) { a0[e] += v0[e]; a1[e] += v1[e]; }
+    }
+#pragma unroll
+    for (int e = 0; e < 4; e++) { sm[threadIdx.x][e] = a0[e]; sm[threadIdx.x][4 + e] = a1[e]; }
+    __syncthreads();
+    if (rxi == 0) {
+        double t[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int i = 0; i < g.rx; i++)
+#pragma unroll
+            for (int e = 0; e < 8; e++) t[e] += (double)sm[i * g.cx + cxi][e];
+        const int c = g.c4 * 4;
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            partial[((int64_t)blockIdx.y * 2 + 0) * c + grp * 4 + e] = t[e];
+            partial[((int64_t)blockIdx.y * 2 + 1) * c + grp * 4 + e] = t[4 + e];
+        }
+    }
+}
+
+struct StatV4 {
+    const float4* x;
+    __device__ void operator()(int64_t j, int, float (&v0)[4], float (&v1)[4]) const {
+        float4 v = x[j];
+        v0[0] = v.x; v0[1] = v.y; v0[2] = v.z; v0[3] = v.w;
+        v1[0] = v.x * v.x; v1[1] = v.y * v.y; v1[2] = v.z * v.z; v1[3] = v.w * v.w;
+    }
+};
+struct SumV4 {   // plain per-channel sum (bias gradient)
+    const float4* x;
+    __device__ void operator()(int64_t j, int, float (&v0)[4], float (&v1)[4]) const {
+        float4 v = x[j];
+        v0[0] = v.x; v0[1] = v.y; v0[2] = v.z; v0[3] = v.w;
+        v1[0] = v1[1] = v1[2] = v1[3] = 0.f;
+    }
+};
+struct BnBwdV4 {
+    const float4 *x, *dy, *y; const float *mean, *inv_std; int relu;
+    __device__ void operator()(int64_t j, int grp, float (&v0)[4], float (&v1)[4]) const {
+        float4 xv = x[j], g = dy[j];
+        if (relu) { float4 yv = y[j]; if (!(yv.x > 0.f)) g.x = 0.f; if (!(yv.y > 0.f)) g.y = 0.f; if (!(yv.z > 0.f)) g.z = 0.f; if (!(yv.w > 0.f)) g.w = 0.f; }
+        const float4 m = *reinterpret_cast<const float4*>(mean + grp * 4), is = *reinterpret_cast<const float4*>(inv_std + grp * 4);
+        v0[0] = g.x * ((xv.x - m.x) * is.x); v0[1] = g.y * ((xv.y - m.y) * is.y);
+        v0[2] = g.z * ((xv.z - m.z) * is.z); v0[3] = g.w * ((xv.w - m.w) * is.w);
+        v1[0] = g.x; v1[1] = g.y; v1[2] = g.z; v1[3] = g.w;
+    }
+};
+
+// One warp per channel sums the per-chunk partials (fixed order per lane, then a shuffle tree).
+// mode 0: batch statistics -> save_mean, save_inv_std, running averages. mode 1: (dgamma, dbeta).
+// mode 2: single sum -> out0.
+__global__ void reduce2_final_warp_kernel(const double* __restrict__ partial, int chunks, int c, int mode, double count,
+                                          double momentum, double eps, float* out0, float* out1, float* run0, float* run1)
+{
+    const int ch = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (ch >= c) return;
+    double s0 = 0.0, s1 = 0.0;
+    for (int i = lane; i < chunks; i += 32) { s0 += partial[((int64_t)i * 2) * c + ch]; s1 += partial[((int64_t)i * 2 + 1) * c + ch]; }
+    for (int o = 16; o > 0; o >>= 1) { s0 += __shfl_down_sync(0xffffffffu, s0, o); s1 += __shfl_down_sync(0xffffffffu, s1, o); }
+    if (lane) return;
+    if (mode == 0) {
+        double mean = s0 / count, var = s1 / count - mean * mean;
+        if (var < 0.0) var = 0.0;
+        out0[ch] = (float)mean; out1[ch] = (float)(1.0 / sqrt(var + eps));
+        run0[ch] = (float)(momentum * (double)run0[ch] + (1.0 - momentum) * mean);
+        run1[ch] = (float)(momentum * (double)run1[ch] + (1.0 - momentum) * var);
+    } else if (mode == 1) { out0[ch] = (float)s0; out1[ch] = (float)s1; }
+    else out0[ch] = (float)s0;
+}
+
+__global__ void __launch_bounds__(256) bn_apply_v4_kernel(const float4* __restrict__ x, float4* __restrict__ y, const float* __restrict__ mean,
+                                                          const float* __restrict__ inv_std, const float* __restrict__ gamma,
+                                                          const float* __restrict__ beta, V4Geo g, int relu)
+{
+    const int cxi = threadIdx.x % g.cx, rxi = threadIdx.x / g.cx;
+    const int grp = blockIdx.x * g.cx + cxi;
+    const float4 m = *reinterpret_cast<const float4*>(mean + grp * 4), is = *reinterpret_cast<const float4*>(inv_std + grp * 4);
+    const float4 ga = *reinterpret_cast<const float4*>(gamma + grp * 4), be = *reinterpret_cast<const float4*>(beta + grp * 4);
+    const int64_t per = (g.rows + gridDim.y - 1) / gridDim.y;
+    const int64_t r0 = (int64_t)blockIdx.y * per, r1 = r0 + per < g.rows ? r0 + per : g.rows;
+    for (int64_t r = r0 + rxi; r < r1; r += g.rx) {
+        float4 v = x[r * g.c4 + grp], o;
+        o.x = ga.x * ((v.x - m.x) * is.x) + be.x; o.y = ga.y * ((v.y - m.y) * is.y) + be.y;
+        o.z = ga.z * ((v.z - m.z) * is.z) + be.z; o.w = ga.w * ((v.w - m.w) * is.w) + be.w;
+        if (relu) { o.x = fmaxf(o.x, 0.f); o.y = fmaxf(o.y, 0.f); o.z = fmaxf(o.z, 0.f); o.w = fmaxf(o.w, 0.f); }
+        y[r * g.c4 + grp] = o;
+    }
+}
+
+__global__ void __launch_bounds__(256) bn_bwd_dx_v4_kernel(const float4* __restrict__ x, const float4* __restrict__ dy, const float4* __restrict__ y,
+                                                           const float* __restrict__ gamma, const float* __restrict__ mean,
+                                                           const float* __restrict__ inv_std, const float* __restrict__ dgamma,
+                                                           const float* __restrict__ dbeta, float4* __restrict__ dx, V4Geo g, int relu, float count)
+{
+    const int cxi = threadIdx.x % g.cx, rxi = threadIdx.x / g.cx;
+    const int grp = blockIdx.x * g.cx + cxi;
+    const float4 m = *reinterpret_cast<const float4*>(mean + grp * 4), is = *reinterpret_cast<const float4*>(inv_std + grp * 4);
+    const float4 ga = *reinterpret_cast<const float4*>(gamma + grp * 4);
+    const float4 dg = *reinterpret_cast<const float4*>(dgamma + grp * 4), db = *reinterpret_cast<const float4*>(dbeta + grp * 4);
+    const float4 sc = make_float4(ga.x * is.x / count, ga.y * is.y / count, ga.z * is.z / count, ga.w * is.w / count);
+    const int64_t per = (g.rows + gridDim.y - 1) / gridDim.y;
+    const int64_t r0 = (int64_t)blockIdx.y * per, r1 = r0 + per < g.rows ? r0 + per : g.rows;
+    for (int64_t r = r0 + rxi; r < r1; r += g.rx) {
+        const int64_t j = r * g.c4 + grp;
+        float4 xv = x[j], gd = dy[j], o;
+        if (relu) { float4 yv = y[j]; if (!(yv.x > 0.f)) gd.x = 0.f; if (!(yv.y > 0.f)) gd.y = 0.f; if (!(yv.z > 0.f)) gd.z = 0.f; if (!(yv.w > 0.f)) gd.w = 0.f; }
+        o.x = sc.x * (count * gd.x - ((xv.x - m.x) * is.x) * dg.x - db.x);
+        o.y = sc.y * (count * gd.y - ((xv.y - m.y) * is.y) * dg.y - db.y);
+        o.z = sc.z * (count * gd.z - ((xv.z - m.z) * is.z) * dg.z - db.z);
+        o.w = sc.w * (count * gd.w - ((xv.w - m.w) * is.w) * dg.w - db.w);
+        dx[j] = o;
+    }
+}
+
+static V4Geo v4_apply_geo(int64_t rows, int c)
+{
+    V4Geo g = v4_geo(rows, c, 1 << 20);
+    int64_t want = (148 * 8 + g.gx - 1) / g.gx;
+    int64_t by_rows = (rows + g.rx * 4 - 1) / (g.rx * 4);
+    g.chunks = (int)(want < by_rows ? want : by_rows);
+    if (g.chunks < 1) g.chunks = 1;
+    return g;
+}
+
+static int final_warp(const double* partial, int chunks, int c, int mode, double count, double momentum, double eps,
+                      float* o0, float* o1, float* r0, float* r1, cudaStream_t st)
+{
+    reduce2_final_warp_kernel<<<(c * 32 + 255) / 256, 256, 0, st>>>(partial, chunks, c, mode, count, momentum, eps, o0, o1, r0, r1);
+    return check_launch("reduce2_final_warp");
+}
+
+// Per-channel sum of an NHWC float32 tensor through the fast path (used for the bias gradient).
+int channel_sum_v4(int n, int c, int hw, const void* src, void* dst, void* ws, size_t ws_bytes, cudaStream_t st)
+{
+    if (!v4_ok(B2C_F32, B2C_LAYOUT_NHWC, c, src, src, src)) return 1;   // not applicable
+    int max_chunks = (int)(ws_bytes / ((size_t)2 * c * sizeof(double)));
+    if (max_chunks < 1) return 1;
+    V4Geo g = v4_geo((int64_t)n * hw, c, max_chunks);
+    SumV4 f{(const float4*)src};
+    reduce2_v4_kernel<SumV4><<<dim3(g.gx, g.chunks), 256, 0, st>>>(f, (double*)ws, g);
+    int rc = check_launch("reduce2_v4(sum)"); if (rc) return rc;
+    return final_warp((const double*)ws, g.chunks, c, 2, 1.0, 0.0, 0.0, (float*)dst, nullptr, nullptr, nullptr, st);
+}
+
 static unsigned ew_blocks(int64_t total) { int64_t b = (total + 255) / 256; return (unsigned)(b > 148 * 16 ? 148 * 16 : (b < 1 ? 1 : b)); }
 
 template <typename T>
 static int bn_train_forward_t(int layout, int n, int c, int hw, const T* x, const T* gamma, const T* beta,
                               T* rm, T* rv, double momentum, double eps, int relu, T* y, T* sm, T* si,
-                              double* scratch, cudaStream_t st)
+                              double* scratch, size_t scratch_bytes, cudaStream_t st)
 {
+    if (sizeof(T) == 4 && v4_ok(B2C_F32, layout, c, x, y, x)) {
+        int max_chunks = (int)(scratch_bytes / ((size_t)2 * c * sizeof(double)));
+        V4Geo g = v4_geo((int64_t)n * hw, c, max_chunks);
+        StatV4 f{(const float4*)x};
+        reduce2_v4_kernel<StatV4><<<dim3(g.gx, g.chunks), 256, 0, st>>>(f, scratch, g);
+        int rc = check_launch("reduce2_v4(stats)"); if (rc) return rc;
+        rc = final_warp(scratch, g.chunks, c, 0, (double)n * hw, momentum, eps, (float*)sm, (float*)si, (float*)rm, (float*)rv, st);
+        if (rc) return rc;
+        V4Geo ga = v4_apply_geo((int64_t)n * hw, c);
+        bn_apply_v4_kernel<<<dim3(ga.gx, ga.chunks), 256, 0, st>>>((const float4*)x, (float4*)y, (const float*)sm, (const float*)si,
+                                                                  (const float*)gamma, (const float*)beta, ga, relu);
+        return check_launch("bn_apply_v4");
+    }
     int chunks;
     StatF<T> f{x};
     int rc = launch_reduce2(f, scratch, layout, n, c, hw, chunks, st);
@@ -176,10 +374,25 @@ static int bn_train_forward_t(int layout, int n, int c, int hw, const T* x, cons
 
 template <typename T>
 static int bn_train_backward_t(int layout, int n, int c, int hw, const T* x, const T* dy, const T* y, const T* gamma,
-                               const T* sm, const T* si, T* dgamma, T* dbeta, T* dx, double* scratch, cudaStream_t st)
+                               const T* sm, const T* si, T* dgamma, T* dbeta, T* dx, double* scratch, size_t scratch_bytes,
+                               cudaStream_t st)
 {
     int chunks;
     int relu = y != nullptr;
+    if (sizeof(T) == 4 && v4_ok(B2C_F32, layout, c, x, dy, dx ? (const void*)dx : (const void*)x) && (!y || ((uintptr_t)y & 15) == 0)) {
+        int max_chunks = (int)(scratch_bytes / ((size_t)2 * c * sizeof(double)));
+        V4Geo g = v4_geo((int64_t)n * hw, c, max_chunks);
+        BnBwdV4 f{(const float4*)x, (const float4*)dy, (const float4*)y, (const float*)sm, (const float*)si, relu};
+        reduce2_v4_kernel<BnBwdV4><<<dim3(g.gx, g.chunks), 256, 0, st>>>(f, scratch, g);
+        int rc = check_launch("reduce2_v4(bn_bwd)"); if (rc) return rc;
+        rc = final_warp(scratch, g.chunks, c, 1, 1.0, 0.0, 0.0, (float*)dgamma, (float*)dbeta, nullptr, nullptr, st);
+        if (rc || !dx) return rc;
+        V4Geo ga = v4_apply_geo((int64_t)n * hw, c);
+        bn_bwd_dx_v4_kernel<<<dim3(ga.gx, ga.chunks), 256, 0, st>>>((const float4*)x, (const float4*)dy, (const float4*)y, (const float*)gamma,
+                                                                   (const float*)sm, (const float*)si, (const float*)dgamma, (const float*)dbeta,
+                                                                   (float4*)dx, ga, relu, (float)((double)n * hw));
+        return check_launch("bn_bwd_dx_v4");
+    }
     BnBwdF<T> f{x, dy, y, sm, si, relu};
     int rc = launch_reduce2(f, scratch, layout, n, c, hw, chunks, st);
     if (rc) return rc;
@@ -323,6 +536,98 @@ __global__ void pool_bwd_kernel(PoolP p, const T* __restrict__ dy, const int32_t
     }
 }
 
+
+// float32 NHWC pooling with 4 channels per thread (c % 4 == 0).
+template <bool IS_MAX>
+__global__ void __launch_bounds__(256) pool_fwd_v4_kernel(PoolP p, const float4* __restrict__ x, float4* __restrict__ y, int4* __restrict__ idx_max)
+{
+    const int c4 = p.c / 4;
+    const int64_t total = (int64_t)p.n * p.ho * p.wo * c4;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int cg = (int)(i % c4); int64_t r = i / c4;
+        const int yy = (int)(r % p.wo); r /= p.wo;
+        const int xx = (int)(r % p.ho); const int nn = (int)(r / p.ho);
+        float4 best = IS_MAX ? make_float4(-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX) : make_float4(0.f, 0.f, 0.f, 0.f);
+        int4 bi = make_int4(0, 0, 0, 0);
+        int items = 0;
+        for (int ii = 0; ii < p.kh; ii++) {
+            const int x_x = p.vstr * xx + p.vdil * ii - p.vpad;
+            if (x_x < 0 || x_x >= p.h) continue;
+            for (int jj = 0; jj < p.kw; jj++) {
+                const int x_y = p.hstr * yy + p.hdil * jj - p.hpad;
+                if (x_y < 0 || x_y >= p.w) continue;
+                const float4 v = x[(((int64_t)nn * p.h + x_x) * p.w + x_y) * c4 + cg];
+                if (IS_MAX) {
+                    const int t = ii * p.kw + jj;
+                    if (v.x > best.x) { best.x = v.x; bi.x = t; }
+                    if (v.y > best.y) { best.y = v.y; bi.y = t; }
+                    if (v.z > best.z) { best.z = v.z; bi.z = t; }
+                    if (v.w > best.w) { best.w = v.w; bi.w = t; }
+                } else { best.x += v.x; best.y += v.y; best.z += v.z; best.w += v.w; items++; }
+            }
+        }
+        if (IS_MAX) { y[i] = best; if (idx_max) idx_max[i] = bi; }
+        else { const float inv = (float)items; y[i] = make_float4(best.x / inv, best.y / inv, best.z / inv, best.w / inv); }
+    }
+}
+
+template <bool IS_MAX>
+__global__ void __launch_bounds__(256) pool_bwd_v4_kernel(PoolP p, const float4* __restrict__ dy, const int4* __restrict__ idx_max, float4* __restrict__ dx)
+{
+    const int c4 = p.c / 4;
+    const int64_t total = (int64_t)p.n * p.h * p.w * c4;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int cg = (int)(i % c4); int64_t r = i / c4;
+        const int iw = (int)(r % p.w); r /= p.w;
+        const int ih = (int)(r % p.h); const int nn = (int)(r / p.h);
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int ii = 0; ii < p.kh; ii++) {
+            const int t = ih + p.vpad - p.vdil * ii;
+            if (t < 0 || t % p.vstr) continue;
+            const int xx = t / p.vstr;
+            if (xx >= p.ho) continue;
+            for (int jj = 0; jj < p.kw; jj++) {
+                const int u = iw + p.hpad - p.hdil * jj;
+                if (u < 0 || u % p.hstr) continue;
+                const int yy = u / p.hstr;
+                if (yy >= p.wo) continue;
+                const int64_t o = (((int64_t)nn * p.ho + xx) * p.wo + yy) * c4 + cg;
+                const float4 g = dy[o];
+                if (IS_MAX) {
+                    const int4 id = idx_max[o];
+                    const int tap = ii * p.kw + jj;
+                    if (id.x == tap) acc.x += g.x;
+                    if (id.y == tap) acc.y += g.y;
+                    if (id.z == tap) acc.z += g.z;
+                    if (id.w == tap) acc.w += g.w;
+                } else {
+                    int items = 0;
+                    for (int a = 0; a < p.kh; a++) { int q = p.vstr * xx + p.vdil * a - p.vpad; if (q < 0 || q >= p.h) continue;
+                        for (int b = 0; b < p.kw; b++) { int r2 = p.hstr * yy + p.hdil * b - p.hpad; if (r2 >= 0 && r2 < p.w) items++; } }
+                    const float inv = (float)items;
+                    acc.x += g.x / inv; acc.y += g.y / inv; acc.z += g.z / inv; acc.w += g.w / inv;
+                }
+            }
+        }
+        dx[i] = acc;
+    }
+}
+
+// out = max(a + b, 0)  (residual sum followed by ReLU in one pass)
+__global__ void add_relu_f4_kernel(const float4* __restrict__ a, const float4* __restrict__ b, float4* __restrict__ out, int64_t n4)
+{
+    int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+        float4 u = a[i], v = b[i];
+        out[i] = make_float4(fmaxf(u.x + v.x, 0.f), fmaxf(u.y + v.y, 0.f), fmaxf(u.z + v.z, 0.f), fmaxf(u.w + v.w, 0.f));
+    }
+}
+template <typename T> __global__ void add_relu_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, int64_t n)
+{
+    int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) { T v = a[i] + b[i]; out[i] = v > T(0) ? v : T(0); }
+}
+
 // ---- softmax / cross-entropy -------------------------------------------------------------------
 
 template <typename T> __device__ T block_reduce(T v, T* sm, bool is_max)
@@ -418,9 +723,9 @@ extern "C" int b2c_bn_train_forward(int dtype, int layout, int n, int c, int hw,
     cudaStream_t st = (cudaStream_t)stream;
     if (dtype == B2C_F32)
         return bn_train_forward_t<float>(layout, n, c, hw, (const float*)x, (const float*)gamma, (const float*)beta, (float*)running_mean,
-                                         (float*)running_var, momentum, eps, fuse_relu, (float*)y, (float*)save_mean, (float*)save_inv_std, (double*)scratch, st);
+                                         (float*)running_var, momentum, eps, fuse_relu, (float*)y, (float*)save_mean, (float*)save_inv_std, (double*)scratch, scratch_bytes, st);
     return bn_train_forward_t<double>(layout, n, c, hw, (const double*)x, (const double*)gamma, (const double*)beta, (double*)running_mean,
-                                      (double*)running_var, momentum, eps, fuse_relu, (double*)y, (double*)save_mean, (double*)save_inv_std, (double*)scratch, st);
+                                      (double*)running_var, momentum, eps, fuse_relu, (double*)y, (double*)save_mean, (double*)save_inv_std, (double*)scratch, scratch_bytes, st);
 }
 
 extern "C" int b2c_bn_train_backward(int dtype, int layout, int n, int c, int hw, const void* x, const void* dy,
@@ -435,9 +740,9 @@ extern "C" int b2c_bn_train_backward(int dtype, int layout, int n, int c, int hw
     cudaStream_t st = (cudaStream_t)stream;
     if (dtype == B2C_F32)
         return bn_train_backward_t<float>(layout, n, c, hw, (const float*)x, (const float*)dy, (const float*)y_for_relu_mask, (const float*)gamma,
-                                          (const float*)save_mean, (const float*)save_inv_std, (float*)dgamma, (float*)dbeta, (float*)dx, (double*)scratch, st);
+                                          (const float*)save_mean, (const float*)save_inv_std, (float*)dgamma, (float*)dbeta, (float*)dx, (double*)scratch, scratch_bytes, st);
     return bn_train_backward_t<double>(layout, n, c, hw, (const double*)x, (const double*)dy, (const double*)y_for_relu_mask, (const double*)gamma,
-                                       (const double*)save_mean, (const double*)save_inv_std, (double*)dgamma, (double*)dbeta, (double*)dx, (double*)scratch, st);
+                                       (const double*)save_mean, (const double*)save_inv_std, (double*)dgamma, (double*)dbeta, (double*)dx, (double*)scratch, scratch_bytes, st);
 }
 
 extern "C" int b2c_bn_inference(int dtype, int layout, int n, int c, int hw, const void* x, const void* mean,
@@ -448,6 +753,12 @@ extern "C" int b2c_bn_inference(int dtype, int layout, int n, int c, int hw, con
     if (n <= 0 || c <= 0 || hw <= 0) return B2C_ERR_BAD_GEOMETRY;
     cudaStream_t st = (cudaStream_t)stream;
     int64_t total = (int64_t)n * c * hw;
+    if (v4_ok(dtype, layout, c, x, y, x)) {
+        V4Geo ga = v4_apply_geo((int64_t)n * hw, c);
+        bn_apply_v4_kernel<<<dim3(ga.gx, ga.chunks), 256, 0, st>>>((const float4*)x, (float4*)y, (const float*)mean, (const float*)inv_std,
+                                                                  (const float*)gamma, (const float*)beta, ga, relu);
+        return check_launch("bn_inference_v4");
+    }
     if (dtype == B2C_F32)
         bn_apply_kernel<float><<<ew_blocks(total), 256, 0, st>>>((const float*)x, (float*)y, (const float*)mean, (const float*)inv_std,
                                                                 (const float*)gamma, (const float*)beta, total, c, hw, layout == B2C_LAYOUT_NCHW, relu, 1);
@@ -499,6 +810,20 @@ extern "C" int b2c_add_inplace(int dtype, int64_t count, void* acc, const void* 
     return check_launch("add_inplace");
 }
 
+extern "C" int b2c_add_relu(int dtype, int64_t count, const void* a, const void* b, void* out, void* stream)
+{
+    CHECK_DTYPE(dtype);
+    if (!a || !b || !out) return B2C_ERR_NULL_POINTER;
+    if (count < 0) return B2C_ERR_BAD_GEOMETRY;
+    if (count == 0) return B2C_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == B2C_F32) {
+        if (f4_ok(count, a, b, out)) add_relu_f4_kernel<<<ew_blocks(count / 4), 256, 0, st>>>((const float4*)a, (const float4*)b, (float4*)out, count / 4);
+        else add_relu_kernel<float><<<ew_blocks(count), 256, 0, st>>>((const float*)a, (const float*)b, (float*)out, count);
+    } else add_relu_kernel<double><<<ew_blocks(count), 256, 0, st>>>((const double*)a, (const double*)b, (double*)out, count);
+    return check_launch("add_relu");
+}
+
 static int make_pool(PoolP& p, int layout, int n, int h, int w, int c, int kh, int kw, int vpad, int hpad, int vstr,
                      int hstr, int vdil, int hdil)
 {
@@ -522,6 +847,11 @@ extern "C" int b2c_pool_forward(int dtype, int layout, int is_max, int n, int h,
     PoolP p; int rc = make_pool(p, layout, n, h, w, c, kh, kw, vpad, hpad, vstr, hstr, vdil, hdil); if (rc) return rc;
     cudaStream_t st = (cudaStream_t)stream;
     int64_t total = (int64_t)n * p.ho * p.wo * c; int nchw = layout == B2C_LAYOUT_NCHW;
+    if (dtype == B2C_F32 && !nchw && c % 4 == 0 && (((uintptr_t)x | (uintptr_t)y | (uintptr_t)idx_max) & 15) == 0) {
+        if (is_max) pool_fwd_v4_kernel<true><<<ew_blocks(total / 4), 256, 0, st>>>(p, (const float4*)x, (float4*)y, (int4*)idx_max);
+        else pool_fwd_v4_kernel<false><<<ew_blocks(total / 4), 256, 0, st>>>(p, (const float4*)x, (float4*)y, (int4*)idx_max);
+        return check_launch("pool_forward_v4");
+    }
     if (dtype == B2C_F32) {
         if (is_max) pool_fwd_kernel<float, true><<<ew_blocks(total), 256, 0, st>>>(p, (const float*)x, (float*)y, idx_max, nchw);
         else pool_fwd_kernel<float, false><<<ew_blocks(total), 256, 0, st>>>(p, (const float*)x, (float*)y, idx_max, nchw);
@@ -541,6 +871,11 @@ extern "C" int b2c_pool_backward(int dtype, int layout, int is_max, int n, int h
     PoolP p; int rc = make_pool(p, layout, n, h, w, c, kh, kw, vpad, hpad, vstr, hstr, vdil, hdil); if (rc) return rc;
     cudaStream_t st = (cudaStream_t)stream;
     int64_t total = (int64_t)n * h * w * c; int nchw = layout == B2C_LAYOUT_NCHW;
+    if (dtype == B2C_F32 && !nchw && c % 4 == 0 && (((uintptr_t)dy | (uintptr_t)dx | (uintptr_t)idx_max) & 15) == 0) {
+        if (is_max) pool_bwd_v4_kernel<true><<<ew_blocks(total / 4), 256, 0, st>>>(p, (const float4*)dy, (const int4*)idx_max, (float4*)dx);
+        else pool_bwd_v4_kernel<false><<<ew_blocks(total / 4), 256, 0, st>>>(p, (const float4*)dy, (const int4*)idx_max, (float4*)dx);
+        return check_launch("pool_backward_v4");
+    }
     if (dtype == B2C_F32) {
         if (is_max) pool_bwd_kernel<float, true><<<ew_blocks(total), 256, 0, st>>>(p, (const float*)dy, idx_max, (float*)dx, nchw);
         else pool_bwd_kernel<float, false><<<ew_blocks(total), 256, 0, st>>>(p, (const float*)dy, idx_max, (float*)dx, nchw);

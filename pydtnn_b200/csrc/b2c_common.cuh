@@ -81,6 +81,7 @@ int fma_index_map(const Geo& g, int64_t* map, cudaStream_t st);
 int channel_sum(int dtype, int layout, int n, int c, int hw, const void* src, void* dst, void* ws, size_t ws_bytes,
                 cudaStream_t st);
 size_t channel_sum_workspace_bytes(int n, int c, int hw);
+int channel_sum_v4(int n, int c, int hw, const void* src, void* dst, void* ws, size_t ws_bytes, cudaStream_t st);
 
 // tensor-core engine (conv_tc.cu)
 bool tc_supported(const Geo& g, int pass);

@@ -479,13 +479,25 @@ __global__ void channel_sum_final_kernel(const double* __restrict__ partial, T* 
     dst[ch] = (T)s;
 }
 
-size_t channel_sum_workspace_bytes(int n, int c, int hw) { (void)n; (void)hw; return (size_t)CS_CHUNKS * c * sizeof(double); }
+// Enough for the float4 fast path to spread over about four CTAs per SM: two doubles per channel and chunk.
+size_t channel_sum_workspace_bytes(int n, int c, int hw)
+{
+    (void)n; (void)hw;
+    int gx = c / 256 > 0 ? c / 256 : 1;
+    int chunks = (592 + gx - 1) / gx;
+    if (chunks < CS_CHUNKS) chunks = CS_CHUNKS;
+    return (size_t)chunks * 2 * c * sizeof(double);
+}
 
 int channel_sum(int dtype, int layout, int n, int c, int hw, const void* src, void* dst, void* ws, size_t ws_bytes,
                 cudaStream_t st)
 {
     if (!src || !dst || !ws) return B2C_ERR_NULL_POINTER;
-    if (ws_bytes < channel_sum_workspace_bytes(n, c, hw)) return B2C_ERR_WORKSPACE_TOO_SMALL;
+    if (ws_bytes < (size_t)CS_CHUNKS * c * sizeof(double)) return B2C_ERR_WORKSPACE_TOO_SMALL;
+    if (dtype == B2C_F32 && layout == B2C_LAYOUT_NHWC) {
+        int r = channel_sum_v4(n, c, hw, src, dst, ws, ws_bytes, st);
+        if (r != 1) return r;     // 1 = fast path not applicable
+    }
     double* partial = (double*)ws;
     int64_t rows = (int64_t)n * hw;
     int chunks = (int)(rows < CS_CHUNKS ? rows : CS_CHUNKS);

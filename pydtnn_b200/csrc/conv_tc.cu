@@ -18,13 +18,16 @@
 // activation tiles are split in shared memory by the transform warps between TMA arrival and MMA
 // issue.
 //
-// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
-// warps 2-5 = operand transform during the main loop, then epilogue (TMEM -> registers ->
-// bias / BN-scale / ReLU -> global).  Every mbarrier wait is bounded: when a wait runs out the
-// CTA raises an abort flag, records a status word in global memory, skips its remaining work,
-// frees its tensor memory and returns.
+// Warp roles (320 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
+// warps 2-5 = operand transform (hi/lo split of the activation tiles in shared memory),
+// warps 6-9 = drain + epilogue: the tensor core's accumulate step truncates, so sums are kept in
+// tensor memory only for a chunk of 8 k-blocks (two TMEM buffers alternate) and added chunk by
+// chunk into float32 registers with round-to-nearest, then bias / BN-scale / ReLU -> global.
+// Every mbarrier wait is bounded: when a wait runs out the CTA raises an abort flag, records a
+// status word in global memory, skips its remaining work, frees its tensor memory and returns.
 #include "b2c_common.cuh"
 #include <cuda.h>
+#include <stdlib.h>
 
 namespace b2c {
 
@@ -120,17 +123,19 @@ __device__ __forceinline__ float to_tf32_rn(float v) {
     return __uint_as_float(r);
 }
 
-// Shared-memory matrix descriptor, 128-byte swizzle, rows of 128 bytes, 8-row groups 1024 bytes
-// apart.  K-major: the 128-byte row is 32 K elements of one M/N row (leading offset unused).
-// MN-major: the 128-byte row is 32 M/N elements of one K index; further 32-element groups lie
-// `lbo_bytes` apart.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+// Shared-memory matrix descriptor for tiles made of 128-byte rows.
+//  K-major (layout 2 = 128B swizzle): a row is 32 K elements of one M/N row; 8-row groups lie
+//    `sbo_bytes` (1024) apart; the leading offset is unused.
+//  MN-major (layout 1 = 128B swizzle with 32-byte atoms, the only MN-major layout tf32 operands may
+//    use): a row is 32 M/N elements of one K index; 4-row K groups lie `sbo_bytes` (512) apart and
+//    further 32-element M/N groups `lbo_bytes` apart.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
     uint64_t d = 0;
     d |= (uint64_t)((saddr >> 4) & 0x3FFF);
     d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
     d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
     d |= (uint64_t)1 << 46;     // descriptor version for sm_100
-    d |= (uint64_t)2 << 61;     // SWIZZLE_128B
+    d |= (uint64_t)layout << 61;
     return d;
 }
 // Instruction descriptor: tf32 x tf32 -> f32, dense.
@@ -142,15 +147,15 @@ __host__ __device__ constexpr uint32_t make_idesc_tf32(int M, int N, int a_mn_ma
 // Device status word shared by all tensor-core kernels (0 = fine).
 __device__ int g_tc_status = 0;
 
-enum { TC_ERR_FULL = 1, TC_ERR_XFORM = 2, TC_ERR_EMPTY = 3, TC_ERR_ACCUM = 4 };
+enum { TC_ERR_FULL = 1, TC_ERR_XFORM = 2, TC_ERR_EMPTY = 3, TC_ERR_TFULL = 4, TC_ERR_TEMPTY = 5 };
 
 // ---------------------------------------------------------------------------------------------
-// Filter preparation: hi/lo split into the K-major GEMM layout the kernels read through TMA
+// Filter preparation: hi/lo split into the K-major GEMM layout the fprop/dgrad kernel reads by TMA
 // ---------------------------------------------------------------------------------------------
 struct PrepParams {
-    int rows, C, R, S;          // output is [rows][(r*S+s)*C + c]
-    int64_t s_row, s_c, s_r, s_s;  // element strides of the source filter by (row, c, r, s)
-    int flip;                   // 1: read tap (R-1-r, S-1-s)
+    int rows, C, R, S;               // output is [rows][(r*S+s)*C + c], r < R, s < S (virtual taps)
+    int64_t s_row, s_c, s_r, s_s;    // element strides of the source filter by (row, c, r, s)
+    int r0, rstep, s0, sstep;        // real tap of virtual tap (r, s): (r0 + rstep*r, s0 + sstep*s)
 };
 
 __global__ void tc_prep_filter_kernel(PrepParams p, const float* __restrict__ w, float* __restrict__ hi, float* __restrict__ lo)
@@ -161,7 +166,7 @@ __global__ void tc_prep_filter_kernel(PrepParams p, const float* __restrict__ w,
         int row = (int)(i / K);
         int k = (int)(i - (int64_t)row * K);
         int c = k % p.C; int rs = k / p.C; int r = rs / p.S; int s = rs - r * p.S;
-        if (p.flip) { r = p.R - 1 - r; s = p.S - 1 - s; }
+        r = p.r0 + p.rstep * r; s = p.s0 + p.sstep * s;
         float v = w[row * p.s_row + c * p.s_c + r * p.s_r + s * p.s_s];
         float h = to_tf32_rn(v);
         hi[i] = h;
@@ -170,53 +175,72 @@ __global__ void tc_prep_filter_kernel(PrepParams p, const float* __restrict__ w,
 }
 
 // ---------------------------------------------------------------------------------------------
-// fprop / dgrad kernel
+// The kernel (one template, two modes)
 // ---------------------------------------------------------------------------------------------
-struct FwdParams {
-    int M, N;                 // GEMM rows (output pixels n*P*Q) and columns (output channels)
-    int P, Q;                 // output grid per image
-    int kblocks, cblocks, S;  // K loop: taps * cblocks blocks of 32 channels; S = filter width
-    int str_h, str_w, pad_h, pad_w, dil_h, dil_w;
+enum { TCM_FWD = 0, TCM_WGRAD = 1 };
+
+#define TC_CHUNK 8   // k-blocks accumulated in tensor memory before the partial sum is drained
+
+struct TcParams {
+    // FWD: GEMM rows = output pixels, columns = output channels. WGRAD: rows = (tap, ci), columns = co.
+    int M, N;
+    int P, Q;                  // pixel grid per image the pixel index runs over
+    int kblocks;               // FWD: taps * cblocks.  WGRAD: 32-pixel blocks per split
+    int cblocks, S;            // channel blocks of 32 per tap, filter width
+    int C;                     // gathered channels per tap
+    int str_h, str_w, dil_h, dil_w;
+    int low_h, low_w;          // lower corner of the im2col window (= -padding for a plain convolution)
+    int Mpix;                  // WGRAD: total pixels
+    int splits;                // WGRAD: pixel ranges (1 for FWD)
+    // FWD epilogue
     const float *bias, *mean, *inv_std, *gamma, *beta;
     int relu;
-    float* out;               // [M][N]
+    float* out;                // FWD: row m=(n,i,j) at out + n*o_sn + i*o_sh + j*o_sw.  WGRAD: partial [split][M][N]
+    int64_t o_sn, o_sh, o_sw;
 };
 
 template <int BN, int STAGES>
-struct FwdSmem {
-    static constexpr int A_BYTES = 128 * 128;   // 128 pixels x 32 floats
+struct TcSmem {
+    static constexpr int A_BYTES = 128 * 128;   // 128 rows x 32 floats (FWD) or 32 pixels x 128 rows (WGRAD)
     static constexpr int B_BYTES = BN * 128;
     static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
     static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
     static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;   // + barriers/flags + alignment slack
 };
 
-template <int BN, int STAGES>
-__global__ void __launch_bounds__(192, 1)
-conv_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_bhi,
-                   const __grid_constant__ CUtensorMap tmap_blo, FwdParams p)
+template <int MODE, int BN, int STAGES, bool WRITE_HI>
+__global__ void __launch_bounds__(320, 1)
+conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b0,
+               const __grid_constant__ CUtensorMap tmap_b1, TcParams p)
 {
-    using L = FwdSmem<BN, STAGES>;
+    // Persistent: each CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ... (column tile fastest, so
+    // CTAs running at the same time share activation rows in L2).  The smem pipeline and the two TMEM
+    // buffers keep running across tile boundaries: the producer prefetches the next tile while the
+    // drain warps still store the previous one.
+    using L = TcSmem<BN, STAGES>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* full_bar = (uint64_t*)(smem + L::BAR_OFFSET);
     uint64_t* xform_bar = full_bar + STAGES;
     uint64_t* empty_bar = xform_bar + STAGES;
-    uint64_t* accum_bar = empty_bar + STAGES;
-    uint32_t* tmem_slot = (uint32_t*)(accum_bar + 1);
+    uint64_t* tfull_bar = empty_bar + STAGES;
+    uint64_t* tempty_bar = tfull_bar + 2;
+    uint32_t* tmem_slot = (uint32_t*)(tempty_bar + 2);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.x * 128, n0 = blockIdx.y * BN;
+    const int mt = (p.M + 127) / 128, nt = (p.N + BN - 1) / BN;
+    const int total_tiles = mt * nt * p.splits;
+    const int nchunks = (p.kblocks + TC_CHUNK - 1) / TC_CHUNK;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&xform_bar[s], 4); mbar_init(&empty_bar[s], 1); }
-        mbar_init(accum_bar, 1);
+        for (int b = 0; b < 2; b++) { mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], 4); }
         *abort_flag = 0;
         fence_barrier_init();
         fence_proxy_async();
     }
-    if (warp == 1) { tmem_alloc(tmem_slot, BN); tmem_relinquish(); }
+    if (warp == 1) { tmem_alloc(tmem_slot, 2 * BN); tmem_relinquish(); }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -225,100 +249,214 @@ conv_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
-            const int img = m0 / (p.P * p.Q);
-            const int rem = m0 - img * (p.P * p.Q);
-            const int p0 = rem / p.Q, q0 = rem - p0 * p.Q;
-            const int base_w = q0 * p.str_w - p.pad_w, base_h = p0 * p.str_h - p.pad_h;
-            for (int kb = 0; kb < p.kblocks; kb++) {
-                const int s = kb % STAGES, use = kb / STAGES;
-                if (use > 0 && !mbar_wait(&empty_bar[s], (use - 1) & 1, abort_flag, &g_tc_status, TC_ERR_EMPTY)) break;
-                uint8_t* st = smem + s * L::STAGE_BYTES;
-                const int tap = kb / p.cblocks, cb = kb - tap * p.cblocks;
-                const int r = tap / p.S, sx = tap - r * p.S;
-                mbar_expect_tx(&full_bar[s], L::A_BYTES + 2 * L::B_BYTES);
-                tma_load_im2col_4d(st, &tmap_a, &full_bar[s], cb * 32, base_w, base_h, img,
-                                   (uint16_t)(sx * p.dil_w), (uint16_t)(r * p.dil_h));
-                tma_load_2d(st + 2 * L::A_BYTES, &tmap_bhi, &full_bar[s], kb * 32, n0);
-                tma_load_2d(st + 2 * L::A_BYTES + L::B_BYTES, &tmap_blo, &full_bar[s], kb * 32, n0);
+            int it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int ni = tile % nt, rest = tile / nt, mi = rest % mt, z = rest / mt;
+                const int m0 = mi * 128, n0 = ni * BN;
+                int img = 0, base_w = 0, base_h = 0;
+                if (MODE == TCM_FWD) {
+                    img = m0 / (p.P * p.Q);
+                    const int rem = m0 - img * (p.P * p.Q);
+                    const int p0 = rem / p.Q, q0 = rem - p0 * p.Q;
+                    base_w = q0 * p.str_w + p.low_w; base_h = p0 * p.str_h + p.low_h;
+                }
+                const int pix_begin = (MODE == TCM_WGRAD) ? z * p.kblocks * 32 : 0;
+                for (int kb = 0; kb < p.kblocks; kb++, it++) {
+                    const int s = it % STAGES, use = it / STAGES;
+                    if (use > 0 && !mbar_wait(&empty_bar[s], (use - 1) & 1, abort_flag, &g_tc_status, TC_ERR_EMPTY)) { ok = false; break; }
+                    uint8_t* st = smem + s * L::STAGE_BYTES;
+                    if (MODE == TCM_FWD) {
+                        const int tap = kb / p.cblocks, cb = kb - tap * p.cblocks;
+                        const int r = tap / p.S, sx = tap - r * p.S;
+                        mbar_expect_tx(&full_bar[s], L::A_BYTES + 2 * L::B_BYTES);
+                        tma_load_im2col_4d(st, &tmap_a, &full_bar[s], cb * 32, base_w, base_h, img,
+                                           (uint16_t)(sx * p.dil_w), (uint16_t)(r * p.dil_h));
+                        tma_load_2d(st + 2 * L::A_BYTES, &tmap_b0, &full_bar[s], kb * 32, n0);
+                        tma_load_2d(st + 2 * L::A_BYTES + L::B_BYTES, &tmap_b1, &full_bar[s], kb * 32, n0);
+                    } else {
+                        const int pix0 = pix_begin + kb * 32;
+                        const int im = pix0 / (p.P * p.Q);
+                        const int rem = pix0 - im * (p.P * p.Q);
+                        const int p0 = rem / p.Q, q0 = rem - p0 * p.Q;
+                        const int bw = q0 * p.str_w + p.low_w, bh = p0 * p.str_h + p.low_h;
+                        int boxes = 0;
+#pragma unroll
+                        for (int j = 0; j < 4; j++) if (m0 + 32 * j < p.M) boxes++;
+#pragma unroll
+                        for (int j = 0; j < BN / 32; j++) if (n0 + 32 * j < p.N) boxes++;
+                        mbar_expect_tx(&full_bar[s], boxes * 4096);
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            const int mrow = m0 + 32 * j;
+                            if (mrow < p.M) {
+                                const int tap = mrow / p.C, c0 = mrow - tap * p.C;
+                                const int r = tap / p.S, sx = tap - r * p.S;
+                                tma_load_im2col_4d(st + j * 4096, &tmap_a, &full_bar[s], c0, bw, bh, im,
+                                                   (uint16_t)(sx * p.dil_w), (uint16_t)(r * p.dil_h));
+                            }
+                        }
+#pragma unroll
+                        for (int j = 0; j < BN / 32; j++)
+                            if (n0 + 32 * j < p.N)
+                                tma_load_2d(st + 2 * L::A_BYTES + j * 4096, &tmap_b0, &full_bar[s], n0 + 32 * j, pix0);
+                    }
+                }
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc_tf32(128, BN, 0, 0);
+            constexpr uint32_t idesc = make_idesc_tf32(128, BN, MODE == TCM_WGRAD, MODE == TCM_WGRAD);
+            // K-major tiles: rows of 128 B, 8-row groups 1024 B apart, K advances 32 B inside the row.
+            // MN-major tiles: 32-row (K) boxes of 4096 B per 32 M/N elements, 4-row swizzle atoms of 512 B,
+            // K advances by 8 rows = 1024 B.
+            constexpr uint32_t LBO = (MODE == TCM_WGRAD) ? 4096 : 0;
+            constexpr uint32_t SBO = (MODE == TCM_WGRAD) ? 512 : 1024;
+            constexpr uint32_t LAYOUT = (MODE == TCM_WGRAD) ? 1 : 2;
+            constexpr uint64_t KADV = (MODE == TCM_WGRAD) ? (1024 >> 4) : (32 >> 4);
             bool ok = true;
-            for (int kb = 0; kb < p.kblocks && ok; kb++) {
-                const int s = kb % STAGES, use = kb / STAGES;
-                ok = mbar_wait(&full_bar[s], use & 1, abort_flag, &g_tc_status, TC_ERR_FULL) &&
-                     mbar_wait(&xform_bar[s], use & 1, abort_flag, &g_tc_status, TC_ERR_XFORM);
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
-                const uint64_t a_hi = make_smem_desc(sa, 0, 1024);
-                const uint64_t a_lo = make_smem_desc(sa + L::A_BYTES, 0, 1024);
-                const uint64_t b_hi = make_smem_desc(sa + 2 * L::A_BYTES, 0, 1024);
-                const uint64_t b_lo = make_smem_desc(sa + 2 * L::A_BYTES + L::B_BYTES, 0, 1024);
+            int it = 0, gc = 0;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                for (int kb = 0; kb < p.kblocks && ok; kb++, it++) {
+                    const int s = it % STAGES, use = it / STAGES;
+                    const int b = gc & 1;
+                    const bool chunk_start = (kb % TC_CHUNK) == 0;
+                    if (chunk_start && gc >= 2) {
+                        ok = mbar_wait(&tempty_bar[b], ((gc >> 1) - 1) & 1, abort_flag, &g_tc_status, TC_ERR_TEMPTY);
+                        if (!ok) break;
+                    }
+                    ok = mbar_wait(&full_bar[s], use & 1, abort_flag, &g_tc_status, TC_ERR_FULL) &&
+                         mbar_wait(&xform_bar[s], use & 1, abort_flag, &g_tc_status, TC_ERR_XFORM);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
+                    const uint64_t a_hi = make_smem_desc(sa, LBO, SBO, LAYOUT);
+                    const uint64_t a_lo = make_smem_desc(sa + L::A_BYTES, LBO, SBO, LAYOUT);
+                    const uint64_t b_hi = make_smem_desc(sa + 2 * L::A_BYTES, LBO, SBO, LAYOUT);
+                    const uint64_t b_lo = make_smem_desc(sa + 2 * L::A_BYTES + L::B_BYTES, LBO, SBO, LAYOUT);
+                    const uint32_t d = tmem_base + (uint32_t)(b * BN);
 #pragma unroll
-                for (int k = 0; k < 4; k++) {           // 4 x (K = 8 tf32 = 32 bytes) per 128-byte row
-                    const uint64_t adv = (uint64_t)(k * 2);
-                    umma_tf32(tmem_base, a_lo + adv, b_hi + adv, idesc, (kb > 0 || k > 0) ? 1u : 0u);
-                    umma_tf32(tmem_base, a_hi + adv, b_lo + adv, idesc, 1u);
-                    umma_tf32(tmem_base, a_hi + adv, b_hi + adv, idesc, 1u);
+                    for (int k = 0; k < 4; k++) {
+                        const uint64_t adv = (uint64_t)k * KADV;
+                        umma_tf32(d, a_lo + adv, b_hi + adv, idesc, (!chunk_start || k > 0) ? 1u : 0u);
+                        umma_tf32(d, a_hi + adv, b_lo + adv, idesc, 1u);
+                        umma_tf32(d, a_hi + adv, b_hi + adv, idesc, 1u);
+                    }
+                    umma_commit(&empty_bar[s]);
+                    if ((kb % TC_CHUNK) == TC_CHUNK - 1 || kb == p.kblocks - 1) { umma_commit(&tfull_bar[b]); gc++; }
                 }
-                umma_commit(&empty_bar[s]);
             }
-            if (ok) umma_commit(accum_bar);
+        }
+    } else if (warp < 6) {
+        // ---------------- operand transform: a = hi + lo ----------------
+        const int t = threadIdx.x - 64;      // 0..127
+        constexpr int A_VEC = L::A_BYTES / 16 / 128;                 // float4 per thread for the A tile
+        constexpr int B_VEC = (MODE == TCM_WGRAD) ? L::B_BYTES / 16 / 128 : 0;
+        int it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            for (int kb = 0; kb < p.kblocks; kb++, it++) {
+                const int s = it % STAGES, use = it / STAGES;
+                if (!mbar_wait(&full_bar[s], use & 1, abort_flag, &g_tc_status, TC_ERR_FULL)) { ok = false; break; }
+                float4* a_hi = (float4*)(smem + s * L::STAGE_BYTES);
+                float4* a_lo = (float4*)(smem + s * L::STAGE_BYTES + L::A_BYTES);
+#pragma unroll
+                for (int i = 0; i < A_VEC; i++) {
+                    float4 v = a_hi[t + i * 128];
+                    float4 h, l;
+                    if (WRITE_HI) { h.x = to_tf32_rn(v.x); h.y = to_tf32_rn(v.y); h.z = to_tf32_rn(v.z); h.w = to_tf32_rn(v.w); }
+                    else {   // the tensor core drops the low 13 mantissa bits of the raw value itself
+                        h.x = __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u); h.y = __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u);
+                        h.z = __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u); h.w = __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u);
+                    }
+                    l.x = v.x - h.x; l.y = v.y - h.y; l.z = v.z - h.z; l.w = v.w - h.w;
+                    if (WRITE_HI) a_hi[t + i * 128] = h;
+                    a_lo[t + i * 128] = l;
+                }
+                if (MODE == TCM_WGRAD) {
+                    float4* b_hi = (float4*)(smem + s * L::STAGE_BYTES + 2 * L::A_BYTES);
+                    float4* b_lo = (float4*)(smem + s * L::STAGE_BYTES + 2 * L::A_BYTES + L::B_BYTES);
+#pragma unroll
+                    for (int i = 0; i < B_VEC; i++) {
+                        float4 v = b_hi[t + i * 128];
+                        float4 h, l;
+                        if (WRITE_HI) { h.x = to_tf32_rn(v.x); h.y = to_tf32_rn(v.y); h.z = to_tf32_rn(v.z); h.w = to_tf32_rn(v.w); }
+                        else {
+                            h.x = __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u); h.y = __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u);
+                            h.z = __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u); h.w = __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u);
+                        }
+                        l.x = v.x - h.x; l.y = v.y - h.y; l.z = v.z - h.z; l.w = v.w - h.w;
+                        if (WRITE_HI) b_hi[t + i * 128] = h;
+                        b_lo[t + i * 128] = l;
+                    }
+                }
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&xform_bar[s]);
+            }
         }
     } else {
-        // ---------------- operand transform, then epilogue ----------------
-        const int t = threadIdx.x - 64;      // 0..127
+        // ---------------- drain of the partial sums, then epilogue ----------------
+        // Each chunk of TC_CHUNK k-blocks is accumulated in tensor memory from zero and added here in
+        // float32 round-to-nearest; the tensor core's own accumulate step truncates, and its bias
+        // grows with the number of accumulations, so it is kept to one chunk.
+        const int quad = warp & 3;                       // TMEM lane quadrant this warp may read
         bool ok = true;
-        for (int kb = 0; kb < p.kblocks; kb++) {
-            const int s = kb % STAGES, use = kb / STAGES;
-            ok = mbar_wait(&full_bar[s], use & 1, abort_flag, &g_tc_status, TC_ERR_FULL);
-            if (!ok) break;
-            float4* a_hi = (float4*)(smem + s * L::STAGE_BYTES);
-            float4* a_lo = (float4*)(smem + s * L::STAGE_BYTES + L::A_BYTES);
+        int gc = 0;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            const int ni = tile % nt, rest = tile / nt, mi = rest % mt, z = rest / mt;
+            const int m0 = mi * 128, n0 = ni * BN;
+            float acc[BN];
 #pragma unroll
-            for (int i = 0; i < 8; i++) {
-                float4 v = a_hi[t + i * 128];
-                float4 h, l;
-                h.x = to_tf32_rn(v.x); h.y = to_tf32_rn(v.y); h.z = to_tf32_rn(v.z); h.w = to_tf32_rn(v.w);
-                l.x = v.x - h.x; l.y = v.y - h.y; l.z = v.z - h.z; l.w = v.w - h.w;
-                a_hi[t + i * 128] = h;
-                a_lo[t + i * 128] = l;
+            for (int j = 0; j < BN; j++) acc[j] = 0.f;
+            for (int c = 0; c < nchunks && ok; c++, gc++) {
+                const int b = gc & 1;
+                ok = mbar_wait(&tfull_bar[b], (gc >> 1) & 1, abort_flag, &g_tc_status, TC_ERR_TFULL);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int cc = 0; cc < BN / 32; cc++) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(b * BN + cc * 32), r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; j++) acc[cc * 32 + j] += __uint_as_float(r[j]);
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&tempty_bar[b]);
             }
-            fence_proxy_async();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&xform_bar[s]);
-        }
-        if (ok) ok = mbar_wait(accum_bar, 0, abort_flag, &g_tc_status, TC_ERR_ACCUM);
-        if (ok) {
-            tc_fence_after();
-            const int quad = warp & 3;                       // TMEM lane quadrant this warp may read
             const int m = m0 + quad * 32 + lane;
-            float* orow = p.out + (int64_t)m * p.N;
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; c++) {
-                uint32_t r[32];
-                tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * 32), r);
-                tmem_ld_wait();
-                if (m < p.M) {
+            if (ok && m < p.M) {
+                if (MODE == TCM_FWD) {
+                    const int img = m / (p.P * p.Q);
+                    const int rem = m - img * (p.P * p.Q);
+                    const int pi = rem / p.Q, qi = rem - pi * p.Q;
+                    float* orow = p.out + img * p.o_sn + pi * p.o_sh + qi * p.o_sw;
 #pragma unroll
-                    for (int j = 0; j < 32; j += 4) {
-                        const int n = n0 + c * 32 + j;
-                        if (n >= p.N) break;
-                        float v[4];
+                    for (int j = 0; j < BN; j += 4) {
+                        const int n = n0 + j;
+                        if (n < p.N) {
+                            float v[4];
 #pragma unroll
-                        for (int e = 0; e < 4; e++) {
-                            float a = __uint_as_float(r[j + e]);
-                            const int ne = n + e;
-                            if (p.bias) a += p.bias[ne];
-                            if (p.mean) { float tt = (a - p.mean[ne]) * p.inv_std[ne]; a = tt * p.gamma[ne] + p.beta[ne]; }
-                            if (p.relu) a = fmaxf(a, 0.f);
-                            v[e] = a;
+                            for (int e = 0; e < 4; e++) {
+                                float a = acc[j + e];
+                                const int ne = n + e;
+                                if (p.bias) a += p.bias[ne];
+                                if (p.mean) { float tt = (a - p.mean[ne]) * p.inv_std[ne]; a = tt * p.gamma[ne] + p.beta[ne]; }
+                                if (p.relu) a = fmaxf(a, 0.f);
+                                v[e] = a;
+                            }
+                            *reinterpret_cast<float4*>(orow + n) = make_float4(v[0], v[1], v[2], v[3]);
                         }
-                        *reinterpret_cast<float4*>(orow + n) = make_float4(v[0], v[1], v[2], v[3]);
+                    }
+                } else {
+                    float* orow = p.out + ((int64_t)z * p.M + m) * p.N;
+#pragma unroll
+                    for (int j = 0; j < BN; j += 4) {
+                        const int n = n0 + j;
+                        if (n < p.N) *reinterpret_cast<float4*>(orow + n) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
                     }
                 }
             }
@@ -326,7 +464,23 @@ conv_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, BN); }
+    if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 2 * BN); }
+}
+
+// Second stage of the weight gradient: fixed-order sum of the per-split partial tiles, written in the
+// caller's filter layout.
+struct WgradReduceParams { int M, N, C, S, splits; int64_t sk, sc, sr, ss; };
+
+__global__ void tc_wgrad_reduce_kernel(WgradReduceParams p, const float* __restrict__ partial, float* __restrict__ dw)
+{
+    int64_t total = (int64_t)p.M * p.N;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        int m = (int)(i / p.N), n = (int)(i - (int64_t)m * p.N);
+        float v = 0.f;
+        for (int z = 0; z < p.splits; z++) v += partial[(int64_t)z * total + i];
+        int tap = m / p.C, c = m - tap * p.C, r = tap / p.S, s = tap - r * p.S;
+        dw[n * p.sk + c * p.sc + r * p.sr + s * p.ss] = v;
+    }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -354,142 +508,270 @@ static bool load_driver_entry_points()
     return true;
 }
 
+// The tensor core reads only the upper 19 bits of a float32 operand, so by default the raw tile
+// serves as "hi" (hi = a with the low 13 mantissa bits cleared) and only "lo" is written.  Setting
+// B2C_TC_WRITE_HI=1 switches to a round-to-nearest split with both halves written back.
+static bool write_hi_mode()
+{
+    static int mode = -1;
+    if (mode < 0) { const char* e = getenv("B2C_TC_WRITE_HI"); mode = (e && e[0] == '1') ? 1 : 0; }
+    return mode == 1;
+}
+
 // 2-D row-major float matrix [rows][cols], box = 32 columns x box_rows rows, 128B swizzle.
-static bool make_map_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows)
+static bool make_map_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                        CUtensorMapSwizzle swz = CU_TENSOR_MAP_SWIZZLE_128B)
 {
     cuuint64_t dims[2] = {cols, rows};
     cuuint64_t strides[1] = {cols * sizeof(float)};
     cuuint32_t box[2] = {32, box_rows};
     cuuint32_t estr[2] = {1, 1};
     return g_encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// NHWC activation tensor (n, h, w, c) seen through an im2col window: `pixels` consecutive output
-// pixels x 32 channels per load. Corners are given in (w, h) order.
-static bool make_map_im2col(CUtensorMap* map, const void* base, int n, int h, int w, int c, int pad_h, int pad_w,
-                            int kh, int kw, int dil_h, int dil_w, int str_h, int str_w, uint32_t pixels)
+// NHWC activation tensor (n, h, w, c) seen through an im2col window of `pixels` consecutive window
+// positions x 32 channels per load. The window's first position sits at (low_h, low_w); it has
+// `cnt_h` x `cnt_w` positions per image before the traversal stride is applied. Corners in (w, h) order.
+static bool make_map_im2col(CUtensorMap* map, const void* base, int n, int h, int w, int c, int low_h, int low_w,
+                            int cnt_h, int cnt_w, int str_h, int str_w, uint32_t pixels,
+                            CUtensorMapSwizzle swz = CU_TENSOR_MAP_SWIZZLE_128B)
 {
     cuuint64_t dims[4] = {(cuuint64_t)c, (cuuint64_t)w, (cuuint64_t)h, (cuuint64_t)n};
     cuuint64_t strides[3] = {(cuuint64_t)c * 4, (cuuint64_t)w * c * 4, (cuuint64_t)h * w * c * 4};
-    int lower[2] = {-pad_w, -pad_h};
-    int upper[2] = {pad_w - (kw - 1) * dil_w, pad_h - (kh - 1) * dil_h};
+    int lower[2] = {low_w, low_h};
+    int upper[2] = {cnt_w - w + low_w, cnt_h - h + low_h};
+    for (int i = 0; i < 2; i++) if (lower[i] < -128 || lower[i] > 127 || upper[i] < -128 || upper[i] > 127) return false;
     cuuint32_t estr[4] = {1, (cuuint32_t)str_w, (cuuint32_t)str_h, 1};
     return g_encode_im2col(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void*>(base), dims, strides, lower, upper,
-                           32, pixels, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                           32, pixels, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
                            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-static bool corners_ok(int v) { return v >= -128 && v <= 127; }
+// One parity class of a strided data gradient along one axis: output positions o = str*i + a.
+// The filter taps that reach them are r = a + pad - str*delta (dilation 1); delta runs over
+// [dmin, dmin + cnt).  cnt == 0: no tap reaches the class (its outputs are zero).
+struct AxisClass { int cnt, dmin, r0, out_cnt; };
+static AxisClass axis_class(int a, int str, int pad, int k, int in_len)
+{
+    AxisClass c{0, 0, 0, 0};
+    c.out_cnt = in_len > a ? (in_len - a + str - 1) / str : 0;
+    int dmin = 1 << 30, dmax = -(1 << 30);
+    for (int r = 0; r < k; r++) {
+        int t = a + pad - r;
+        if (t % str != 0) continue;                    // C remainder: exact for negative t too
+        int d = t / str;
+        if (d < dmin) dmin = d;
+        if (d > dmax) dmax = d;
+    }
+    if (dmax < dmin) return c;
+    c.cnt = dmax - dmin + 1; c.dmin = dmin; c.r0 = a + pad - str * dmin;
+    return c;
+}
 
 bool tc_supported(const Geo& g, int pass)
 {
     if (g.dtype != B2C_F32 || g.layout != B2C_LAYOUT_NHWC || g.engine == B2C_ENGINE_FMA) return false;
     if (g.vstr > 8 || g.hstr > 8) return false;
-    if ((g.kh - 1) * g.vdil > 255 || (g.kw - 1) * g.hdil > 255) return false;
-    if (pass == B2C_PASS_FPROP) {
-        if (g.ci % 32 || g.co % 4) return false;
-        return corners_ok(-g.vpad) && corners_ok(-g.hpad) && corners_ok(g.vpad - (g.kh - 1) * g.vdil) &&
-               corners_ok(g.hpad - (g.kw - 1) * g.hdil);
-    }
+    if ((g.kh - 1) * g.vdil > 255 || (g.kw - 1) * g.hdil > 255 || g.vpad > 127 || g.hpad > 127) return false;
+    if (pass == B2C_PASS_FPROP) return g.ci % 32 == 0 && g.co % 4 == 0;
     if (pass == B2C_PASS_DGRAD) {
-        if (g.vstr != 1 || g.hstr != 1) return false;
         if (g.co % 32 || g.ci % 4) return false;
-        int pv = (g.kh - 1) * g.vdil - g.vpad, ph = (g.kw - 1) * g.hdil - g.hpad;
-        if (pv < 0 || ph < 0) return false;
-        return corners_ok(-pv) && corners_ok(-ph) && corners_ok(pv - (g.kh - 1) * g.vdil) && corners_ok(ph - (g.kw - 1) * g.hdil);
+        if (g.vstr == 1 && g.hstr == 1) return (g.kh - 1) * g.vdil - g.vpad >= -127 && (g.kw - 1) * g.hdil - g.hpad >= -127;
+        return g.vdil == 1 && g.hdil == 1;             // strided: parity-class decomposition, dilation 1 only
     }
-    return false;
+    return g.ci % 32 == 0 && g.co % 32 == 0;
 }
 
-static size_t fwd_filter_bytes(const Geo& g, int pass)
+static size_t filter_split_bytes(const Geo& g, int pass)
 {
     int rows = pass == B2C_PASS_FPROP ? g.co : g.ci;
     int C = pass == B2C_PASS_FPROP ? g.ci : g.co;
     return align_up((size_t)rows * g.kh * g.kw * C * sizeof(float), 1024);
 }
 
+struct WgradPlan { int splits, kblocks, bn; };
+static WgradPlan wgrad_plan(const Geo& g)
+{
+    WgradPlan pl;
+    pl.bn = g.co <= 64 ? 64 : 128;
+    int64_t tiles = ((g.K + 127) / 128) * ((g.co + pl.bn - 1) / pl.bn);
+    int64_t want = (296 + tiles - 1) / tiles;
+    int64_t max_by_pix = g.M / 512;
+    if (max_by_pix < 1) max_by_pix = 1;
+    int64_t s = want < max_by_pix ? want : max_by_pix;
+    if (s > 512) s = 512;
+    int64_t blocks = (g.M + 31) / 32;
+    pl.kblocks = (int)((blocks + s - 1) / s);
+    pl.splits = (int)((blocks + pl.kblocks - 1) / pl.kblocks);
+    return pl;
+}
+
 size_t tc_workspace_bytes(const Geo& g, int pass)
 {
-    if (pass == B2C_PASS_FPROP || pass == B2C_PASS_DGRAD) return 2 * fwd_filter_bytes(g, pass) + 1024;
-    return 0;
+    if (pass == B2C_PASS_FPROP || pass == B2C_PASS_DGRAD) return 2 * filter_split_bytes(g, pass) + 1024;
+    WgradPlan pl = wgrad_plan(g);
+    return align_up((size_t)pl.splits * g.K * g.co * sizeof(float), 1024) + 1024 +
+           channel_sum_workspace_bytes(g.n, g.co, g.ho * g.wo);
 }
 
-template <int BN, int STAGES>
-static int launch_fwd(const CUtensorMap& ma, const CUtensorMap& mbh, const CUtensorMap& mbl, const FwdParams& p, cudaStream_t st)
+template <int MODE, int BN, int STAGES, bool WH>
+static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb0, const CUtensorMap& mb1, const TcParams& p, int splits, cudaStream_t st)
 {
-    using L = FwdSmem<BN, STAGES>;
+    using L = TcSmem<BN, STAGES>;
     static bool attr_set = false;
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(conv_tc_fwd_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
-        if (e != cudaSuccess) { set_cuda_error(e, "cudaFuncSetAttribute(conv_tc_fwd_kernel)"); return B2C_ERR_CUDA; }
+        cudaError_t e = cudaFuncSetAttribute(conv_tc_kernel<MODE, BN, STAGES, WH>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+        if (e != cudaSuccess) { set_cuda_error(e, "cudaFuncSetAttribute(conv_tc_kernel)"); return B2C_ERR_CUDA; }
         attr_set = true;
     }
-    dim3 grid((p.M + 127) / 128, (p.N + BN - 1) / BN);
-    if (grid.y > 65535) return B2C_ERR_TOO_LARGE;
-    conv_tc_fwd_kernel<BN, STAGES><<<grid, 192, L::TOTAL, st>>>(ma, mbh, mbl, p);
-    return check_launch("conv_tc_fwd_kernel");
+    static int sm_count = 0;
+    if (!sm_count) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
+    }
+    int64_t tiles = (int64_t)((p.M + 127) / 128) * ((p.N + BN - 1) / BN) * splits;
+    if (tiles > 0x7fffffffLL) return B2C_ERR_TOO_LARGE;
+    TcParams q = p;
+    q.splits = splits;
+    const int grid = (int)(tiles < sm_count ? tiles : sm_count);     // one persistent CTA per SM
+    conv_tc_kernel<MODE, BN, STAGES, WH><<<grid, 320, L::TOTAL, st>>>(ma, mb0, mb1, q);
+    return check_launch("conv_tc_kernel");
 }
 
-// Shared by fprop and dgrad: `act` is the gathered NHWC tensor (n, ah, aw, C), the filter source is
-// described by PrepParams, the output is [n*P*Q][N].
-static int run_fwd(int n, int ah, int aw, int C, int P, int Q, int N, int kh, int kw, int pad_h, int pad_w, int str_h,
-                   int str_w, int dil_h, int dil_w, const void* act, const void* w, const PrepParams& pp,
-                   const void* bias, const b2c_bn_params* bn, int relu, void* out, void* ws, size_t ws_bytes,
-                   cudaStream_t st)
+template <int MODE>
+static int dispatch_tc(int bn, const CUtensorMap& ma, const CUtensorMap& mb0, const CUtensorMap& mb1, const TcParams& p, int splits, cudaStream_t st)
+{
+    const bool wh = write_hi_mode();
+    if (bn == 64) return wh ? launch_tc<MODE, 64, 4, true>(ma, mb0, mb1, p, splits, st) : launch_tc<MODE, 64, 4, false>(ma, mb0, mb1, p, splits, st);
+    return wh ? launch_tc<MODE, 128, 3, true>(ma, mb0, mb1, p, splits, st) : launch_tc<MODE, 128, 3, false>(ma, mb0, mb1, p, splits, st);
+}
+
+// fprop-shaped launch: `act` (n, ah, aw, C) gathered through a window whose first position is
+// (low_h, low_w), with cnt_h x cnt_w positions per image and traversal stride (str_h, str_w); virtual
+// filter kh x kw (dilation dil); output rows (n, i, j) over P x Q written at out + n*o_sn + i*o_sh + j*o_sw.
+struct FwdLaunch {
+    int n, ah, aw, C, P, Q, N, kh, kw, low_h, low_w, cnt_h, cnt_w, str_h, str_w, dil_h, dil_w;
+    int64_t o_sn, o_sh, o_sw;
+};
+
+static int run_fwd(const FwdLaunch& f, const void* act, const void* w, const PrepParams& pp, const void* bias,
+                   const b2c_bn_params* bn, int relu, float* out, void* ws, size_t ws_bytes, cudaStream_t st)
 {
     if (!load_driver_entry_points()) return B2C_ERR_UNSUPPORTED;
-    const int64_t K = (int64_t)kh * kw * C;
-    const size_t fbytes = align_up((size_t)N * K * sizeof(float), 1024);
+    const int64_t K = (int64_t)f.kh * f.kw * f.C;
+    const size_t fbytes = align_up((size_t)f.N * K * sizeof(float), 1024);
     uintptr_t base = align_up((uintptr_t)ws, 1024);
     if (!ws || base + 2 * fbytes > (uintptr_t)ws + ws_bytes) return B2C_ERR_WORKSPACE_TOO_SMALL;
     if (((uintptr_t)act & 15) || ((uintptr_t)out & 15)) return B2C_ERR_MISALIGNED;
     float* w_hi = (float*)base;
     float* w_lo = (float*)(base + fbytes);
     {
-        int64_t total = (int64_t)N * K;
+        int64_t total = (int64_t)f.N * K;
         int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
         tc_prep_filter_kernel<<<blocks, 256, 0, st>>>(pp, (const float*)w, w_hi, w_lo);
         int rc = check_launch("tc_prep_filter_kernel");
         if (rc) return rc;
     }
-    const int BN = N <= 64 ? 64 : 128;
+    const int BN = f.N <= 64 ? 64 : 128;
     CUtensorMap ma, mbh, mbl;
-    if (!make_map_im2col(&ma, act, n, ah, aw, C, pad_h, pad_w, kh, kw, dil_h, dil_w, str_h, str_w, 128)) return B2C_ERR_UNSUPPORTED;
-    if (!make_map_2d(&mbh, w_hi, N, K, BN) || !make_map_2d(&mbl, w_lo, N, K, BN)) return B2C_ERR_UNSUPPORTED;
-    FwdParams p{};
-    p.M = n * P * Q; p.N = N; p.P = P; p.Q = Q;
-    p.cblocks = C / 32; p.kblocks = kh * kw * p.cblocks; p.S = kw;
-    p.str_h = str_h; p.str_w = str_w; p.pad_h = pad_h; p.pad_w = pad_w; p.dil_h = dil_h; p.dil_w = dil_w;
+    if (!make_map_im2col(&ma, act, f.n, f.ah, f.aw, f.C, f.low_h, f.low_w, f.cnt_h, f.cnt_w, f.str_h, f.str_w, 128)) return B2C_ERR_UNSUPPORTED;
+    if (!make_map_2d(&mbh, w_hi, f.N, K, BN) || !make_map_2d(&mbl, w_lo, f.N, K, BN)) return B2C_ERR_UNSUPPORTED;
+    TcParams p{};
+    p.M = f.n * f.P * f.Q; p.N = f.N; p.P = f.P; p.Q = f.Q;
+    p.C = f.C; p.cblocks = f.C / 32; p.kblocks = f.kh * f.kw * p.cblocks; p.S = f.kw;
+    p.str_h = f.str_h; p.str_w = f.str_w; p.dil_h = f.dil_h; p.dil_w = f.dil_w; p.low_h = f.low_h; p.low_w = f.low_w;
     p.bias = (const float*)bias;
     if (bn) { p.mean = (const float*)bn->mean; p.inv_std = (const float*)bn->inv_std; p.gamma = (const float*)bn->gamma; p.beta = (const float*)bn->beta; }
     p.relu = relu;
-    p.out = (float*)out;
-    if (BN == 64) return launch_fwd<64, 4>(ma, mbh, mbl, p, st);
-    return launch_fwd<128, 3>(ma, mbh, mbl, p, st);
+    p.out = out; p.o_sn = f.o_sn; p.o_sh = f.o_sh; p.o_sw = f.o_sw;
+    return dispatch_tc<TCM_FWD>(BN, ma, mbh, mbl, p, 1, st);
 }
 
 int tc_fprop(const Geo& g, const void* x, const void* w, const void* bias, const b2c_bn_params* bn, int relu,
              void* y, void* ws, size_t ws_bytes, cudaStream_t st)
 {
     WStride wsd = w_stride(g.w_layout, g.ci, g.co, g.kh, g.kw);
-    PrepParams pp{g.co, g.ci, g.kh, g.kw, wsd.sk, wsd.sc, wsd.sr, wsd.ss, 0};
-    return run_fwd(g.n, g.h, g.w, g.ci, g.ho, g.wo, g.co, g.kh, g.kw, g.vpad, g.hpad, g.vstr, g.hstr, g.vdil, g.hdil,
-                   x, w, pp, bias, bn, relu, y, ws, ws_bytes, st);
+    PrepParams pp{g.co, g.ci, g.kh, g.kw, wsd.sk, wsd.sc, wsd.sr, wsd.ss, 0, 1, 0, 1};
+    FwdLaunch f{g.n, g.h, g.w, g.ci, g.ho, g.wo, g.co, g.kh, g.kw, -g.vpad, -g.hpad,
+                g.h + 2 * g.vpad - (g.kh - 1) * g.vdil, g.w + 2 * g.hpad - (g.kw - 1) * g.hdil,
+                g.vstr, g.hstr, g.vdil, g.hdil, (int64_t)g.ho * g.wo * g.co, (int64_t)g.wo * g.co, (int64_t)g.co};
+    return run_fwd(f, x, w, pp, bias, bn, relu, (float*)y, ws, ws_bytes, st);
 }
 
 int tc_dgrad(const Geo& g, const void* dy, const void* w, void* dx, void* ws, size_t ws_bytes, cudaStream_t st)
 {
     WStride wsd = w_stride(g.w_layout, g.ci, g.co, g.kh, g.kw);
-    // rows = ci, gathered channels = co, taps flipped
-    PrepParams pp{g.ci, g.co, g.kh, g.kw, wsd.sc, wsd.sk, wsd.sr, wsd.ss, 1};
-    const int pv = (g.kh - 1) * g.vdil - g.vpad, ph = (g.kw - 1) * g.hdil - g.hpad;
-    return run_fwd(g.n, g.ho, g.wo, g.co, g.h, g.w, g.ci, g.kh, g.kw, pv, ph, 1, 1, g.vdil, g.hdil,
-                   dy, w, pp, nullptr, nullptr, 0, dx, ws, ws_bytes, st);
+    if (g.vstr == 1 && g.hstr == 1) {
+        // dx = convolution of dy with the flipped, transposed filter and padding (k-1)*dil - pad
+        const int pv = (g.kh - 1) * g.vdil - g.vpad, ph = (g.kw - 1) * g.hdil - g.hpad;
+        PrepParams pp{g.ci, g.co, g.kh, g.kw, wsd.sc, wsd.sk, wsd.sr, wsd.ss, g.kh - 1, -1, g.kw - 1, -1};
+        FwdLaunch f{g.n, g.ho, g.wo, g.co, g.h, g.w, g.ci, g.kh, g.kw, -pv, -ph, g.h, g.w, 1, 1, g.vdil, g.hdil,
+                    (int64_t)g.h * g.w * g.ci, (int64_t)g.w * g.ci, (int64_t)g.ci};
+        return run_fwd(f, dy, w, pp, nullptr, nullptr, 0, (float*)dx, ws, ws_bytes, st);
+    }
+    // Strided: the input positions split into str_h*str_w parity classes; each class is a dense
+    // stride-1 convolution of dy with the sub-filter of the taps that reach it, written to its
+    // strided positions of dx. Classes no tap reaches stay zero.
+    bool any_empty = false;
+    for (int a = 0; a < g.vstr; a++)
+        for (int b = 0; b < g.hstr; b++) {
+            AxisClass ca = axis_class(a, g.vstr, g.vpad, g.kh, g.h), cb = axis_class(b, g.hstr, g.hpad, g.kw, g.w);
+            if ((ca.cnt == 0 || cb.cnt == 0) && ca.out_cnt > 0 && cb.out_cnt > 0) any_empty = true;
+        }
+    if (any_empty) {
+        cudaError_t e = cudaMemsetAsync(dx, 0, (size_t)g.n * g.h * g.w * g.ci * sizeof(float), st);
+        if (e != cudaSuccess) { set_cuda_error(e, "cudaMemsetAsync(dx)"); return B2C_ERR_CUDA; }
+    }
+    for (int a = 0; a < g.vstr; a++)
+        for (int b = 0; b < g.hstr; b++) {
+            AxisClass ca = axis_class(a, g.vstr, g.vpad, g.kh, g.h), cb = axis_class(b, g.hstr, g.hpad, g.kw, g.w);
+            if (ca.out_cnt == 0 || cb.out_cnt == 0 || ca.cnt == 0 || cb.cnt == 0) continue;
+            PrepParams pp{g.ci, g.co, ca.cnt, cb.cnt, wsd.sc, wsd.sk, wsd.sr, wsd.ss, ca.r0, -g.vstr, cb.r0, -g.hstr};
+            FwdLaunch f{g.n, g.ho, g.wo, g.co, ca.out_cnt, cb.out_cnt, g.ci, ca.cnt, cb.cnt, ca.dmin, cb.dmin,
+                        ca.out_cnt, cb.out_cnt, 1, 1, 1, 1,
+                        (int64_t)g.h * g.w * g.ci, (int64_t)g.vstr * g.w * g.ci, (int64_t)g.hstr * g.ci};
+            float* out = (float*)dx + ((int64_t)a * g.w + b) * g.ci;
+            int rc = run_fwd(f, dy, w, pp, nullptr, nullptr, 0, out, ws, ws_bytes, st);
+            if (rc) return rc;
+        }
+    return B2C_OK;
 }
 
-int tc_wgrad(const Geo&, const void*, const void*, void*, void*, void*, size_t, cudaStream_t) { return B2C_ERR_UNSUPPORTED; }
+int tc_wgrad(const Geo& g, const void* x, const void* dy, void* dw, void* db, void* ws, size_t ws_bytes, cudaStream_t st)
+{
+    if (!load_driver_entry_points()) return B2C_ERR_UNSUPPORTED;
+    WgradPlan pl = wgrad_plan(g);
+    const size_t pbytes = align_up((size_t)pl.splits * g.K * g.co * sizeof(float), 1024);
+    uintptr_t base = align_up((uintptr_t)ws, 1024);
+    const size_t cs = channel_sum_workspace_bytes(g.n, g.co, g.ho * g.wo);
+    if (!ws || base + pbytes + (db ? cs : 0) > (uintptr_t)ws + ws_bytes) return B2C_ERR_WORKSPACE_TOO_SMALL;
+    if (((uintptr_t)x & 15) || ((uintptr_t)dy & 15)) return B2C_ERR_MISALIGNED;
+    float* partial = (float*)base;
+    CUtensorMap ma, mb;
+    if (!make_map_im2col(&ma, x, g.n, g.h, g.w, g.ci, -g.vpad, -g.hpad, g.h + 2 * g.vpad - (g.kh - 1) * g.vdil,
+                         g.w + 2 * g.hpad - (g.kw - 1) * g.hdil, g.vstr, g.hstr, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B))
+        return B2C_ERR_UNSUPPORTED;
+    if (!make_map_2d(&mb, dy, (uint64_t)g.M, (uint64_t)g.co, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) return B2C_ERR_UNSUPPORTED;
+    TcParams p{};
+    p.M = (int)g.K; p.N = g.co; p.P = g.ho; p.Q = g.wo; p.kblocks = pl.kblocks;
+    p.C = g.ci; p.cblocks = g.ci / 32; p.S = g.kw;
+    p.str_h = g.vstr; p.str_w = g.hstr; p.dil_h = g.vdil; p.dil_w = g.hdil; p.low_h = -g.vpad; p.low_w = -g.hpad;
+    p.Mpix = (int)g.M;
+    p.out = partial;
+    int rc = dispatch_tc<TCM_WGRAD>(pl.bn, ma, mb, mb, p, pl.splits, st);
+    if (rc) return rc;
+    WStride wsd = w_stride(g.w_layout, g.ci, g.co, g.kh, g.kw);
+    WgradReduceParams rp{(int)g.K, g.co, g.ci, g.kw, pl.splits, wsd.sk, wsd.sc, wsd.sr, wsd.ss};
+    int64_t total = g.K * g.co;
+    int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+    tc_wgrad_reduce_kernel<<<blocks, 256, 0, st>>>(rp, partial, (float*)dw);
+    rc = check_launch("tc_wgrad_reduce_kernel");
+    if (rc || !db) return rc;
+    return channel_sum(B2C_F32, B2C_LAYOUT_NHWC, g.n, g.co, g.ho * g.wo, dy, db, (void*)(base + pbytes), cs, st);
+}
 
 int tc_read_status(int* out)
 {

@@ -67,6 +67,7 @@ class Model:
         self._train_fused = False
         self._eval_layers = None
         self.fast_update = True
+        self.fuse_add_relu = True
         if model_name:
             from . import nets
             getattr(nets, f"create_{model_name}")(self)
@@ -100,12 +101,17 @@ class Model:
     def _fuse_training(self):
         """BatchNormalization followed by Relu: the normalisation kernel applies the ReLU and the
         backward kernel applies its mask, so the activation tensor makes one HBM round trip fewer."""
-        if self._train_fused or not self.enable_fused_bn_relu:
+        if self._train_fused:
             return
         def walk(seq):
             for a, b in zip(seq, seq[1:]):
-                if isinstance(a, BatchNormalization) and isinstance(b, Relu):
+                if self.enable_fused_bn_relu and isinstance(a, BatchNormalization) and isinstance(b, Relu):
                     a.fuse_relu, b.absorbed = True, True
+                # an addition block followed by a ReLU: the last residual sum writes max(sum, 0)
+                # straight into the ReLU's output (same arithmetic, one pass over memory fewer)
+                if self.fuse_add_relu and a.is_block_layer and len(a.paths) > 1 and isinstance(b, Relu) \
+                        and type(a).__name__ == "AdditionBlockGPU":
+                    a.relu_after, b.fed_by_block = b, True
             for layer in seq:
                 for p in layer.paths:
                     walk(p)

@@ -11,14 +11,14 @@ pytestmark = pytest.mark.gpu
 
 
 def rel_l2(got, ref):
-    """Relative L2 error with an absolute floor: gradients that are analytically zero (the bias of a
-    convolution that feeds a batch normalisation) are rounding noise on both sides."""
+    """Relative L2 error, zero when the absolute error is below a floor: gradients that are
+    analytically zero (the bias of a convolution that feeds a batch normalisation) are rounding
+    noise on both sides."""
     got, ref = np.asarray(got, np.float64), np.asarray(ref, np.float64)
-    floor = (1e-13 if got.dtype == np.float64 and np.asarray(ref).dtype == np.float64 else 1e-13)
     err = np.linalg.norm(got - ref)
-    scale = np.linalg.norm(ref)
-    noise = np.sqrt(ref.size) * (1e-6 if _NOISE["f32"] else 1e-14)
-    return err / max(scale, noise * 1e2)
+    if err <= (1e-5 if _NOISE["f32"] else 1e-12) * np.sqrt(ref.size):
+        return 0.0
+    return err / max(np.linalg.norm(ref), 1e-300)
 
 
 _NOISE = {"f32": False}
@@ -61,8 +61,9 @@ def test_train_step_matches_cpu_twin(layout, dtype, fused):
         assert abs(loss_obj.loss() - loss_ref) <= tol * max(1.0, abs(loss_ref))
         # activations of the top-level layers (absorbed ReLUs return their input's buffer)
         for i, layer in enumerate(model.layers[1:]):
-            if layer.canonical_name in ("Flatten",) or getattr(layer, "absorbed", False):
-                continue
+            if layer.canonical_name in ("Flatten",) or getattr(layer, "absorbed", False) \
+                    or getattr(layer, "relu_after", None) is not None:
+                continue        # views, and blocks whose sum lands directly in the following ReLU
             got = layer.y.ary.get().reshape(net.acts[i + 1].shape)
             assert rel_l2(got, net.acts[i + 1]) <= tol, f"step {step} y of {layer}"
         for layer, node in walk_pairs(model.layers[1:], net.nodes):
