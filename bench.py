@@ -313,6 +313,70 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_single_conv(args):
+    """One Conv2D pass through the C ABI on device-resident synthetic tensors: the small, fixed case
+    used for kernel profiles. Buffers rotate over more than the L2 size between launches."""
+    import ctypes
+    import torch
+    from pydtnn_b200 import _lib
+    n, h, w, ci, co, k, stride, pad = [int(v) for v in args.conv.split(",")]
+    L = _lib.lib()
+    torch.cuda.set_device(0)
+    ho, wo = (h + 2 * pad - k) // stride + 1, (w + 2 * pad - k) // stride + 1
+    desc = _lib.ConvDesc(_lib.LAYOUT_NHWC, _lib.F32, _lib.W_KRSC, _lib.ENGINE_AUTO, n, h, w, ci, co, k, k, pad, pad,
+                         stride, stride, 1, 1)
+    pidx = {"fprop": 0, "dgrad": 1, "wgrad": 2}[args.conv_pass]
+    engine = L.b2c_conv_engine_for(ctypes.byref(desc), pidx)
+    nb = max(L.b2c_conv_workspace_bytes(ctypes.byref(desc), p) for p in range(3))
+    ws = torch.empty(max(int(nb), 256), dtype=torch.uint8, device="cuda")
+    bytes_x, bytes_y = n * h * w * ci * 4, n * ho * wo * co * 4
+    nbuf = max(2, int(256e6 // max(bytes_x + bytes_y, 1)) + 1)          # rotate through > 2x L2
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    xs = [torch.randn((n, h, w, ci), device="cuda", generator=gen) for _ in range(nbuf)]
+    ys = [torch.randn((n, ho, wo, co), device="cuda", generator=gen) for _ in range(nbuf)]
+    wt = torch.randn((co, k, k, ci), device="cuda", generator=gen) * (2.0 / (ci * k * k)) ** 0.5
+    dw = torch.empty_like(wt)
+    st = torch.cuda.current_stream().cuda_stream
+
+    def call(i):
+        x, y = xs[i % nbuf], ys[i % nbuf]
+        if pidx == 0:
+            rc = L.b2c_conv_fprop(ctypes.byref(desc), x.data_ptr(), wt.data_ptr(), None, None, 0, y.data_ptr(),
+                                  ws.data_ptr(), ws.numel(), st)
+        elif pidx == 1:
+            rc = L.b2c_conv_dgrad(ctypes.byref(desc), y.data_ptr(), wt.data_ptr(), x.data_ptr(), ws.data_ptr(),
+                                  ws.numel(), st)
+        else:
+            rc = L.b2c_conv_wgrad(ctypes.byref(desc), x.data_ptr(), y.data_ptr(), dw.data_ptr(), None, ws.data_ptr(),
+                                  ws.numel(), st)
+        _lib.check(rc)
+
+    for i in range(max(args.warmup, 3)):
+        call(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        call(i)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    flops = 2.0 * n * ho * wo * co * ci * k * k
+    min_bytes = 4.0 * (n * h * w * ci + k * k * ci * co + n * ho * wo * co)
+    peaks = measured_peaks()
+    peak = peaks["bf16"] / 6.0
+    tflops = flops / (ms * 1e-3) / 1e12
+    print(json.dumps({
+        "metric": "conv_pass_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"conv2d_{args.conv_pass}", "shape": args.conv, "tensor_format": "NHWC",
+                   "engine": "tensor" if engine == _lib.ENGINE_TENSOR else "fma", "l2": f"{nbuf} rotating buffer sets"},
+        "roofline": {"bound": "tensor", "achieved": tflops, "peak": peak, "unit": "TFLOP/s", "frac": tflops / peak,
+                     "peak_basis": f"{peaks['source']} bf16 burst {peaks['bf16']:.1f} / 2 / 3 (kernel timed alone)",
+                     "min_bytes": min_bytes, "hbm_gbs_at_min_bytes": min_bytes / (ms * 1e-3) / 1e9,
+                     "arithmetic_intensity": flops / min_bytes}}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -321,7 +385,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--layers", action="store_true", help="add per-layer convolution timings to the JSON line")
+    ap.add_argument("--conv", default=None, help="n,h,w,ci,co,k,stride,pad: time one Conv2D pass instead of the model")
+    ap.add_argument("--conv-pass", default="fprop", choices=["fprop", "dgrad", "wgrad"])
     args = ap.parse_args()
+    if args.conv:
+        run_single_conv(args)
+        return
     if args.impl == "reference":
         run_reference_arm(args)
     else:
