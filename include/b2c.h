@@ -135,6 +135,23 @@ int b2c_bn_train_forward(int dtype, int layout, int n, int c, int hw, const void
                          const void *beta, void *running_mean, void *running_var, double momentum,
                          double eps, int fuse_relu, void *y, void *save_mean, void *save_inv_std,
                          void *scratch, size_t scratch_bytes, void *stream);
+/* b2c_bn_train_forward for callers that must not allocate and have no scratch buffer to lend: hosts
+ * that give all device memory to their own pool at start-up and then forbid allocation (a late
+ * cudaMalloc stalls the device and may fail once the pool owns the card).  Same arguments and results
+ * as b2c_bn_train_forward without the scratch pair; the partial sums live in a fixed 2 MiB array inside
+ * the library (one copy per GPU that loads it, kept until the process ends).
+ *  - Limit: c <= 2048 channels, otherwise B2C_ERR_TOO_LARGE ("size exceeds a fixed capacity").
+ *  - The first call on each device looks up the array's device address (cudaGetSymbolAddress); make
+ *    that first call during set-up, before any stream capture begins.
+ *  - No cudaMalloc / cudaFree / allocating library call is made, on the first call or later.
+ *  - All calls on a device share the one array: calls that can overlap on the GPU (different streams)
+ *    race on it; keep them on one stream or order them with events.  The array keeps the previous
+ *    call's partial sums, which is harmless: each call overwrites every entry it later reads.
+ * This entry point has no counterpart in the reference. */
+int b2c_bn_train_forward_static(int dtype, int layout, int n, int c, int hw, const void *x, const void *gamma,
+                                const void *beta, void *running_mean, void *running_var, double momentum,
+                                double eps, int fuse_relu, void *y, void *save_mean, void *save_inv_std,
+                                void *stream);
 /* dgamma, dbeta, dx (dx may be NULL). If fuse_relu, dy is first masked by y > 0.
  * Replaces cudnnBatchNormalizationBackward, batch_normalization_gpu.py:146-156. scratch: as for the forward pass. */
 int b2c_bn_train_backward(int dtype, int layout, int n, int c, int hw, const void *x, const void *dy,

@@ -4,6 +4,7 @@
 // two-stage with double partial sums so the result does not depend on launch order.
 #include "b2c_common.cuh"
 #include <float.h>
+#include <mutex>
 
 namespace b2c {
 
@@ -726,6 +727,65 @@ extern "C" int b2c_bn_train_forward(int dtype, int layout, int n, int c, int hw,
                                          (float*)running_var, momentum, eps, fuse_relu, (float*)y, (float*)save_mean, (float*)save_inv_std, (double*)scratch, scratch_bytes, st);
     return bn_train_forward_t<double>(layout, n, c, hw, (const double*)x, (const double*)gamma, (const double*)beta, (double*)running_mean,
                                       (double*)running_var, momentum, eps, fuse_relu, (double*)y, (double*)save_mean, (double*)save_inv_std, (double*)scratch, scratch_bytes, st);
+}
+
+
+// ---- batch-norm forward without caller-supplied scratch ----------------------------------------
+// Some hosts of this library hand all device memory to their own pool when they start and from then
+// on refuse to allocate: a late cudaMalloc synchronises the whole device, can fragment or simply fail
+// once the pool owns the card, and a training or serving loop with a latency budget cannot absorb
+// that.  Such a caller may have no spare buffer to lend as reduction scratch either.  For them the
+// per-channel partial sums of this one kernel live in a fixed array inside the library image
+// (2 MiB per GPU that loads the library, held until the process exits).
+#define B2C_STATIC_SCRATCH_DOUBLES (64 * 2 * 2048)      // 64 row chunks x (sum, sum of squares) x 2048 channels
+#define B2C_STATIC_MAX_CHANNELS 2048
+static __device__ __align__(256) double g_bn_static_scratch[B2C_STATIC_SCRATCH_DOUBLES];
+
+// In host code the array's name is only a handle for the runtime, not a device address; the address
+// the kernels need is looked up once per device (with that device current) and kept.
+static double* g_bn_static_ptr[64] = {nullptr};
+static std::mutex g_bn_static_mutex;
+
+static int bn_static_scratch(double** out)
+{
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) { b2c::set_cuda_error(e, "cudaGetDevice"); return B2C_ERR_CUDA; }
+    if (dev < 0 || dev >= 64) return B2C_ERR_TOO_LARGE;
+    std::lock_guard<std::mutex> lock(g_bn_static_mutex);
+    if (!g_bn_static_ptr[dev]) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_bn_static_scratch);
+        if (e != cudaSuccess || !p) { b2c::set_cuda_error(e, "cudaGetSymbolAddress(g_bn_static_scratch)"); return B2C_ERR_CUDA; }
+        g_bn_static_ptr[dev] = (double*)p;
+    }
+    *out = g_bn_static_ptr[dev];
+    return B2C_OK;
+}
+
+extern "C" int b2c_bn_train_forward_static(int dtype, int layout, int n, int c, int hw, const void* x, const void* gamma,
+                                           const void* beta, void* running_mean, void* running_var, double momentum,
+                                           double eps, int fuse_relu, void* y, void* save_mean, void* save_inv_std,
+                                           void* stream)
+{
+    CHECK_DTYPE(dtype); CHECK_LAYOUT(layout);
+    if (!x || !gamma || !beta || !running_mean || !running_var || !y || !save_mean || !save_inv_std) return B2C_ERR_NULL_POINTER;
+    if (n <= 0 || c <= 0 || hw <= 0) return B2C_ERR_BAD_GEOMETRY;
+    if (c > B2C_STATIC_MAX_CHANNELS) return B2C_ERR_TOO_LARGE;     // the fixed array holds 64 chunks of at most 2048 channels
+    double* scratch = nullptr;
+    int rc = bn_static_scratch(&scratch);
+    if (rc) return rc;
+    const size_t scratch_bytes = sizeof(double) * B2C_STATIC_SCRATCH_DOUBLES;
+    cudaStream_t st = (cudaStream_t)stream;
+    // Every partial the second stage reads is written by the first stage of the same call, so the
+    // previous call's contents never need clearing.
+    if (dtype == B2C_F32)
+        return bn_train_forward_t<float>(layout, n, c, hw, (const float*)x, (const float*)gamma, (const float*)beta, (float*)running_mean,
+                                         (float*)running_var, momentum, eps, fuse_relu, (float*)y, (float*)save_mean, (float*)save_inv_std,
+                                         scratch, scratch_bytes, st);
+    return bn_train_forward_t<double>(layout, n, c, hw, (const double*)x, (const double*)gamma, (const double*)beta, (double*)running_mean,
+                                      (double*)running_var, momentum, eps, fuse_relu, (double*)y, (double*)save_mean, (double*)save_inv_std,
+                                      scratch, scratch_bytes, st);
 }
 
 extern "C" int b2c_bn_train_backward(int dtype, int layout, int n, int c, int hw, const void* x, const void* dy,
