@@ -86,6 +86,18 @@ __device__ __forceinline__ void tma_load_im2col_4d(void* dst, const CUtensorMap*
                  : "memory");
 }
 
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(smem_u32(src)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void* src, int x, int y, int z) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 ::"l"(map), "r"(smem_u32(src)), "r"(x), "r"(y), "r"(z) : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Wait until at most N of this thread's committed store groups still read their shared-memory source.
+template <int N> __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+
 __device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols) : "memory");
 }
@@ -149,6 +161,16 @@ __device__ int g_tc_status = 0;
 
 enum { TC_ERR_FULL = 1, TC_ERR_XFORM = 2, TC_ERR_EMPTY = 3, TC_ERR_TFULL = 4, TC_ERR_TEMPTY = 5 };
 
+#ifdef B2C_TC_PROFILE
+// Development build only: per-role cycle counters of CTA 0 (slots documented at the call sites).
+__device__ long long g_tc_prof[32];
+#define TC_PROF_T0() long long _pt = clock64()
+#define TC_PROF_ADD(slot) do { long long _n = clock64(); if (blockIdx.x == 0) g_tc_prof[slot] += _n - _pt; _pt = _n; } while (0)
+#else
+#define TC_PROF_T0() do { } while (0)
+#define TC_PROF_ADD(slot) do { } while (0)
+#endif
+
 // ---------------------------------------------------------------------------------------------
 // Filter preparation: hi/lo split into the K-major GEMM layout the fprop/dgrad kernel reads by TMA
 // ---------------------------------------------------------------------------------------------
@@ -197,6 +219,7 @@ struct TcParams {
     int relu;
     float* out;                // FWD: row m=(n,i,j) at out + n*o_sn + i*o_sh + j*o_sw.  WGRAD: partial [split][M][N]
     int64_t o_sn, o_sh, o_sw;
+    int tma_store;             // output rows are dense [M][N] (or [split][M][N]): store tiles through the output tensor map
 };
 
 template <int BN, int STAGES>
@@ -205,13 +228,15 @@ struct TcSmem {
     static constexpr int B_BYTES = BN * 128;
     static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
     static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-    static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;   // + barriers/flags + alignment slack
+    static constexpr int EPI_OFFSET = BAR_OFFSET + 1024;          // barriers and flags live in the first 256 bytes
+    static constexpr int EPI_BYTES = 4 * 2 * 4096;                // per drain warp: two 32 x 32 float staging slabs
+    static constexpr int TOTAL = EPI_OFFSET + EPI_BYTES + 1024;   // + alignment slack
 };
 
 template <int MODE, int BN, int STAGES, bool WRITE_HI>
 __global__ void __launch_bounds__(320, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b0,
-               const __grid_constant__ CUtensorMap tmap_b1, TcParams p)
+               const __grid_constant__ CUtensorMap tmap_b1, const __grid_constant__ CUtensorMap tmap_out, TcParams p)
 {
     // Persistent: each CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ... (column tile fastest, so
     // CTAs running at the same time share activation rows in L2).  The smem pipeline and the two TMEM
@@ -248,60 +273,77 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
-        if (lane == 0) {
-            int it = 0;
-            bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const int ni = tile % nt, rest = tile / nt, mi = rest % mt, z = rest / mt;
-                const int m0 = mi * 128, n0 = ni * BN;
-                int img = 0, base_w = 0, base_h = 0;
-                if (MODE == TCM_FWD) {
-                    img = m0 / (p.P * p.Q);
-                    const int rem = m0 - img * (p.P * p.Q);
-                    const int p0 = rem / p.Q, q0 = rem - p0 * p.Q;
-                    base_w = q0 * p.str_w + p.low_w; base_h = p0 * p.str_h + p.low_h;
+        // The whole warp takes part: lane 0 waits for the stage and arms the barrier, then lanes 0..(boxes-1)
+        // each issue one TMA box, so the issue cost of the (up to eight) boxes of a k-block is paid in parallel.
+        int it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            const int ni = tile % nt, rest = tile / nt, mi = rest % mt, z = rest / mt;
+            const int m0 = mi * 128, n0 = ni * BN;
+            int img = 0, base_w = 0, base_h = 0;
+            if (MODE == TCM_FWD) {
+                img = m0 / (p.P * p.Q);
+                const int rem = m0 - img * (p.P * p.Q);
+                const int p0 = rem / p.Q, q0 = rem - p0 * p.Q;
+                base_w = q0 * p.str_w + p.low_w; base_h = p0 * p.str_h + p.low_h;
+            }
+            // WGRAD: this lane's box is fixed for the tile: lanes 0-3 an x box (32 rows of (tap, ci)),
+            // lanes 4.. a dy box (32 output channels)
+            bool lane_has_box = false;
+            int box_c0 = 0, box_offw = 0, box_offh = 0, box_co = 0, boxes = 0;
+            if (MODE == TCM_WGRAD) {
+                if (lane < 4) {
+                    const int mrow = m0 + 32 * lane;
+                    if (mrow < p.M) {
+                        const int tap = mrow / p.C;
+                        box_c0 = mrow - tap * p.C;
+                        const int r = tap / p.S, sx = tap - r * p.S;
+                        box_offw = sx * p.dil_w; box_offh = r * p.dil_h;
+                        lane_has_box = true;
+                    }
+                } else if (lane < 4 + BN / 32) {
+                    box_co = n0 + 32 * (lane - 4);
+                    lane_has_box = box_co < p.N;
                 }
-                const int pix_begin = (MODE == TCM_WGRAD) ? z * p.kblocks * 32 : 0;
-                for (int kb = 0; kb < p.kblocks; kb++, it++) {
-                    const int s = it % STAGES, use = it / STAGES;
-                    if (use > 0 && !mbar_wait(&empty_bar[s], (use - 1) & 1, abort_flag, &g_tc_status, TC_ERR_EMPTY)) { ok = false; break; }
-                    uint8_t* st = smem + s * L::STAGE_BYTES;
-                    if (MODE == TCM_FWD) {
+                boxes = __popc(__ballot_sync(0xffffffffu, lane_has_box));
+            }
+            const int pix_begin = (MODE == TCM_WGRAD) ? z * p.kblocks * 32 : 0;
+            for (int kb = 0; kb < p.kblocks; kb++, it++) {
+                const int s = it % STAGES, use = it / STAGES;
+                int good = 1;
+                if (lane == 0) {
+                    TC_PROF_T0();
+                    if (use > 0 && !mbar_wait(&empty_bar[s], (use - 1) & 1, abort_flag, &g_tc_status, TC_ERR_EMPTY)) good = 0;
+                    TC_PROF_ADD(0);    // producer: waiting for a free stage
+                    if (good) mbar_expect_tx(&full_bar[s], MODE == TCM_FWD ? (uint32_t)(L::A_BYTES + 2 * L::B_BYTES) : (uint32_t)(boxes * 4096));
+                }
+                good = __shfl_sync(0xffffffffu, good, 0);
+                if (!good) { ok = false; break; }
+                uint8_t* st = smem + s * L::STAGE_BYTES;
+                if (MODE == TCM_FWD) {
+                    if (lane == 0) {
                         const int tap = kb / p.cblocks, cb = kb - tap * p.cblocks;
                         const int r = tap / p.S, sx = tap - r * p.S;
-                        mbar_expect_tx(&full_bar[s], L::A_BYTES + 2 * L::B_BYTES);
                         tma_load_im2col_4d(st, &tmap_a, &full_bar[s], cb * 32, base_w, base_h, img,
                                            (uint16_t)(sx * p.dil_w), (uint16_t)(r * p.dil_h));
+                    } else if (lane == 1) {
                         tma_load_2d(st + 2 * L::A_BYTES, &tmap_b0, &full_bar[s], kb * 32, n0);
+                    } else if (lane == 2) {
                         tma_load_2d(st + 2 * L::A_BYTES + L::B_BYTES, &tmap_b1, &full_bar[s], kb * 32, n0);
-                    } else {
-                        const int pix0 = pix_begin + kb * 32;
+                    }
+                } else if (lane_has_box) {
+                    const int pix0 = pix_begin + kb * 32;
+                    if (lane < 4) {
                         const int im = pix0 / (p.P * p.Q);
                         const int rem = pix0 - im * (p.P * p.Q);
                         const int p0 = rem / p.Q, q0 = rem - p0 * p.Q;
-                        const int bw = q0 * p.str_w + p.low_w, bh = p0 * p.str_h + p.low_h;
-                        int boxes = 0;
-#pragma unroll
-                        for (int j = 0; j < 4; j++) if (m0 + 32 * j < p.M) boxes++;
-#pragma unroll
-                        for (int j = 0; j < BN / 32; j++) if (n0 + 32 * j < p.N) boxes++;
-                        mbar_expect_tx(&full_bar[s], boxes * 4096);
-#pragma unroll
-                        for (int j = 0; j < 4; j++) {
-                            const int mrow = m0 + 32 * j;
-                            if (mrow < p.M) {
-                                const int tap = mrow / p.C, c0 = mrow - tap * p.C;
-                                const int r = tap / p.S, sx = tap - r * p.S;
-                                tma_load_im2col_4d(st + j * 4096, &tmap_a, &full_bar[s], c0, bw, bh, im,
-                                                   (uint16_t)(sx * p.dil_w), (uint16_t)(r * p.dil_h));
-                            }
-                        }
-#pragma unroll
-                        for (int j = 0; j < BN / 32; j++)
-                            if (n0 + 32 * j < p.N)
-                                tma_load_2d(st + 2 * L::A_BYTES + j * 4096, &tmap_b0, &full_bar[s], n0 + 32 * j, pix0);
+                        tma_load_im2col_4d(st + lane * 4096, &tmap_a, &full_bar[s], box_c0, q0 * p.str_w + p.low_w,
+                                           p0 * p.str_h + p.low_h, im, (uint16_t)box_offw, (uint16_t)box_offh);
+                    } else {
+                        tma_load_2d(st + 2 * L::A_BYTES + (lane - 4) * 4096, &tmap_b0, &full_bar[s], box_co, pix0);
                     }
                 }
+                __syncwarp();
             }
         }
     } else if (warp == 1) {
@@ -322,12 +364,16 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     const int s = it % STAGES, use = it / STAGES;
                     const int b = gc & 1;
                     const bool chunk_start = (kb % TC_CHUNK) == 0;
+                    TC_PROF_T0();
                     if (chunk_start && gc >= 2) {
                         ok = mbar_wait(&tempty_bar[b], ((gc >> 1) - 1) & 1, abort_flag, &g_tc_status, TC_ERR_TEMPTY);
                         if (!ok) break;
                     }
-                    ok = mbar_wait(&full_bar[s], use & 1, abort_flag, &g_tc_status, TC_ERR_FULL) &&
-                         mbar_wait(&xform_bar[s], use & 1, abort_flag, &g_tc_status, TC_ERR_XFORM);
+                    TC_PROF_ADD(1);    // MMA: waiting for a drained TMEM buffer
+                    ok = mbar_wait(&full_bar[s], use & 1, abort_flag, &g_tc_status, TC_ERR_FULL);
+                    TC_PROF_ADD(2);    // MMA: waiting for TMA data
+                    ok = ok && mbar_wait(&xform_bar[s], use & 1, abort_flag, &g_tc_status, TC_ERR_XFORM);
+                    TC_PROF_ADD(3);    // MMA: waiting for the transform
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
@@ -345,6 +391,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     }
                     umma_commit(&empty_bar[s]);
                     if ((kb % TC_CHUNK) == TC_CHUNK - 1 || kb == p.kblocks - 1) { umma_commit(&tfull_bar[b]); gc++; }
+                    TC_PROF_ADD(4);    // MMA: issue
                 }
             }
         }
@@ -358,7 +405,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
             for (int kb = 0; kb < p.kblocks; kb++, it++) {
                 const int s = it % STAGES, use = it / STAGES;
+                TC_PROF_T0();
                 if (!mbar_wait(&full_bar[s], use & 1, abort_flag, &g_tc_status, TC_ERR_FULL)) { ok = false; break; }
+                if (t == 0) TC_PROF_ADD(5);    // transform: waiting for TMA data
                 float4* a_hi = (float4*)(smem + s * L::STAGE_BYTES);
                 float4* a_lo = (float4*)(smem + s * L::STAGE_BYTES + L::A_BYTES);
 #pragma unroll
@@ -394,6 +443,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 fence_proxy_async();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&xform_bar[s]);
+                if (t == 0) TC_PROF_ADD(6);    // transform: work
             }
         }
     } else {
@@ -403,7 +453,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         // grows with the number of accumulations, so it is kept to one chunk.
         const int quad = warp & 3;                       // TMEM lane quadrant this warp may read
         bool ok = true;
-        int gc = 0;
+        int gc = 0, ecount = 0;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
             const int ni = tile % nt, rest = tile / nt, mi = rest % mt, z = rest / mt;
             const int m0 = mi * 128, n0 = ni * BN;
@@ -412,7 +462,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             for (int j = 0; j < BN; j++) acc[j] = 0.f;
             for (int c = 0; c < nchunks && ok; c++, gc++) {
                 const int b = gc & 1;
+                TC_PROF_T0();
                 ok = mbar_wait(&tfull_bar[b], (gc >> 1) & 1, abort_flag, &g_tc_status, TC_ERR_TFULL);
+                if (threadIdx.x == 192) TC_PROF_ADD(7);    // drain: waiting for a finished chunk
                 if (!ok) break;
                 tc_fence_after();
 #pragma unroll
@@ -426,41 +478,102 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&tempty_bar[b]);
+                if (threadIdx.x == 192) TC_PROF_ADD(8);    // drain: TMEM load + add
             }
+            TC_PROF_T0();
+            // Epilogue. A thread owns one output row, but a warp writing 32 different rows per store would
+            // touch 32 cache lines with 16 bytes each; the values go through a per-warp smem tile instead so
+            // that every store instruction writes whole 128-byte row segments (8 lanes per row, 4 rows).
             const int m = m0 + quad * 32 + lane;
-            if (ok && m < p.M) {
+            int64_t my_off = -1;
+            if (m < p.M) {
                 if (MODE == TCM_FWD) {
                     const int img = m / (p.P * p.Q);
                     const int rem = m - img * (p.P * p.Q);
                     const int pi = rem / p.Q, qi = rem - pi * p.Q;
-                    float* orow = p.out + img * p.o_sn + pi * p.o_sh + qi * p.o_sw;
+                    my_off = img * p.o_sn + pi * p.o_sh + qi * p.o_sw;
+                } else {
+                    my_off = ((int64_t)z * p.M + m) * p.N;
+                }
+            }
+            if (ok && p.tma_store) {
+                // Dense output: each warp stages its 32 rows x 32 columns in a 128B-swizzled slab (conflict-free
+                // float4 writes) and hands it to the TMA store engine, which writes whole rows asynchronously and
+                // clips rows >= M and columns >= N; two slabs per warp alternate so the warp never waits on HBM.
+                uint8_t* ebuf = smem + L::EPI_OFFSET + (warp - 6) * 8192;
 #pragma unroll
-                    for (int j = 0; j < BN; j += 4) {
-                        const int n = n0 + j;
-                        if (n < p.N) {
+                for (int cc = 0; cc < BN / 32; cc++) {
+                    if (n0 + cc * 32 < p.N && m0 + quad * 32 < p.M) {       // slabs wholly outside the output are skipped
+                        uint8_t* buf = ebuf + (ecount & 1) * 4096;
+                        if (lane == 0) tma_store_wait_read<1>();     // the store that last read this slab is done
+                        __syncwarp();
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
                             float v[4];
 #pragma unroll
                             for (int e = 0; e < 4; e++) {
-                                float a = acc[j + e];
-                                const int ne = n + e;
-                                if (p.bias) a += p.bias[ne];
-                                if (p.mean) { float tt = (a - p.mean[ne]) * p.inv_std[ne]; a = tt * p.gamma[ne] + p.beta[ne]; }
-                                if (p.relu) a = fmaxf(a, 0.f);
+                                float a = acc[cc * 32 + j + e];
+                                if (MODE == TCM_FWD) {
+                                    const int ne = n0 + cc * 32 + j + e;
+                                    if (ne < p.N) {
+                                        if (p.bias) a += p.bias[ne];
+                                        if (p.mean) { float tt = (a - p.mean[ne]) * p.inv_std[ne]; a = tt * p.gamma[ne] + p.beta[ne]; }
+                                        if (p.relu) a = fmaxf(a, 0.f);
+                                    }
+                                }
                                 v[e] = a;
                             }
-                            *reinterpret_cast<float4*>(orow + n) = make_float4(v[0], v[1], v[2], v[3]);
+                            *reinterpret_cast<float4*>(buf + lane * 128 + ((((j >> 2) ^ (lane & 7))) << 4)) = make_float4(v[0], v[1], v[2], v[3]);
                         }
+                        fence_proxy_async();
+                        __syncwarp();
+                        if (lane == 0) {
+                            if (MODE == TCM_FWD) tma_store_2d(&tmap_out, buf, n0 + cc * 32, m0 + quad * 32);
+                            else tma_store_3d(&tmap_out, buf, n0 + cc * 32, m0 + quad * 32, z);
+                            tma_store_commit();
+                        }
+                        ecount++;
                     }
-                } else {
-                    float* orow = p.out + ((int64_t)z * p.M + m) * p.N;
+                }
+            } else if (ok) {
+                float* stage = (float*)(smem + L::EPI_OFFSET) + (warp - 6) * (8192 / 4);
 #pragma unroll
-                    for (int j = 0; j < BN; j += 4) {
-                        const int n = n0 + j;
-                        if (n < p.N) *reinterpret_cast<float4*>(orow + n) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+                for (int cc = 0; cc < BN / 32; cc++) {
+                    if (n0 + cc * 32 < p.N) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            float v[4];
+#pragma unroll
+                            for (int e = 0; e < 4; e++) {
+                                float a = acc[cc * 32 + j + e];
+                                if (MODE == TCM_FWD) {
+                                    const int ne = n0 + cc * 32 + j + e;
+                                    if (ne < p.N) {
+                                        if (p.bias) a += p.bias[ne];
+                                        if (p.mean) { float tt = (a - p.mean[ne]) * p.inv_std[ne]; a = tt * p.gamma[ne] + p.beta[ne]; }
+                                        if (p.relu) a = fmaxf(a, 0.f);
+                                    }
+                                }
+                                v[e] = a;
+                            }
+                            *reinterpret_cast<float4*>(stage + lane * 36 + j) = make_float4(v[0], v[1], v[2], v[3]);
+                        }
+                        __syncwarp();
+#pragma unroll
+                        for (int i = 0; i < 8; i++) {
+                            const int r = i * 4 + (lane >> 3), c4 = (lane & 7) * 4;
+                            const int64_t off_r = __shfl_sync(0xffffffffu, my_off, r);
+                            const int n = n0 + cc * 32 + c4;
+                            if (off_r >= 0 && n < p.N)
+                                *reinterpret_cast<float4*>(p.out + off_r + n) = *reinterpret_cast<const float4*>(stage + r * 36 + c4);
+                        }
+                        __syncwarp();
                     }
                 }
             }
+            if (threadIdx.x == 192) TC_PROF_ADD(9);        // drain: epilogue
         }
+        if (p.tma_store && lane == 0) tma_store_wait_read<0>();   // the slabs stay allocated until the last store has read them
     }
     tc_fence_before();
     __syncthreads();
@@ -617,7 +730,7 @@ size_t tc_workspace_bytes(const Geo& g, int pass)
 }
 
 template <int MODE, int BN, int STAGES, bool WH>
-static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb0, const CUtensorMap& mb1, const TcParams& p, int splits, cudaStream_t st)
+static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb0, const CUtensorMap& mb1, const CUtensorMap& mo, const TcParams& p, int splits, cudaStream_t st)
 {
     using L = TcSmem<BN, STAGES>;
     static bool attr_set = false;
@@ -637,16 +750,39 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb0, const CUtens
     TcParams q = p;
     q.splits = splits;
     const int grid = (int)(tiles < sm_count ? tiles : sm_count);     // one persistent CTA per SM
-    conv_tc_kernel<MODE, BN, STAGES, WH><<<grid, 320, L::TOTAL, st>>>(ma, mb0, mb1, q);
+    conv_tc_kernel<MODE, BN, STAGES, WH><<<grid, 320, L::TOTAL, st>>>(ma, mb0, mb1, mo, q);
     return check_launch("conv_tc_kernel");
 }
 
 template <int MODE>
-static int dispatch_tc(int bn, const CUtensorMap& ma, const CUtensorMap& mb0, const CUtensorMap& mb1, const TcParams& p, int splits, cudaStream_t st)
+static int dispatch_tc(int bn, const CUtensorMap& ma, const CUtensorMap& mb0, const CUtensorMap& mb1, const CUtensorMap& mo, const TcParams& p, int splits, cudaStream_t st)
 {
     const bool wh = write_hi_mode();
-    if (bn == 64) return wh ? launch_tc<MODE, 64, 4, true>(ma, mb0, mb1, p, splits, st) : launch_tc<MODE, 64, 4, false>(ma, mb0, mb1, p, splits, st);
-    return wh ? launch_tc<MODE, 128, 3, true>(ma, mb0, mb1, p, splits, st) : launch_tc<MODE, 128, 3, false>(ma, mb0, mb1, p, splits, st);
+    if (bn == 64) return wh ? launch_tc<MODE, 64, 4, true>(ma, mb0, mb1, mo, p, splits, st) : launch_tc<MODE, 64, 4, false>(ma, mb0, mb1, mo, p, splits, st);
+    return wh ? launch_tc<MODE, 128, 3, true>(ma, mb0, mb1, mo, p, splits, st) : launch_tc<MODE, 128, 3, false>(ma, mb0, mb1, mo, p, splits, st);
+}
+
+// Output seen as [planes][rows][cols] floats, box = 32 cols x 32 rows (x 1 plane), 128B swizzle.
+// planes == 0 asks for the 2-D form (the forward kernel stores with 2-D coordinates, the weight-gradient
+// kernel always with 3-D ones, so the rank must match the kernel, not the data).
+static bool make_map_out(CUtensorMap* map, const void* base, uint64_t planes, uint64_t rows, uint64_t cols)
+{
+    if (planes == 0) {
+        cuuint64_t dims[2] = {cols, rows};
+        cuuint64_t strides[1] = {cols * sizeof(float)};
+        cuuint32_t box[2] = {32, 32};
+        cuuint32_t estr[2] = {1, 1};
+        return g_encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    }
+    cuuint64_t dims[3] = {cols, rows, planes};
+    cuuint64_t strides[2] = {cols * sizeof(float), rows * cols * sizeof(float)};
+    cuuint32_t box[3] = {32, 32, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    return g_encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 // fprop-shaped launch: `act` (n, ah, aw, C) gathered through a window whose first position is
@@ -687,7 +823,12 @@ static int run_fwd(const FwdLaunch& f, const void* act, const void* w, const Pre
     if (bn) { p.mean = (const float*)bn->mean; p.inv_std = (const float*)bn->inv_std; p.gamma = (const float*)bn->gamma; p.beta = (const float*)bn->beta; }
     p.relu = relu;
     p.out = out; p.o_sn = f.o_sn; p.o_sh = f.o_sh; p.o_sw = f.o_sw;
-    return dispatch_tc<TCM_FWD>(BN, ma, mbh, mbl, p, 1, st);
+    // dense rows (plain fprop / stride-1 dgrad): rows are N floats apart in (n, i, j) order
+    const bool dense = f.o_sw == f.N && f.o_sh == (int64_t)f.Q * f.N && f.o_sn == (int64_t)f.P * f.Q * f.N;
+    CUtensorMap mo = mbh;
+    p.tma_store = 0;
+    if (dense && make_map_out(&mo, out, 0, (uint64_t)p.M, (uint64_t)f.N)) p.tma_store = 1;
+    return dispatch_tc<TCM_FWD>(BN, ma, mbh, mbl, mo, p, 1, st);
 }
 
 int tc_fprop(const Geo& g, const void* x, const void* w, const void* bias, const b2c_bn_params* bn, int relu,
@@ -761,7 +902,9 @@ int tc_wgrad(const Geo& g, const void* x, const void* dy, void* dw, void* db, vo
     p.str_h = g.vstr; p.str_w = g.hstr; p.dil_h = g.vdil; p.dil_w = g.hdil; p.low_h = -g.vpad; p.low_w = -g.hpad;
     p.Mpix = (int)g.M;
     p.out = partial;
-    int rc = dispatch_tc<TCM_WGRAD>(pl.bn, ma, mb, mb, p, pl.splits, st);
+    CUtensorMap mo = mb;
+    p.tma_store = make_map_out(&mo, partial, (uint64_t)pl.splits, (uint64_t)g.K, (uint64_t)g.co) ? 1 : 0;
+    int rc = dispatch_tc<TCM_WGRAD>(pl.bn, ma, mb, mb, mo, p, pl.splits, st);
     if (rc) return rc;
     WStride wsd = w_stride(g.w_layout, g.ci, g.co, g.kh, g.kw);
     WgradReduceParams rp{(int)g.K, g.co, g.ci, g.kw, pl.splits, wsd.sk, wsd.sc, wsd.sr, wsd.ss};
@@ -772,6 +915,16 @@ int tc_wgrad(const Geo& g, const void* x, const void* dy, void* dw, void* db, vo
     if (rc || !db) return rc;
     return channel_sum(B2C_F32, B2C_LAYOUT_NHWC, g.n, g.co, g.ho * g.wo, dy, db, (void*)(base + pbytes), cs, st);
 }
+
+#ifdef B2C_TC_PROFILE
+extern "C" int b2c_debug_prof(long long* out, int reset)
+{
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out, g_tc_prof, sizeof(long long) * 32);
+    if (reset) { long long z[32] = {0}; cudaMemcpyToSymbol(g_tc_prof, z, sizeof(z)); }
+    return 0;
+}
+#endif
 
 int tc_read_status(int* out)
 {
