@@ -246,6 +246,10 @@ def run_ours(args):
         key = (f"{layer.hi}x{layer.wi}x{layer.ci}->{layer.co} k{layer.kh} s{layer.vstride}", name)
         q = per_layer.setdefault(key, [0.0, 0.0, 0])
         q[0] += ms; q[1] += layer.flops_per_pass; q[2] += 1
+    conv_min_bytes = 0.0
+    for name, layer, e0, e1 in prof:
+        conv_min_bytes += 4.0 * model.batch_size * (layer.hi * layer.wi * layer.ci + layer.ho * layer.wo * layer.co) + \
+            4.0 * layer.kh * layer.kw * layer.ci * layer.co
     conv_ms = sum(v[0] for v in per_pass.values())
     conv_flops = sum(v[1] for v in per_pass.values())
     conv_launches = sum(v[2] for v in per_pass.values())
@@ -259,14 +263,19 @@ def run_ours(args):
             for p, pname in enumerate(("fprop", "dgrad", "wgrad")):
                 e = L.b2c_conv_engine_for(ctypes.byref(layer.desc), p)
                 engines[pname + ("_tensor" if e == _lib.ENGINE_TENSOR else "_fma")] = engines.get(pname + ("_tensor" if e == _lib.ENGINE_TENSOR else "_fma"), 0) + 1
-    traffic = None
+    traffic, traffic_note = None, None
     tpath = os.path.join(ROOT, "profiles", "traffic.json")
-    if os.path.exists(tpath):
+    if os.path.exists(tpath) and conv_launches:
         with open(tpath) as f:
-            traffic = json.load(f).get("conv_dram_bytes_per_launch")
+            tj = json.load(f)
+        # DRAM bytes per launch: the measured/algorithmic ratio of the ncu capture (a smaller case of the
+        # same kernel) applied to the average algorithmic bytes of the launches timed here
+        traffic = tj["measured_over_algorithmic"] * conv_min_bytes / conv_launches
+        traffic_note = tj["case"]
     roofline = {
         "bound": "tensor", "achieved": achieved, "peak": peak_3xtf32, "unit": "TFLOP/s",
-        "frac": achieved / peak_3xtf32, "traffic": traffic,
+        "frac": achieved / peak_3xtf32, "traffic": traffic, "traffic_basis": traffic_note,
+        "algorithmic_bytes_per_launch_avg": conv_min_bytes / max(conv_launches, 1),
         "kernel": "Conv2D fprop+dgrad+wgrad launches of the step (implicit GEMM)",
         "peak_basis": f"{peaks['source']} bf16 sustained {peaks['bf16_sustained']:.1f} TFLOP/s / 2 (tf32) / 3 (3xTF32)",
         "launches_timed": conv_launches, "avg_launch_ms": conv_ms / max(conv_launches, 1),

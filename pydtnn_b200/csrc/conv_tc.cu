@@ -197,6 +197,59 @@ __global__ void tc_prep_filter_kernel(PrepParams p, const float* __restrict__ w,
 }
 
 // ---------------------------------------------------------------------------------------------
+// Few-channel layers (the Ci=3 network stem): the TMA gather needs 32-channel, 16-byte aligned rows, so
+// for these the im2row matrix is written out once, [pixel][(r*S+s)*C + c] zero-padded to a multiple of
+// 32 columns, and the layer then runs as a 1x1 convolution over it.  With C*R*S small the matrix costs
+// less HBM traffic than the output tensor it produces.
+// ---------------------------------------------------------------------------------------------
+struct LowerParams { int n, h, w, c, ho, wo, kh, kw, vpad, hpad, vstr, hstr, vdil, hdil, K, Kp; };
+
+__global__ void tc_lower_kernel(LowerParams p, const float* __restrict__ x, float4* __restrict__ rows)
+{
+    // column k -> (row offset, column offset, channel), decoded once per block
+    __shared__ int tab_dh[1024], tab_dw[1024], tab_c[1024];
+    for (int k = threadIdx.x; k < p.Kp; k += blockDim.x) {
+        if (k < p.K) {
+            const int c = k % p.c, rs = k / p.c, r = rs / p.kw, sx = rs - r * p.kw;
+            tab_dh[k] = r * p.vdil; tab_dw[k] = sx * p.hdil; tab_c[k] = c;
+        } else { tab_dh[k] = 1 << 28; tab_dw[k] = 0; tab_c[k] = 0; }     // padding column: always out of range
+    }
+    __syncthreads();
+    const int kq = p.Kp / 4;
+    const int64_t total = (int64_t)p.n * p.ho * p.wo * kq;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int q4 = (int)(i % kq);
+        int64_t m = i / kq;
+        const int yy = (int)(m % p.wo); m /= p.wo;
+        const int xx = (int)(m % p.ho); const int nn = (int)(m / p.ho);
+        const int h0 = xx * p.vstr - p.vpad, w0 = yy * p.hstr - p.hpad;
+        const float* img = x + (int64_t)nn * p.h * p.w * p.c;
+        float v[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const int k = q4 * 4 + e;
+            const int ih = h0 + tab_dh[k], iw = w0 + tab_dw[k];
+            v[e] = ((unsigned)ih < (unsigned)p.h && (unsigned)iw < (unsigned)p.w) ? img[((int64_t)ih * p.w + iw) * p.c + tab_c[k]] : 0.f;
+        }
+        rows[i] = make_float4(v[0], v[1], v[2], v[3]);
+    }
+}
+
+// hi/lo split of the filter in the lowered column order, zero in the padding columns
+__global__ void tc_prep_filter_lowered_kernel(int rows, int K, int Kp, int C, int S, int64_t s_row, int64_t s_c, int64_t s_r,
+                                              int64_t s_s, const float* __restrict__ w, float* __restrict__ hi, float* __restrict__ lo)
+{
+    const int64_t total = (int64_t)rows * Kp;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int row = (int)(i / Kp), k = (int)(i - (int64_t)row * Kp);
+        float v = 0.f;
+        if (k < K) { const int c = k % C, rs = k / C, r = rs / S, sx = rs - r * S; v = w[row * s_row + c * s_c + r * s_r + sx * s_s]; }
+        const float h = to_tf32_rn(v);
+        hi[i] = h; lo[i] = v - h;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // The kernel (one template, two modes)
 // ---------------------------------------------------------------------------------------------
 enum { TCM_FWD = 0, TCM_WGRAD = 1 };
@@ -582,13 +635,14 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
 // Second stage of the weight gradient: fixed-order sum of the per-split partial tiles, written in the
 // caller's filter layout.
-struct WgradReduceParams { int M, N, C, S, splits; int64_t sk, sc, sr, ss; };
+struct WgradReduceParams { int M, N, C, S, splits; int64_t sk, sc, sr, ss; int Mreal; };
 
 __global__ void tc_wgrad_reduce_kernel(WgradReduceParams p, const float* __restrict__ partial, float* __restrict__ dw)
 {
     int64_t total = (int64_t)p.M * p.N;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         int m = (int)(i / p.N), n = (int)(i - (int64_t)m * p.N);
+        if (m >= p.Mreal) continue;            // zero-padding rows of a lowered few-channel layer
         float v = 0.f;
         for (int z = 0; z < p.splits; z++) v += partial[(int64_t)z * total + i];
         int tap = m / p.C, c = m - tap * p.C, r = tap / p.S, s = tap - r * p.S;
@@ -683,18 +737,27 @@ static AxisClass axis_class(int a, int str, int pad, int k, int in_len)
     return c;
 }
 
+// Few-channel layers run through the written-out im2row matrix (see tc_lower_kernel).
+static int lowered_kp(const Geo& g) { return (int)((g.K + 31) / 32 * 32); }
+static bool lowered_ok(const Geo& g)
+{
+    if (g.ci % 32 == 0 || g.ci > 16) return false;
+    if (g.K > 1024) return false;
+    return (int64_t)g.M * lowered_kp(g) * 4 <= (int64_t)3 << 30;
+}
+
 bool tc_supported(const Geo& g, int pass)
 {
     if (g.dtype != B2C_F32 || g.layout != B2C_LAYOUT_NHWC || g.engine == B2C_ENGINE_FMA) return false;
     if (g.vstr > 8 || g.hstr > 8) return false;
     if ((g.kh - 1) * g.vdil > 255 || (g.kw - 1) * g.hdil > 255 || g.vpad > 127 || g.hpad > 127) return false;
-    if (pass == B2C_PASS_FPROP) return g.ci % 32 == 0 && g.co % 4 == 0;
+    if (pass == B2C_PASS_FPROP) return (g.ci % 32 == 0 || lowered_ok(g)) && g.co % 4 == 0;
     if (pass == B2C_PASS_DGRAD) {
         if (g.co % 32 || g.ci % 4) return false;
         if (g.vstr == 1 && g.hstr == 1) return (g.kh - 1) * g.vdil - g.vpad >= -127 && (g.kw - 1) * g.hdil - g.hpad >= -127;
         return g.vdil == 1 && g.hdil == 1;             // strided: parity-class decomposition, dilation 1 only
     }
-    return g.ci % 32 == 0 && g.co % 32 == 0;
+    return (g.ci % 32 == 0 || lowered_ok(g)) && g.co % 32 == 0;
 }
 
 static size_t filter_split_bytes(const Geo& g, int pass)
@@ -709,7 +772,8 @@ static WgradPlan wgrad_plan(const Geo& g)
 {
     WgradPlan pl;
     pl.bn = g.co <= 64 ? 64 : 128;
-    int64_t tiles = ((g.K + 127) / 128) * ((g.co + pl.bn - 1) / pl.bn);
+    const int64_t Krows = g.ci % 32 == 0 ? g.K : lowered_kp(g);
+    int64_t tiles = ((Krows + 127) / 128) * ((g.co + pl.bn - 1) / pl.bn);
     int64_t want = (296 + tiles - 1) / tiles;
     int64_t max_by_pix = g.M / 512;
     if (max_by_pix < 1) max_by_pix = 1;
@@ -723,9 +787,13 @@ static WgradPlan wgrad_plan(const Geo& g)
 
 size_t tc_workspace_bytes(const Geo& g, int pass)
 {
+    const bool low = g.ci % 32 != 0;
+    const size_t lowered = low ? align_up((size_t)g.M * lowered_kp(g) * sizeof(float), 1024) : 0;
+    if (pass == B2C_PASS_FPROP && low) return lowered + 2 * align_up((size_t)g.co * lowered_kp(g) * sizeof(float), 1024) + 2048;
     if (pass == B2C_PASS_FPROP || pass == B2C_PASS_DGRAD) return 2 * filter_split_bytes(g, pass) + 1024;
     WgradPlan pl = wgrad_plan(g);
-    return align_up((size_t)pl.splits * g.K * g.co * sizeof(float), 1024) + 1024 +
+    const size_t Krows = low ? (size_t)lowered_kp(g) : (size_t)g.K;
+    return lowered + align_up((size_t)pl.splits * Krows * g.co * sizeof(float), 1024) + 2048 +
            channel_sum_workspace_bytes(g.n, g.co, g.ho * g.wo);
 }
 
@@ -794,7 +862,8 @@ struct FwdLaunch {
 };
 
 static int run_fwd(const FwdLaunch& f, const void* act, const void* w, const PrepParams& pp, const void* bias,
-                   const b2c_bn_params* bn, int relu, float* out, void* ws, size_t ws_bytes, cudaStream_t st)
+                   const b2c_bn_params* bn, int relu, float* out, void* ws, size_t ws_bytes, cudaStream_t st,
+                   bool filters_ready = false)
 {
     if (!load_driver_entry_points()) return B2C_ERR_UNSUPPORTED;
     const int64_t K = (int64_t)f.kh * f.kw * f.C;
@@ -804,7 +873,7 @@ static int run_fwd(const FwdLaunch& f, const void* act, const void* w, const Pre
     if (((uintptr_t)act & 15) || ((uintptr_t)out & 15)) return B2C_ERR_MISALIGNED;
     float* w_hi = (float*)base;
     float* w_lo = (float*)(base + fbytes);
-    {
+    if (!filters_ready) {
         int64_t total = (int64_t)f.N * K;
         int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
         tc_prep_filter_kernel<<<blocks, 256, 0, st>>>(pp, (const float*)w, w_hi, w_lo);
@@ -831,10 +900,45 @@ static int run_fwd(const FwdLaunch& f, const void* act, const void* w, const Pre
     return dispatch_tc<TCM_FWD>(BN, ma, mbh, mbl, mo, p, 1, st);
 }
 
+static LowerParams lower_params(const Geo& g)
+{
+    return LowerParams{g.n, g.h, g.w, g.ci, g.ho, g.wo, g.kh, g.kw, g.vpad, g.hpad, g.vstr, g.hstr, g.vdil, g.hdil, (int)g.K, lowered_kp(g)};
+}
+static int launch_lower(const Geo& g, const void* x, float* rows, cudaStream_t st)
+{
+    LowerParams lp = lower_params(g);
+    int64_t total = g.M * (lp.Kp / 4);
+    int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    tc_lower_kernel<<<blocks, 256, 0, st>>>(lp, (const float*)x, (float4*)rows);
+    return check_launch("tc_lower_kernel");
+}
+
 int tc_fprop(const Geo& g, const void* x, const void* w, const void* bias, const b2c_bn_params* bn, int relu,
              void* y, void* ws, size_t ws_bytes, cudaStream_t st)
 {
     WStride wsd = w_stride(g.w_layout, g.ci, g.co, g.kh, g.kw);
+    if (g.ci % 32 != 0) {
+        // few-channel layer: write out the im2row matrix, then a 1x1 convolution over it
+        const int Kp = lowered_kp(g);
+        const size_t lbytes = align_up((size_t)g.M * Kp * sizeof(float), 1024);
+        const size_t fbytes = align_up((size_t)g.co * Kp * sizeof(float), 1024);
+        uintptr_t base = align_up((uintptr_t)ws, 1024);
+        if (!ws || base + lbytes + 2 * fbytes + 1024 > (uintptr_t)ws + ws_bytes) return B2C_ERR_WORKSPACE_TOO_SMALL;
+        float* rows = (float*)base;
+        float* w_hi = (float*)align_up(base + lbytes, 1024);
+        float* w_lo = (float*)((uintptr_t)w_hi + fbytes);
+        int rc = launch_lower(g, x, rows, st);
+        if (rc) return rc;
+        int64_t total = (int64_t)g.co * Kp;
+        tc_prep_filter_lowered_kernel<<<(int)((total + 255) / 256), 256, 0, st>>>(g.co, (int)g.K, Kp, g.ci, g.kw, wsd.sk, wsd.sc, wsd.sr,
+                                                                                 wsd.ss, (const float*)w, w_hi, w_lo);
+        rc = check_launch("tc_prep_filter_lowered_kernel");
+        if (rc) return rc;
+        PrepParams none{};
+        FwdLaunch f{g.n, g.ho, g.wo, Kp, g.ho, g.wo, g.co, 1, 1, 0, 0, g.ho, g.wo, 1, 1, 1, 1,
+                    (int64_t)g.ho * g.wo * g.co, (int64_t)g.wo * g.co, (int64_t)g.co};
+        return run_fwd(f, rows, nullptr, none, bias, bn, relu, (float*)y, (void*)w_hi, 2 * fbytes + 1024, st, true);
+    }
     PrepParams pp{g.co, g.ci, g.kh, g.kw, wsd.sk, wsd.sc, wsd.sr, wsd.ss, 0, 1, 0, 1};
     FwdLaunch f{g.n, g.h, g.w, g.ci, g.ho, g.wo, g.co, g.kh, g.kw, -g.vpad, -g.hpad,
                 g.h + 2 * g.vpad - (g.kh - 1) * g.vdil, g.w + 2 * g.hpad - (g.kw - 1) * g.hdil,
@@ -884,36 +988,50 @@ int tc_dgrad(const Geo& g, const void* dy, const void* w, void* dx, void* ws, si
 int tc_wgrad(const Geo& g, const void* x, const void* dy, void* dw, void* db, void* ws, size_t ws_bytes, cudaStream_t st)
 {
     if (!load_driver_entry_points()) return B2C_ERR_UNSUPPORTED;
+    const bool low = g.ci % 32 != 0;
+    const int Krows = low ? lowered_kp(g) : (int)g.K;
     WgradPlan pl = wgrad_plan(g);
-    const size_t pbytes = align_up((size_t)pl.splits * g.K * g.co * sizeof(float), 1024);
+    const size_t lbytes = low ? align_up((size_t)g.M * Krows * sizeof(float), 1024) : 0;
+    const size_t pbytes = align_up((size_t)pl.splits * Krows * g.co * sizeof(float), 1024);
     uintptr_t base = align_up((uintptr_t)ws, 1024);
     const size_t cs = channel_sum_workspace_bytes(g.n, g.co, g.ho * g.wo);
-    if (!ws || base + pbytes + (db ? cs : 0) > (uintptr_t)ws + ws_bytes) return B2C_ERR_WORKSPACE_TOO_SMALL;
+    if (!ws || base + lbytes + pbytes + (db ? cs : 0) > (uintptr_t)ws + ws_bytes) return B2C_ERR_WORKSPACE_TOO_SMALL;
     if (((uintptr_t)x & 15) || ((uintptr_t)dy & 15)) return B2C_ERR_MISALIGNED;
-    float* partial = (float*)base;
+    float* partial = (float*)(base + lbytes);
     CUtensorMap ma, mb;
-    if (!make_map_im2col(&ma, x, g.n, g.h, g.w, g.ci, -g.vpad, -g.hpad, g.h + 2 * g.vpad - (g.kh - 1) * g.vdil,
-                         g.w + 2 * g.hpad - (g.kw - 1) * g.hdil, g.vstr, g.hstr, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B))
-        return B2C_ERR_UNSUPPORTED;
-    if (!make_map_2d(&mb, dy, (uint64_t)g.M, (uint64_t)g.co, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) return B2C_ERR_UNSUPPORTED;
     TcParams p{};
-    p.M = (int)g.K; p.N = g.co; p.P = g.ho; p.Q = g.wo; p.kblocks = pl.kblocks;
-    p.C = g.ci; p.cblocks = g.ci / 32; p.S = g.kw;
-    p.str_h = g.vstr; p.str_w = g.hstr; p.dil_h = g.vdil; p.dil_w = g.hdil; p.low_h = -g.vpad; p.low_w = -g.hpad;
+    if (low) {
+        // few-channel layer: gradient of the 1x1 convolution over the written-out im2row matrix
+        float* rows = (float*)base;
+        int rc = launch_lower(g, x, rows, st);
+        if (rc) return rc;
+        if (!make_map_im2col(&ma, rows, g.n, g.ho, g.wo, Krows, 0, 0, g.ho, g.wo, 1, 1, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B))
+            return B2C_ERR_UNSUPPORTED;
+        p.C = Krows; p.cblocks = Krows / 32; p.S = 1;
+        p.str_h = 1; p.str_w = 1; p.dil_h = 1; p.dil_w = 1; p.low_h = 0; p.low_w = 0;
+    } else {
+        if (!make_map_im2col(&ma, x, g.n, g.h, g.w, g.ci, -g.vpad, -g.hpad, g.h + 2 * g.vpad - (g.kh - 1) * g.vdil,
+                             g.w + 2 * g.hpad - (g.kw - 1) * g.hdil, g.vstr, g.hstr, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B))
+            return B2C_ERR_UNSUPPORTED;
+        p.C = g.ci; p.cblocks = g.ci / 32; p.S = g.kw;
+        p.str_h = g.vstr; p.str_w = g.hstr; p.dil_h = g.vdil; p.dil_w = g.hdil; p.low_h = -g.vpad; p.low_w = -g.hpad;
+    }
+    if (!make_map_2d(&mb, dy, (uint64_t)g.M, (uint64_t)g.co, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) return B2C_ERR_UNSUPPORTED;
+    p.M = Krows; p.N = g.co; p.P = g.ho; p.Q = g.wo; p.kblocks = pl.kblocks;
     p.Mpix = (int)g.M;
     p.out = partial;
     CUtensorMap mo = mb;
-    p.tma_store = make_map_out(&mo, partial, (uint64_t)pl.splits, (uint64_t)g.K, (uint64_t)g.co) ? 1 : 0;
+    p.tma_store = make_map_out(&mo, partial, (uint64_t)pl.splits, (uint64_t)Krows, (uint64_t)g.co) ? 1 : 0;
     int rc = dispatch_tc<TCM_WGRAD>(pl.bn, ma, mb, mb, mo, p, pl.splits, st);
     if (rc) return rc;
     WStride wsd = w_stride(g.w_layout, g.ci, g.co, g.kh, g.kw);
-    WgradReduceParams rp{(int)g.K, g.co, g.ci, g.kw, pl.splits, wsd.sk, wsd.sc, wsd.sr, wsd.ss};
-    int64_t total = g.K * g.co;
+    WgradReduceParams rp{Krows, g.co, g.ci, g.kw, pl.splits, wsd.sk, wsd.sc, wsd.sr, wsd.ss, (int)g.K};
+    int64_t total = (int64_t)Krows * g.co;
     int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
     tc_wgrad_reduce_kernel<<<blocks, 256, 0, st>>>(rp, partial, (float*)dw);
     rc = check_launch("tc_wgrad_reduce_kernel");
     if (rc || !db) return rc;
-    return channel_sum(B2C_F32, B2C_LAYOUT_NHWC, g.n, g.co, g.ho * g.wo, dy, db, (void*)(base + pbytes), cs, st);
+    return channel_sum(B2C_F32, B2C_LAYOUT_NHWC, g.n, g.co, g.ho * g.wo, dy, db, (void*)(base + lbytes + pbytes), cs, st);
 }
 
 #ifdef B2C_TC_PROFILE

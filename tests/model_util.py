@@ -5,9 +5,14 @@ from oracle import cpu_model as cm
 from pydtnn_b200.utils import PYDTNN_TENSOR_FORMAT_NCHW
 
 
+def _real(layers):
+    """Dropout is the identity in evaluation and has no CPU node."""
+    return [l for l in layers if l.canonical_name != "Dropout"]
+
+
 def _spec(layers):
     spec = []
-    for l in layers:
+    for l in _real(layers):
         name = l.canonical_name
         if name == "Conv2D":
             spec.append(("conv", l.co, l.kh, l.vstride, l.vpadding))
@@ -33,7 +38,7 @@ def _spec(layers):
 
 
 def _copy(layers, nodes, nchw):
-    for l, n in zip(layers, nodes):
+    for l, n in zip(_real(layers), nodes):
         name = l.canonical_name
         if name == "Conv2D":
             w = l.weights.ary.get()
@@ -83,7 +88,7 @@ def params_of(layer, nchw):
 
 
 def walk_pairs(layers, nodes):
-    for l, n in zip(layers, nodes):
+    for l, n in zip(_real(layers), nodes):
         yield l, n
         if l.canonical_name == "AdditionBlock":
             for lp, npth in zip(l.paths, n.paths):

@@ -113,6 +113,39 @@ def test_inference_fusion_matches_unfused_chain(layout):
     assert rel_l2(y.ary.get(), ref) <= 2e-4
 
 
+@pytest.mark.parametrize("layout", ["NCHW", "NHWC"])
+def test_alexnet_style_inference_with_fused_conv_relu(layout):
+    """The AlexNet recipe at small size (11x11 stride-4 stem, 5x5 and 3x3 convolutions with their ReLU folded
+    into the convolution epilogue, 3x3 stride-2 max pools, three FC layers, dropout as identity) in evaluation
+    mode against the CPU oracle chain; inputs are uint8 pixels scaled by 1/255."""
+    from pydtnn_b200.layers import FC, Conv2D, Dropout, Flatten, Input, MaxPool2D
+    from pydtnn_b200.model import Model
+    np.random.seed(1)
+    m = Model(batch_size=4, tensor_format=layout, dtype=np.float32, enable_fused_conv_relu=True)
+    m.add(Input(shape=(67, 67, 3)))
+    m.add(Conv2D(nfilters=32, filter_shape=(11, 11), padding=0, stride=4, activation="relu", weights_initializer="he_uniform"))
+    m.add(MaxPool2D(pool_shape=(3, 3), stride=2))
+    m.add(Conv2D(nfilters=64, filter_shape=(5, 5), padding=2, stride=1, activation="relu", weights_initializer="he_uniform"))
+    m.add(MaxPool2D(pool_shape=(3, 3), stride=2))
+    m.add(Conv2D(nfilters=96, filter_shape=(3, 3), padding=1, stride=1, activation="relu", weights_initializer="he_uniform"))
+    m.add(Conv2D(nfilters=64, filter_shape=(3, 3), padding=1, stride=1, activation="relu", weights_initializer="he_uniform"))
+    m.add(MaxPool2D(pool_shape=(3, 3), stride=2))
+    m.add(Flatten())
+    m.add(FC(shape=(64,), activation="relu", weights_initializer="he_uniform"))
+    m.add(Dropout(rate=0.5))
+    m.add(FC(shape=(10,), activation="softmax", weights_initializer="he_uniform"))
+    net = cpu_twin(m)
+    rng = np.random.Generator(np.random.PCG64(9))
+    shape = (4, 67, 67, 3) if layout == "NHWC" else (4, 3, 67, 67)
+    x = (rng.integers(0, 256, shape).astype(np.uint8) / 255.0).astype(np.float32)
+    y = m.evaluate_batch(x)
+    m.synchronize()
+    names = [type(l).__name__ for l in m._eval_layers]
+    assert names.count("Conv2DReluGPU") == 4 and "Conv2DGPU" not in names
+    ref = net.forward(x, False)
+    assert _rel_l2(y.ary.get(), ref) <= 1e-5
+
+
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     from pydtnn_b200 import _lib
     monkeypatch.setattr(_lib, "_lib", None)
