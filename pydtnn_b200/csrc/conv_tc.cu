@@ -55,16 +55,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 #define TC_WAIT_CYCLES 2000000000LL   // about one second at the boost clock
 
 // Bounded wait. Returns false when the wait ran out or another role already gave up.
+// mbarrier.try_wait suspends the thread in hardware for a short while, so the loop is not hot; the abort
+// flag and the clock are looked at only every 32 failed tries to keep waiting warps off the LSU and the
+// issue ports the working warps need.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
     if (mbar_try_wait(bar, parity)) return true;
-    long long t0 = clock64();
+    long long t0 = 0;
+    uint32_t tries = 0;
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if (clock64() - t0 > TC_WAIT_CYCLES) {
-            *abort_flag = 1;
-            atomicCAS(status, 0, code);
-            return false;
+        if ((++tries & 31u) == 0) {
+            if (*abort_flag) return false;
+            const long long now = clock64();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > TC_WAIT_CYCLES) {
+                *abort_flag = 1;
+                atomicCAS(status, 0, code);
+                return false;
+            }
         }
     }
 }
@@ -125,6 +133,17 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
                    "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
                    "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
                    "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+}
+// The same load with the 32 columns landing in float registers r[0..31] (constant indices after inlining).
+__device__ __forceinline__ void tmem_ld_32x32_f(uint32_t taddr, float* r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=f"(r[0]), "=f"(r[1]), "=f"(r[2]), "=f"(r[3]), "=f"(r[4]), "=f"(r[5]), "=f"(r[6]), "=f"(r[7]),
+                   "=f"(r[8]), "=f"(r[9]), "=f"(r[10]), "=f"(r[11]), "=f"(r[12]), "=f"(r[13]), "=f"(r[14]), "=f"(r[15]),
+                   "=f"(r[16]), "=f"(r[17]), "=f"(r[18]), "=f"(r[19]), "=f"(r[20]), "=f"(r[21]), "=f"(r[22]), "=f"(r[23]),
+                   "=f"(r[24]), "=f"(r[25]), "=f"(r[26]), "=f"(r[27]), "=f"(r[28]), "=f"(r[29]), "=f"(r[30]), "=f"(r[31])
                  : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
@@ -272,8 +291,63 @@ struct TcParams {
     int relu;
     float* out;                // FWD: row m=(n,i,j) at out + n*o_sn + i*o_sh + j*o_sw.  WGRAD: partial [split][M][N]
     int64_t o_sn, o_sh, o_sw;
+    int epi;                   // TC_EPI_* bits: which per-channel steps the FWD epilogue applies
     int tma_store;             // output rows are dense [M][N] (or [split][M][N]): store tiles through the output tensor map
 };
+
+// Per-channel epilogue steps of the forward pass, decided once on the host so the drain warps branch on
+// one register instead of testing three pointers per element.
+enum { TC_EPI_BIAS = 1, TC_EPI_BN = 2, TC_EPI_RELU = 4, TC_EPI_VEC = 8 };
+
+// bias / BN-scale / ReLU on the 32 accumulators a[0..31] of one output row, channels nbase..nbase+31.
+// The per-channel vectors are read at warp-uniform addresses (every lane owns a different row of the
+// same channels); with TC_EPI_VEC (all vectors 16-byte aligned, N a multiple of 4) four channels per load.
+__device__ __forceinline__ void tc_epilogue_math(const TcParams& p, int nbase, float* a)
+{
+    if (p.epi & TC_EPI_VEC) {
+        if (p.epi & TC_EPI_BIAS) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+                if (nbase + j < p.N) {
+                    const float4 b = __ldg(reinterpret_cast<const float4*>(p.bias + nbase + j));
+                    a[j] += b.x; a[j + 1] += b.y; a[j + 2] += b.z; a[j + 3] += b.w;
+                }
+        }
+        if (p.epi & TC_EPI_BN) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+                if (nbase + j < p.N) {
+                    const float4 mu = __ldg(reinterpret_cast<const float4*>(p.mean + nbase + j));
+                    const float4 is = __ldg(reinterpret_cast<const float4*>(p.inv_std + nbase + j));
+                    const float4 ga = __ldg(reinterpret_cast<const float4*>(p.gamma + nbase + j));
+                    const float4 be = __ldg(reinterpret_cast<const float4*>(p.beta + nbase + j));
+                    float t;
+                    t = (a[j] - mu.x) * is.x;     a[j] = t * ga.x + be.x;
+                    t = (a[j + 1] - mu.y) * is.y; a[j + 1] = t * ga.y + be.y;
+                    t = (a[j + 2] - mu.z) * is.z; a[j + 2] = t * ga.z + be.z;
+                    t = (a[j + 3] - mu.w) * is.w; a[j + 3] = t * ga.w + be.w;
+                }
+        }
+    } else {
+        if (p.epi & TC_EPI_BIAS) {
+#pragma unroll
+            for (int j = 0; j < 32; j++)
+                if (nbase + j < p.N) a[j] += __ldg(p.bias + nbase + j);
+        }
+        if (p.epi & TC_EPI_BN) {
+#pragma unroll
+            for (int j = 0; j < 32; j++)
+                if (nbase + j < p.N) {
+                    const float t = (a[j] - __ldg(p.mean + nbase + j)) * __ldg(p.inv_std + nbase + j);
+                    a[j] = t * __ldg(p.gamma + nbase + j) + __ldg(p.beta + nbase + j);
+                }
+        }
+    }
+    if (p.epi & TC_EPI_RELU) {
+#pragma unroll
+        for (int j = 0; j < 32; j++) a[j] = fmaxf(a[j], 0.f);
+    }
+}
 
 template <int BN, int STAGES>
 struct TcSmem {
@@ -425,8 +499,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     TC_PROF_ADD(1);    // MMA: waiting for a drained TMEM buffer
                     ok = mbar_wait(&full_bar[s], use & 1, abort_flag, &g_tc_status, TC_ERR_FULL);
                     TC_PROF_ADD(2);    // MMA: waiting for TMA data
-                    ok = ok && mbar_wait(&xform_bar[s], use & 1, abort_flag, &g_tc_status, TC_ERR_XFORM);
-                    TC_PROF_ADD(3);    // MMA: waiting for the transform
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
@@ -435,12 +507,32 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     const uint64_t b_hi = make_smem_desc(sa + 2 * L::A_BYTES, LBO, SBO, LAYOUT);
                     const uint64_t b_lo = make_smem_desc(sa + 2 * L::A_BYTES + L::B_BYTES, LBO, SBO, LAYOUT);
                     const uint32_t d = tmem_base + (uint32_t)(b * BN);
+                    // Products that need no transformed operand go first, so the tensor pipe works while the
+                    // transform warps split this stage: hi*hi always (the raw tile is "hi"); in FWD also
+                    // hi*lo, because the filter's lo half arrives ready-made by TMA.
+                    if (!WRITE_HI) {
+#pragma unroll
+                        for (int k = 0; k < 4; k++) {
+                            const uint64_t adv = (uint64_t)k * KADV;
+                            umma_tf32(d, a_hi + adv, b_hi + adv, idesc, (!chunk_start || k > 0) ? 1u : 0u);
+                            if (MODE == TCM_FWD) umma_tf32(d, a_hi + adv, b_lo + adv, idesc, 1u);
+                        }
+                    }
+                    ok = mbar_wait(&xform_bar[s], use & 1, abort_flag, &g_tc_status, TC_ERR_XFORM);
+                    TC_PROF_ADD(3);    // MMA: waiting for the transform
+                    if (!ok) break;
+                    tc_fence_after();
 #pragma unroll
                     for (int k = 0; k < 4; k++) {
                         const uint64_t adv = (uint64_t)k * KADV;
-                        umma_tf32(d, a_lo + adv, b_hi + adv, idesc, (!chunk_start || k > 0) ? 1u : 0u);
-                        umma_tf32(d, a_hi + adv, b_lo + adv, idesc, 1u);
-                        umma_tf32(d, a_hi + adv, b_hi + adv, idesc, 1u);
+                        if (WRITE_HI) {
+                            umma_tf32(d, a_lo + adv, b_hi + adv, idesc, (!chunk_start || k > 0) ? 1u : 0u);
+                            umma_tf32(d, a_hi + adv, b_lo + adv, idesc, 1u);
+                            umma_tf32(d, a_hi + adv, b_hi + adv, idesc, 1u);
+                        } else {
+                            umma_tf32(d, a_lo + adv, b_hi + adv, idesc, 1u);
+                            if (MODE == TCM_WGRAD) umma_tf32(d, a_hi + adv, b_lo + adv, idesc, 1u);
+                        }
                     }
                     umma_commit(&empty_bar[s]);
                     if ((kb % TC_CHUNK) == TC_CHUNK - 1 || kb == p.kblocks - 1) { umma_commit(&tfull_bar[b]); gc++; }
@@ -511,8 +603,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             const int ni = tile % nt, rest = tile / nt, mi = rest % mt, z = rest / mt;
             const int m0 = mi * 128, n0 = ni * BN;
             float acc[BN];
-#pragma unroll
-            for (int j = 0; j < BN; j++) acc[j] = 0.f;
             for (int c = 0; c < nchunks && ok; c++, gc++) {
                 const int b = gc & 1;
                 TC_PROF_T0();
@@ -520,13 +610,21 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 if (threadIdx.x == 192) TC_PROF_ADD(7);    // drain: waiting for a finished chunk
                 if (!ok) break;
                 tc_fence_after();
+                const uint32_t tsrc = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(b * BN);
+                if (c == 0) {
+                    // first chunk: straight into the accumulators, all loads in flight before the one wait
 #pragma unroll
-                for (int cc = 0; cc < BN / 32; cc++) {
-                    uint32_t r[32];
-                    tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(b * BN + cc * 32), r);
+                    for (int cc = 0; cc < BN / 32; cc++) tmem_ld_32x32_f(tsrc + (uint32_t)(cc * 32), &acc[cc * 32]);
                     tmem_ld_wait();
+                } else {
 #pragma unroll
-                    for (int j = 0; j < 32; j++) acc[cc * 32 + j] += __uint_as_float(r[j]);
+                    for (int cc = 0; cc < BN / 32; cc++) {
+                        uint32_t r[32];
+                        tmem_ld_32x32(tsrc + (uint32_t)(cc * 32), r);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 32; j++) acc[cc * 32 + j] += __uint_as_float(r[j]);
+                    }
                 }
                 tc_fence_before();
                 __syncwarp();
@@ -558,26 +656,13 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 for (int cc = 0; cc < BN / 32; cc++) {
                     if (n0 + cc * 32 < p.N && m0 + quad * 32 < p.M) {       // slabs wholly outside the output are skipped
                         uint8_t* buf = ebuf + (ecount & 1) * 4096;
+                        if (MODE == TCM_FWD && p.epi) tc_epilogue_math(p, n0 + cc * 32, &acc[cc * 32]);
                         if (lane == 0) tma_store_wait_read<1>();     // the store that last read this slab is done
                         __syncwarp();
 #pragma unroll
-                        for (int j = 0; j < 32; j += 4) {
-                            float v[4];
-#pragma unroll
-                            for (int e = 0; e < 4; e++) {
-                                float a = acc[cc * 32 + j + e];
-                                if (MODE == TCM_FWD) {
-                                    const int ne = n0 + cc * 32 + j + e;
-                                    if (ne < p.N) {
-                                        if (p.bias) a += p.bias[ne];
-                                        if (p.mean) { float tt = (a - p.mean[ne]) * p.inv_std[ne]; a = tt * p.gamma[ne] + p.beta[ne]; }
-                                        if (p.relu) a = fmaxf(a, 0.f);
-                                    }
-                                }
-                                v[e] = a;
-                            }
-                            *reinterpret_cast<float4*>(buf + lane * 128 + ((((j >> 2) ^ (lane & 7))) << 4)) = make_float4(v[0], v[1], v[2], v[3]);
-                        }
+                        for (int j = 0; j < 32; j += 4)
+                            *reinterpret_cast<float4*>(buf + lane * 128 + ((((j >> 2) ^ (lane & 7))) << 4)) =
+                                make_float4(acc[cc * 32 + j], acc[cc * 32 + j + 1], acc[cc * 32 + j + 2], acc[cc * 32 + j + 3]);
                         fence_proxy_async();
                         __syncwarp();
                         if (lane == 0) {
@@ -593,24 +678,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll
                 for (int cc = 0; cc < BN / 32; cc++) {
                     if (n0 + cc * 32 < p.N) {
+                        if (MODE == TCM_FWD && p.epi) tc_epilogue_math(p, n0 + cc * 32, &acc[cc * 32]);
 #pragma unroll
-                        for (int j = 0; j < 32; j += 4) {
-                            float v[4];
-#pragma unroll
-                            for (int e = 0; e < 4; e++) {
-                                float a = acc[cc * 32 + j + e];
-                                if (MODE == TCM_FWD) {
-                                    const int ne = n0 + cc * 32 + j + e;
-                                    if (ne < p.N) {
-                                        if (p.bias) a += p.bias[ne];
-                                        if (p.mean) { float tt = (a - p.mean[ne]) * p.inv_std[ne]; a = tt * p.gamma[ne] + p.beta[ne]; }
-                                        if (p.relu) a = fmaxf(a, 0.f);
-                                    }
-                                }
-                                v[e] = a;
-                            }
-                            *reinterpret_cast<float4*>(stage + lane * 36 + j) = make_float4(v[0], v[1], v[2], v[3]);
-                        }
+                        for (int j = 0; j < 32; j += 4)
+                            *reinterpret_cast<float4*>(stage + lane * 36 + j) =
+                                make_float4(acc[cc * 32 + j], acc[cc * 32 + j + 1], acc[cc * 32 + j + 2], acc[cc * 32 + j + 3]);
                         __syncwarp();
 #pragma unroll
                         for (int i = 0; i < 8; i++) {
@@ -891,6 +963,9 @@ static int run_fwd(const FwdLaunch& f, const void* act, const void* w, const Pre
     p.bias = (const float*)bias;
     if (bn) { p.mean = (const float*)bn->mean; p.inv_std = (const float*)bn->inv_std; p.gamma = (const float*)bn->gamma; p.beta = (const float*)bn->beta; }
     p.relu = relu;
+    p.epi = (p.bias ? TC_EPI_BIAS : 0) | (p.mean ? TC_EPI_BN : 0) | (relu ? TC_EPI_RELU : 0);
+    if (f.N % 4 == 0 && !(((uintptr_t)p.bias | (uintptr_t)p.mean | (uintptr_t)p.inv_std | (uintptr_t)p.gamma | (uintptr_t)p.beta) & 15))
+        p.epi |= TC_EPI_VEC;
     p.out = out; p.o_sn = f.o_sn; p.o_sh = f.o_sh; p.o_sw = f.o_sw;
     // dense rows (plain fprop / stride-1 dgrad): rows are N floats apart in (n, i, j) order
     const bool dense = f.o_sw == f.N && f.o_sh == (int64_t)f.Q * f.N && f.o_sn == (int64_t)f.P * f.Q * f.N;
