@@ -52,6 +52,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 
+// One lane of the (converged) warp is chosen; the compiler knows that exactly one thread runs the guarded
+// code, which lets it keep descriptors, coordinates and barrier addresses in uniform registers, the form
+// the TMA and tensor-core instructions take their operands in.
+__device__ __forceinline__ bool elect_one_sync() {
+    uint32_t pred = 0;
+    asm volatile("{\n\t.reg .b32 rx;\n\t.reg .pred px;\n\telect.sync rx|px, %1;\n\tselp.u32 %0, 1, 0, px;\n\t}"
+                 : "=r"(pred) : "r"(0xFFFFFFFFu));
+    return pred != 0;
+}
+
 #define TC_WAIT_CYCLES 2000000000LL   // about one second at the boost clock
 
 // Bounded wait. Returns false when the wait ran out or another role already gave up.
@@ -120,6 +130,13 @@ __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint6
                  "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
                  ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// D[tmem] (+)= A[tmem] * B[smem]: the A tile sits in tensor memory (row m in lane m, one tf32 element per
+// 32-bit column, K-major), so only B is fetched from shared memory.
+__device__ __forceinline__ void umma_tf32_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
 // Arrive on an mbarrier once every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -146,6 +163,19 @@ __device__ __forceinline__ void tmem_ld_32x32_f(uint32_t taddr, float* r) {
                    "=f"(r[24]), "=f"(r[25]), "=f"(r[26]), "=f"(r[27]), "=f"(r[28]), "=f"(r[29]), "=f"(r[30]), "=f"(r[31])
                  : "r"(taddr) : "memory");
 }
+// Registers -> tensor memory: lane i of the warp writes r[0..31] to columns taddr.col .. +31 of TMEM lane
+// (taddr.lane + i); a warp may only touch the 32-lane quadrant (warp index mod 4).
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                 "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+                 "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                   "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+                   "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+                   "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ float to_tf32_rn(float v) {
@@ -180,14 +210,21 @@ __device__ int g_tc_status = 0;
 
 enum { TC_ERR_FULL = 1, TC_ERR_XFORM = 2, TC_ERR_EMPTY = 3, TC_ERR_TFULL = 4, TC_ERR_TEMPTY = 5 };
 
+#if defined(B2C_TC_PROFILE) || defined(B2C_TC_SWITCHES)
+#define B2C_TC_DEV 1
+#endif
 #ifdef B2C_TC_PROFILE
 // Development build only: per-role cycle counters of CTA 0 (slots documented at the call sites).
 __device__ long long g_tc_prof[32];
+#define TC_PROF_DECL() long long _pa[16]; for (int _i = 0; _i < 16; _i++) _pa[_i] = 0
 #define TC_PROF_T0() long long _pt = clock64()
-#define TC_PROF_ADD(slot) do { long long _n = clock64(); if (blockIdx.x == 0) g_tc_prof[slot] += _n - _pt; _pt = _n; } while (0)
+#define TC_PROF_ADD(slot) do { long long _n = clock64(); _pa[slot] += _n - _pt; _pt = _n; } while (0)
+#define TC_PROF_FLUSH() do { if (blockIdx.x == 0) for (int _i = 0; _i < 16; _i++) if (_pa[_i]) atomicAdd((unsigned long long*)&g_tc_prof[_i], (unsigned long long)_pa[_i]); } while (0)
 #else
+#define TC_PROF_DECL() do { } while (0)
 #define TC_PROF_T0() do { } while (0)
 #define TC_PROF_ADD(slot) do { } while (0)
+#define TC_PROF_FLUSH() do { } while (0)
 #endif
 
 // ---------------------------------------------------------------------------------------------
@@ -292,6 +329,9 @@ struct TcParams {
     float* out;                // FWD: row m=(n,i,j) at out + n*o_sn + i*o_sh + j*o_sw.  WGRAD: partial [split][M][N]
     int64_t o_sn, o_sh, o_sw;
     int epi;                   // TC_EPI_* bits: which per-channel steps the FWD epilogue applies
+#ifdef B2C_TC_DEV
+    int dbg;                   // development build only: 2 = issue one MMA of three, 4 = transform warps do no work
+#endif
     int tma_store;             // output rows are dense [M][N] (or [split][M][N]): store tiles through the output tensor map
 };
 
@@ -349,18 +389,25 @@ __device__ __forceinline__ void tc_epilogue_math(const TcParams& p, int nbase, f
     }
 }
 
+// Shared memory per pipeline stage: the raw A tile (activations), then the hi and lo halves of the B tile.
+// Tensor memory (512 columns): two accumulator buffers of BN columns, then per stage 64 columns holding
+// the hi and lo halves of the A tile (128 rows x 32 k).
 template <int BN, int STAGES>
 struct TcSmem {
     static constexpr int A_BYTES = 128 * 128;   // 128 rows x 32 floats (FWD) or 32 pixels x 128 rows (WGRAD)
     static constexpr int B_BYTES = BN * 128;
-    static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
+    static constexpr int STAGE_BYTES = A_BYTES + 2 * B_BYTES;
     static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
     static constexpr int EPI_OFFSET = BAR_OFFSET + 1024;          // barriers and flags live in the first 256 bytes
     static constexpr int EPI_BYTES = 4 * 2 * 4096;                // per drain warp: two 32 x 32 float staging slabs
     static constexpr int TOTAL = EPI_OFFSET + EPI_BYTES + 1024;   // + alignment slack
+    static constexpr int TMEM_A_COL = 2 * BN;                     // first column of the A slots
+    static constexpr int TMEM_COLS = 512;
+    static_assert(2 * BN + STAGES * 64 <= TMEM_COLS, "tensor memory budget");
+    static_assert(TOTAL <= 232448, "shared memory budget");
 };
 
-template <int MODE, int BN, int STAGES, bool WRITE_HI>
+template <int MODE, int BN, int STAGES>
 __global__ void __launch_bounds__(320, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b0,
                const __grid_constant__ CUtensorMap tmap_b1, const __grid_constant__ CUtensorMap tmap_out, TcParams p)
@@ -381,6 +428,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    TC_PROF_DECL();
     const int mt = (p.M + 127) / 128, nt = (p.N + BN - 1) / BN;
     const int total_tiles = mt * nt * p.splits;
     const int nchunks = (p.kblocks + TC_CHUNK - 1) / TC_CHUNK;
@@ -392,7 +440,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         fence_barrier_init();
         fence_proxy_async();
     }
-    if (warp == 1) { tmem_alloc(tmem_slot, 2 * BN); tmem_relinquish(); }
+    if (warp == 1) { tmem_alloc(tmem_slot, L::TMEM_COLS); tmem_relinquish(); }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -400,8 +448,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
-        // The whole warp takes part: lane 0 waits for the stage and arms the barrier, then lanes 0..(boxes-1)
-        // each issue one TMA box, so the issue cost of the (up to eight) boxes of a k-block is paid in parallel.
+        // The warp stays converged (every lane waits and computes the same coordinates); one elected lane arms
+        // the barrier and issues the boxes of the k-block.
         int it = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
@@ -414,72 +462,82 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 const int p0 = rem / p.Q, q0 = rem - p0 * p.Q;
                 base_w = q0 * p.str_w + p.low_w; base_h = p0 * p.str_h + p.low_h;
             }
-            // WGRAD: this lane's box is fixed for the tile: lanes 0-3 an x box (32 rows of (tap, ci)),
-            // lanes 4.. a dy box (32 output channels)
-            bool lane_has_box = false;
-            int box_c0 = 0, box_offw = 0, box_offh = 0, box_co = 0, boxes = 0;
+            // WGRAD: the tile's boxes are fixed: up to four x boxes (32 rows of (tap, ci) each) and BN/32 dy
+            // boxes (32 output channels each)
+            int box_c0[4] = {0, 0, 0, 0}, box_offw[4] = {0, 0, 0, 0}, box_offh[4] = {0, 0, 0, 0};
+            int boxes = 0;
             if (MODE == TCM_WGRAD) {
-                if (lane < 4) {
-                    const int mrow = m0 + 32 * lane;
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const int mrow = m0 + 32 * j;
                     if (mrow < p.M) {
                         const int tap = mrow / p.C;
-                        box_c0 = mrow - tap * p.C;
+                        box_c0[j] = mrow - tap * p.C;
                         const int r = tap / p.S, sx = tap - r * p.S;
-                        box_offw = sx * p.dil_w; box_offh = r * p.dil_h;
-                        lane_has_box = true;
+                        box_offw[j] = sx * p.dil_w; box_offh[j] = r * p.dil_h;
+                        boxes++;
                     }
-                } else if (lane < 4 + BN / 32) {
-                    box_co = n0 + 32 * (lane - 4);
-                    lane_has_box = box_co < p.N;
                 }
-                boxes = __popc(__ballot_sync(0xffffffffu, lane_has_box));
+#pragma unroll
+                for (int j = 0; j < BN / 32; j++) if (n0 + 32 * j < p.N) boxes++;
             }
             const int pix_begin = (MODE == TCM_WGRAD) ? z * p.kblocks * 32 : 0;
             for (int kb = 0; kb < p.kblocks; kb++, it++) {
                 const int s = it % STAGES, use = it / STAGES;
-                int good = 1;
-                if (lane == 0) {
-                    TC_PROF_T0();
-                    if (use > 0 && !mbar_wait(&empty_bar[s], (use - 1) & 1, abort_flag, &g_tc_status, TC_ERR_EMPTY)) good = 0;
-                    TC_PROF_ADD(0);    // producer: waiting for a free stage
-                    if (good) mbar_expect_tx(&full_bar[s], MODE == TCM_FWD ? (uint32_t)(L::A_BYTES + 2 * L::B_BYTES) : (uint32_t)(boxes * 4096));
-                }
-                good = __shfl_sync(0xffffffffu, good, 0);
+                TC_PROF_T0();
+                bool good = true;
+                if (use > 0) good = mbar_wait(&empty_bar[s], (use - 1) & 1, abort_flag, &g_tc_status, TC_ERR_EMPTY);
+                good = __all_sync(0xffffffffu, good);
+                if (lane == 0) TC_PROF_ADD(0);    // producer: waiting for a free stage
                 if (!good) { ok = false; break; }
                 uint8_t* st = smem + s * L::STAGE_BYTES;
                 if (MODE == TCM_FWD) {
-                    if (lane == 0) {
-                        const int tap = kb / p.cblocks, cb = kb - tap * p.cblocks;
-                        const int r = tap / p.S, sx = tap - r * p.S;
-                        tma_load_im2col_4d(st, &tmap_a, &full_bar[s], cb * 32, base_w, base_h, img,
-                                           (uint16_t)(sx * p.dil_w), (uint16_t)(r * p.dil_h));
-                    } else if (lane == 1) {
-                        tma_load_2d(st + 2 * L::A_BYTES, &tmap_b0, &full_bar[s], kb * 32, n0);
-                    } else if (lane == 2) {
-                        tma_load_2d(st + 2 * L::A_BYTES + L::B_BYTES, &tmap_b1, &full_bar[s], kb * 32, n0);
+                    const int tap = kb / p.cblocks, cb = kb - tap * p.cblocks;
+                    const int r = tap / p.S, sx = tap - r * p.S;
+                    if (elect_one_sync()) {
+#ifdef B2C_TC_DEV
+                        if (p.dbg & 64) mbar_arrive(&full_bar[s]);
+                        else
+#endif
+                        {
+                            mbar_expect_tx(&full_bar[s], (uint32_t)L::STAGE_BYTES);
+                            tma_load_im2col_4d(st, &tmap_a, &full_bar[s], cb * 32, base_w, base_h, img,
+                                               (uint16_t)(sx * p.dil_w), (uint16_t)(r * p.dil_h));
+                            tma_load_2d(st + L::A_BYTES, &tmap_b0, &full_bar[s], kb * 32, n0);
+                            tma_load_2d(st + L::A_BYTES + L::B_BYTES, &tmap_b1, &full_bar[s], kb * 32, n0);
+                        }
                     }
-                } else if (lane_has_box) {
+                } else {
                     const int pix0 = pix_begin + kb * 32;
-                    if (lane < 4) {
-                        const int im = pix0 / (p.P * p.Q);
-                        const int rem = pix0 - im * (p.P * p.Q);
-                        const int p0 = rem / p.Q, q0 = rem - p0 * p.Q;
-                        tma_load_im2col_4d(st + lane * 4096, &tmap_a, &full_bar[s], box_c0, q0 * p.str_w + p.low_w,
-                                           p0 * p.str_h + p.low_h, im, (uint16_t)box_offw, (uint16_t)box_offh);
-                    } else {
-                        tma_load_2d(st + 2 * L::A_BYTES + (lane - 4) * 4096, &tmap_b0, &full_bar[s], box_co, pix0);
+                    const int im = pix0 / (p.P * p.Q);
+                    const int rem = pix0 - im * (p.P * p.Q);
+                    const int p0 = rem / p.Q, q0 = rem - p0 * p.Q;
+                    const int cw = q0 * p.str_w + p.low_w, chh = p0 * p.str_h + p.low_h;
+                    if (elect_one_sync()) {
+                        mbar_expect_tx(&full_bar[s], (uint32_t)(boxes * 4096));
+#pragma unroll
+                        for (int j = 0; j < 4; j++)
+                            if (m0 + 32 * j < p.M)
+                                tma_load_im2col_4d(st + j * 4096, &tmap_a, &full_bar[s], box_c0[j], cw, chh, im,
+                                                   (uint16_t)box_offw[j], (uint16_t)box_offh[j]);
+#pragma unroll
+                        for (int j = 0; j < BN / 32; j++)
+                            if (n0 + 32 * j < p.N)
+                                tma_load_2d(st + L::A_BYTES + j * 4096, &tmap_b0, &full_bar[s], n0 + 32 * j, pix0);
                     }
                 }
                 __syncwarp();
+                if (lane == 0) TC_PROF_ADD(14);   // producer: TMA issue
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
-        if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc_tf32(128, BN, MODE == TCM_WGRAD, MODE == TCM_WGRAD);
-            // K-major tiles: rows of 128 B, 8-row groups 1024 B apart, K advances 32 B inside the row.
-            // MN-major tiles: 32-row (K) boxes of 4096 B per 32 M/N elements, 4-row swizzle atoms of 512 B,
-            // K advances by 8 rows = 1024 B.
+        // Converged warp, one elected lane issues (see elect_one_sync).
+        {
+            constexpr uint32_t idesc = make_idesc_tf32(128, BN, 0, MODE == TCM_WGRAD);
+            // B tiles, K-major (FWD): rows of 128 B, 8-row groups 1024 B apart, K advances 32 B inside the row.
+            // B tiles, MN-major (WGRAD): 32-row (K) boxes of 4096 B per 32 N elements, 4-row swizzle atoms of
+            // 512 B, K advances by 8 rows = 1024 B.  A comes from tensor memory, K advances 8 columns.
             constexpr uint32_t LBO = (MODE == TCM_WGRAD) ? 4096 : 0;
             constexpr uint32_t SBO = (MODE == TCM_WGRAD) ? 512 : 1024;
             constexpr uint32_t LAYOUT = (MODE == TCM_WGRAD) ? 1 : 2;
@@ -491,60 +549,58 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     const int s = it % STAGES, use = it / STAGES;
                     const int b = gc & 1;
                     const bool chunk_start = (kb % TC_CHUNK) == 0;
+                    const bool chunk_end = (kb % TC_CHUNK) == TC_CHUNK - 1 || kb == p.kblocks - 1;
                     TC_PROF_T0();
-                    if (chunk_start && gc >= 2) {
+                    if (chunk_start && gc >= 2)
                         ok = mbar_wait(&tempty_bar[b], ((gc >> 1) - 1) & 1, abort_flag, &g_tc_status, TC_ERR_TEMPTY);
-                        if (!ok) break;
-                    }
-                    TC_PROF_ADD(1);    // MMA: waiting for a drained TMEM buffer
-                    ok = mbar_wait(&full_bar[s], use & 1, abort_flag, &g_tc_status, TC_ERR_FULL);
-                    TC_PROF_ADD(2);    // MMA: waiting for TMA data
+                    if (lane == 0) TC_PROF_ADD(1);    // MMA: waiting for a drained TMEM buffer
+                    // the transform warps arrive only after they have seen the stage's TMA data land
+                    if (ok) ok = mbar_wait(&xform_bar[s], use & 1, abort_flag, &g_tc_status, TC_ERR_XFORM);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (lane == 0) TC_PROF_ADD(3);    // MMA: waiting for the transform
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
-                    const uint64_t a_hi = make_smem_desc(sa, LBO, SBO, LAYOUT);
-                    const uint64_t a_lo = make_smem_desc(sa + L::A_BYTES, LBO, SBO, LAYOUT);
-                    const uint64_t b_hi = make_smem_desc(sa + 2 * L::A_BYTES, LBO, SBO, LAYOUT);
-                    const uint64_t b_lo = make_smem_desc(sa + 2 * L::A_BYTES + L::B_BYTES, LBO, SBO, LAYOUT);
+                    const uint64_t b_hi = make_smem_desc(sa + L::A_BYTES, LBO, SBO, LAYOUT);
+                    const uint64_t b_lo = make_smem_desc(sa + L::A_BYTES + L::B_BYTES, LBO, SBO, LAYOUT);
+                    const uint32_t a_hi = tmem_base + (uint32_t)(L::TMEM_A_COL + s * 64);
+                    const uint32_t a_lo = a_hi + 32;
                     const uint32_t d = tmem_base + (uint32_t)(b * BN);
-                    // Products that need no transformed operand go first, so the tensor pipe works while the
-                    // transform warps split this stage: hi*hi always (the raw tile is "hi"); in FWD also
-                    // hi*lo, because the filter's lo half arrives ready-made by TMA.
-                    if (!WRITE_HI) {
+                    if (elect_one_sync()) {
+                        // small terms first: lo*hi, hi*lo, then hi*hi
 #pragma unroll
                         for (int k = 0; k < 4; k++) {
                             const uint64_t adv = (uint64_t)k * KADV;
-                            umma_tf32(d, a_hi + adv, b_hi + adv, idesc, (!chunk_start || k > 0) ? 1u : 0u);
-                            if (MODE == TCM_FWD) umma_tf32(d, a_hi + adv, b_lo + adv, idesc, 1u);
+#ifdef B2C_TC_DEV
+                            if (p.dbg & 32) continue;
+#endif
+                            umma_tf32_ts(d, a_lo + k * 8, b_hi + adv, idesc, (!chunk_start || k > 0) ? 1u : 0u);
+#ifdef B2C_TC_DEV
+                            if (p.dbg & 2) continue;
+#endif
+                            umma_tf32_ts(d, a_hi + k * 8, b_lo + adv, idesc, 1u);
+                            umma_tf32_ts(d, a_hi + k * 8, b_hi + adv, idesc, 1u);
                         }
+                        umma_commit(&empty_bar[s]);
+                        if (chunk_end) umma_commit(&tfull_bar[b]);
                     }
-                    ok = mbar_wait(&xform_bar[s], use & 1, abort_flag, &g_tc_status, TC_ERR_XFORM);
-                    TC_PROF_ADD(3);    // MMA: waiting for the transform
-                    if (!ok) break;
-                    tc_fence_after();
-#pragma unroll
-                    for (int k = 0; k < 4; k++) {
-                        const uint64_t adv = (uint64_t)k * KADV;
-                        if (WRITE_HI) {
-                            umma_tf32(d, a_lo + adv, b_hi + adv, idesc, (!chunk_start || k > 0) ? 1u : 0u);
-                            umma_tf32(d, a_hi + adv, b_lo + adv, idesc, 1u);
-                            umma_tf32(d, a_hi + adv, b_hi + adv, idesc, 1u);
-                        } else {
-                            umma_tf32(d, a_lo + adv, b_hi + adv, idesc, 1u);
-                            if (MODE == TCM_WGRAD) umma_tf32(d, a_hi + adv, b_lo + adv, idesc, 1u);
-                        }
-                    }
-                    umma_commit(&empty_bar[s]);
-                    if ((kb % TC_CHUNK) == TC_CHUNK - 1 || kb == p.kblocks - 1) { umma_commit(&tfull_bar[b]); gc++; }
-                    TC_PROF_ADD(4);    // MMA: issue
+                    __syncwarp();
+                    if (chunk_end) gc++;
+                    if (lane == 0) TC_PROF_ADD(4);    // MMA: issue
                 }
             }
         }
     } else if (warp < 6) {
         // ---------------- operand transform: a = hi + lo ----------------
-        const int t = threadIdx.x - 64;      // 0..127
-        constexpr int A_VEC = L::A_BYTES / 16 / 128;                 // float4 per thread for the A tile
+        // hi = a with the low 13 mantissa bits cleared (what the tensor core reads of a float32 anyway),
+        // lo = a - hi (exact).  Each thread owns one row of the A tile: it reads the row's 32 k-values from the
+        // shared-memory tile and writes hi and lo into the stage's tensor-memory slot, from where the MMAs take
+        // the A operand, so the A tile costs one shared-memory read in total.  In WGRAD the B tile (dy) is split
+        // in shared memory as well (only lo is written: the raw tile serves as hi).
+        const int quad = warp & 3;                   // TMEM lane quadrant this warp may write
+        const int row = quad * 32 + lane;            // A-tile row (GEMM M index inside the tile)
         constexpr int B_VEC = (MODE == TCM_WGRAD) ? L::B_BYTES / 16 / 128 : 0;
+        const int t = threadIdx.x - 64;              // 0..127
         int it = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
@@ -553,39 +609,49 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 TC_PROF_T0();
                 if (!mbar_wait(&full_bar[s], use & 1, abort_flag, &g_tc_status, TC_ERR_FULL)) { ok = false; break; }
                 if (t == 0) TC_PROF_ADD(5);    // transform: waiting for TMA data
-                float4* a_hi = (float4*)(smem + s * L::STAGE_BYTES);
-                float4* a_lo = (float4*)(smem + s * L::STAGE_BYTES + L::A_BYTES);
+                const uint8_t* st = smem + s * L::STAGE_BYTES;
+#ifdef B2C_TC_DEV
+                if (p.dbg & 4) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(&xform_bar[s]); continue; }
+#endif
+                uint32_t v[32], h[32];
+                if (MODE == TCM_FWD) {
+                    // K-major 128B-swizzled tile: row r is 128 B, its 16-byte chunk c sits at chunk c ^ (r & 7)
+                    const uint8_t* a_row = st + row * 128;
 #pragma unroll
-                for (int i = 0; i < A_VEC; i++) {
-                    float4 v = a_hi[t + i * 128];
-                    float4 h, l;
-                    if (WRITE_HI) { h.x = to_tf32_rn(v.x); h.y = to_tf32_rn(v.y); h.z = to_tf32_rn(v.z); h.w = to_tf32_rn(v.w); }
-                    else {   // the tensor core drops the low 13 mantissa bits of the raw value itself
-                        h.x = __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u); h.y = __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u);
-                        h.z = __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u); h.w = __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u);
+                    for (int c = 0; c < 8; c++) {
+                        const uint4 q = *reinterpret_cast<const uint4*>(a_row + ((c ^ (row & 7)) << 4));
+                        v[4 * c] = q.x; v[4 * c + 1] = q.y; v[4 * c + 2] = q.z; v[4 * c + 3] = q.w;
                     }
-                    l.x = v.x - h.x; l.y = v.y - h.y; l.z = v.z - h.z; l.w = v.w - h.w;
-                    if (WRITE_HI) a_hi[t + i * 128] = h;
-                    a_lo[t + i * 128] = l;
+                } else {
+                    // unswizzled boxes of [32 pixels][32 rows]: this thread's row is column `lane` of box `quad`
+                    const uint32_t* a_col = reinterpret_cast<const uint32_t*>(st + quad * 4096) + lane;
+#pragma unroll
+                    for (int k = 0; k < 32; k++) v[k] = a_col[k * 32];
                 }
+#pragma unroll
+                for (int j = 0; j < 32; j++) h[j] = v[j] & 0xFFFFE000u;
+                const uint32_t slot = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(L::TMEM_A_COL + s * 64);
+                tmem_st_32x32(slot, h);
+#pragma unroll
+                for (int j = 0; j < 32; j++) v[j] = __float_as_uint(__uint_as_float(v[j]) - __uint_as_float(h[j]));
+                tmem_st_32x32(slot + 32, v);
                 if (MODE == TCM_WGRAD) {
-                    float4* b_hi = (float4*)(smem + s * L::STAGE_BYTES + 2 * L::A_BYTES);
-                    float4* b_lo = (float4*)(smem + s * L::STAGE_BYTES + 2 * L::A_BYTES + L::B_BYTES);
+                    const float4* b_hi = (const float4*)(st + L::A_BYTES);
+                    float4* b_lo = (float4*)(smem + s * L::STAGE_BYTES + L::A_BYTES + L::B_BYTES);
 #pragma unroll
                     for (int i = 0; i < B_VEC; i++) {
-                        float4 v = b_hi[t + i * 128];
-                        float4 h, l;
-                        if (WRITE_HI) { h.x = to_tf32_rn(v.x); h.y = to_tf32_rn(v.y); h.z = to_tf32_rn(v.z); h.w = to_tf32_rn(v.w); }
-                        else {
-                            h.x = __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u); h.y = __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u);
-                            h.z = __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u); h.w = __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u);
-                        }
-                        l.x = v.x - h.x; l.y = v.y - h.y; l.z = v.z - h.z; l.w = v.w - h.w;
-                        if (WRITE_HI) b_hi[t + i * 128] = h;
+                        const float4 q = b_hi[t + i * 128];
+                        float4 l;
+                        l.x = q.x - __uint_as_float(__float_as_uint(q.x) & 0xFFFFE000u);
+                        l.y = q.y - __uint_as_float(__float_as_uint(q.y) & 0xFFFFE000u);
+                        l.z = q.z - __uint_as_float(__float_as_uint(q.z) & 0xFFFFE000u);
+                        l.w = q.w - __uint_as_float(__float_as_uint(q.w) & 0xFFFFE000u);
                         b_lo[t + i * 128] = l;
                     }
+                    fence_proxy_async();
                 }
-                fence_proxy_async();
+                tmem_st_wait();
+                tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&xform_bar[s]);
                 if (t == 0) TC_PROF_ADD(6);    // transform: work
@@ -700,9 +766,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
         if (p.tma_store && lane == 0) tma_store_wait_read<0>();   // the slabs stay allocated until the last store has read them
     }
+    TC_PROF_FLUSH();
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 2 * BN); }
+    if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, L::TMEM_COLS); }
 }
 
 // Second stage of the weight gradient: fixed-order sum of the per-split partial tiles, written in the
@@ -745,16 +812,6 @@ static bool load_driver_entry_points()
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn) return false;
     g_encode_im2col = (EncodeIm2colFn)fn;
     return true;
-}
-
-// The tensor core reads only the upper 19 bits of a float32 operand, so by default the raw tile
-// serves as "hi" (hi = a with the low 13 mantissa bits cleared) and only "lo" is written.  Setting
-// B2C_TC_WRITE_HI=1 switches to a round-to-nearest split with both halves written back.
-static bool write_hi_mode()
-{
-    static int mode = -1;
-    if (mode < 0) { const char* e = getenv("B2C_TC_WRITE_HI"); mode = (e && e[0] == '1') ? 1 : 0; }
-    return mode == 1;
 }
 
 // 2-D row-major float matrix [rows][cols], box = 32 columns x box_rows rows, 128B swizzle.
@@ -869,13 +926,13 @@ size_t tc_workspace_bytes(const Geo& g, int pass)
            channel_sum_workspace_bytes(g.n, g.co, g.ho * g.wo);
 }
 
-template <int MODE, int BN, int STAGES, bool WH>
+template <int MODE, int BN, int STAGES>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb0, const CUtensorMap& mb1, const CUtensorMap& mo, const TcParams& p, int splits, cudaStream_t st)
 {
     using L = TcSmem<BN, STAGES>;
     static bool attr_set = false;
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(conv_tc_kernel<MODE, BN, STAGES, WH>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+        cudaError_t e = cudaFuncSetAttribute(conv_tc_kernel<MODE, BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
         if (e != cudaSuccess) { set_cuda_error(e, "cudaFuncSetAttribute(conv_tc_kernel)"); return B2C_ERR_CUDA; }
         attr_set = true;
     }
@@ -889,17 +946,19 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb0, const CUtens
     if (tiles > 0x7fffffffLL) return B2C_ERR_TOO_LARGE;
     TcParams q = p;
     q.splits = splits;
+#ifdef B2C_TC_DEV
+    { const char* e = getenv("B2C_TC_DBG"); q.dbg = e ? atoi(e) : 0; }
+#endif
     const int grid = (int)(tiles < sm_count ? tiles : sm_count);     // one persistent CTA per SM
-    conv_tc_kernel<MODE, BN, STAGES, WH><<<grid, 320, L::TOTAL, st>>>(ma, mb0, mb1, mo, q);
+    conv_tc_kernel<MODE, BN, STAGES><<<grid, 320, L::TOTAL, st>>>(ma, mb0, mb1, mo, q);
     return check_launch("conv_tc_kernel");
 }
 
 template <int MODE>
 static int dispatch_tc(int bn, const CUtensorMap& ma, const CUtensorMap& mb0, const CUtensorMap& mb1, const CUtensorMap& mo, const TcParams& p, int splits, cudaStream_t st)
 {
-    const bool wh = write_hi_mode();
-    if (bn == 64) return wh ? launch_tc<MODE, 64, 4, true>(ma, mb0, mb1, mo, p, splits, st) : launch_tc<MODE, 64, 4, false>(ma, mb0, mb1, mo, p, splits, st);
-    return wh ? launch_tc<MODE, 128, 3, true>(ma, mb0, mb1, mo, p, splits, st) : launch_tc<MODE, 128, 3, false>(ma, mb0, mb1, mo, p, splits, st);
+    if (bn == 64) return launch_tc<MODE, 64, 6>(ma, mb0, mb1, mo, p, splits, st);
+    return launch_tc<MODE, 128, 4>(ma, mb0, mb1, mo, p, splits, st);
 }
 
 // Output seen as [planes][rows][cols] floats, box = 32 cols x 32 rows (x 1 plane), 128B swizzle.
@@ -1080,13 +1139,13 @@ int tc_wgrad(const Geo& g, const void* x, const void* dy, void* dw, void* db, vo
         float* rows = (float*)base;
         int rc = launch_lower(g, x, rows, st);
         if (rc) return rc;
-        if (!make_map_im2col(&ma, rows, g.n, g.ho, g.wo, Krows, 0, 0, g.ho, g.wo, 1, 1, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B))
+        if (!make_map_im2col(&ma, rows, g.n, g.ho, g.wo, Krows, 0, 0, g.ho, g.wo, 1, 1, 32, CU_TENSOR_MAP_SWIZZLE_NONE))
             return B2C_ERR_UNSUPPORTED;
         p.C = Krows; p.cblocks = Krows / 32; p.S = 1;
         p.str_h = 1; p.str_w = 1; p.dil_h = 1; p.dil_w = 1; p.low_h = 0; p.low_w = 0;
     } else {
         if (!make_map_im2col(&ma, x, g.n, g.h, g.w, g.ci, -g.vpad, -g.hpad, g.h + 2 * g.vpad - (g.kh - 1) * g.vdil,
-                             g.w + 2 * g.hpad - (g.kw - 1) * g.hdil, g.vstr, g.hstr, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B))
+                             g.w + 2 * g.hpad - (g.kw - 1) * g.hdil, g.vstr, g.hstr, 32, CU_TENSOR_MAP_SWIZZLE_NONE))
             return B2C_ERR_UNSUPPORTED;
         p.C = g.ci; p.cblocks = g.ci / 32; p.S = g.kw;
         p.str_h = g.vstr; p.str_w = g.hstr; p.dil_h = g.vdil; p.dil_w = g.hdil; p.low_h = -g.vpad; p.low_w = -g.hpad;
