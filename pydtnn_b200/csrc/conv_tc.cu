@@ -12,14 +12,15 @@
 //              filter copy
 //   wgrad : dw[co][tap][ci] = sum_pixel x[pixel+tap][ci] * dy[pixel][co]           (split over pixels)
 //
-// 3xTF32: every float32 operand a is split as a = hi + lo with hi = tf32(a) (round to nearest) and
-// lo = a - hi (exact in float32).  Three tensor-core products lo*hi + hi*lo + hi*hi accumulate in
-// the float32 TMEM tile (small terms first).  Filters are split once per call by a small kernel;
-// activation tiles are split in shared memory by the transform warps between TMA arrival and MMA
-// issue.
+// 3xTF32: every float32 operand a is split as a = hi + lo with hi = a with the low 13 mantissa bits
+// cleared (what the tensor core reads of a float32 anyway) and lo = a - hi (exact in float32).  Three
+// tensor-core products lo*hi + hi*lo + hi*hi accumulate in the float32 TMEM tile (small terms first).
+// Filters are split once per call by a small kernel.  The A tile (activations; x^T in wgrad) is split by
+// the transform warps, which read it once from shared memory and write hi and lo into tensor memory with
+// tcgen05.st; the MMAs take A from tensor memory and only B from shared memory.
 //
-// Warp roles (320 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
-// warps 2-5 = operand transform (hi/lo split of the activation tiles in shared memory),
+// Warp roles (320 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer (both stay
+// converged and issue through one elected lane), warps 2-5 = operand transform,
 // warps 6-9 = drain + epilogue: the tensor core's accumulate step truncates, so sums are kept in
 // tensor memory only for a chunk of 8 k-blocks (two TMEM buffers alternate) and added chunk by
 // chunk into float32 registers with round-to-nearest, then bias / BN-scale / ReLU -> global.
