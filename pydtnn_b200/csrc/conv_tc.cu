@@ -898,20 +898,28 @@ static size_t filter_split_bytes(const Geo& g, int pass)
 }
 
 struct WgradPlan { int splits, kblocks, bn; };
+// The pixel axis is cut into `splits` ranges of `kblocks` 32-pixel blocks; tiles x splits work items run on one
+// persistent CTA per SM.  The split count minimises a cost in k-block units: rounds of the CTA grid x (k-blocks per
+// item + a fixed per-item cost for pipeline fill, drain and the partial-tile store) + the second-stage reduce, whose
+// traffic grows with the split count.
 static WgradPlan wgrad_plan(const Geo& g)
 {
     WgradPlan pl;
     pl.bn = g.co <= 64 ? 64 : 128;
     const int64_t Krows = g.ci % 32 == 0 ? g.K : lowered_kp(g);
-    int64_t tiles = ((Krows + 127) / 128) * ((g.co + pl.bn - 1) / pl.bn);
-    int64_t want = (296 + tiles - 1) / tiles;
-    int64_t max_by_pix = g.M / 512;
-    if (max_by_pix < 1) max_by_pix = 1;
-    int64_t s = want < max_by_pix ? want : max_by_pix;
-    if (s > 512) s = 512;
-    int64_t blocks = (g.M + 31) / 32;
-    pl.kblocks = (int)((blocks + s - 1) / s);
-    pl.splits = (int)((blocks + pl.kblocks - 1) / pl.kblocks);
+    const int64_t tiles = ((Krows + 127) / 128) * ((g.co + pl.bn - 1) / pl.bn);
+    const int64_t blocks = (g.M + 31) / 32;
+    const double reduce_per_split = (double)Krows * g.co * 4.0 / 5e12 / 0.6e-6;   // k-block units (0.6 us each)
+    double best = 0.0;
+    pl.splits = 1; pl.kblocks = (int)blocks;
+    for (int64_t s = 1; s <= 512 && s <= blocks; s++) {
+        const int64_t kb = (blocks + s - 1) / s;
+        if ((blocks + kb - 1) / kb != s) continue;       // same k-blocks per split as a smaller count
+        if (kb < 4 && s > 1) break;
+        const int64_t rounds = (tiles * s + 147) / 148;
+        const double cost = (double)rounds * (double)(kb + 6) + (double)s * reduce_per_split;
+        if (s == 1 || cost < best) { best = cost; pl.splits = (int)s; pl.kblocks = (int)kb; }
+    }
     return pl;
 }
 
