@@ -255,7 +255,19 @@ __global__ void reduce2_final_warp_kernel(const double* __restrict__ partial, in
     const int ch = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (ch >= c) return;
     double s0 = 0.0, s1 = 0.0;
-    for (int i = lane; i < chunks; i += 32) { s0 += partial[((int64_t)i * 2) * c + ch]; s1 += partial[((int64_t)i * 2 + 1) * c + ch]; }
+    int i = lane;
+    // four independent loads per value in flight; the order of the additions stays fixed
+    for (; i + 96 < chunks; i += 128) {
+        double a0[4], a1[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            a0[u] = partial[((int64_t)(i + 32 * u) * 2) * c + ch];
+            a1[u] = partial[((int64_t)(i + 32 * u) * 2 + 1) * c + ch];
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++) { s0 += a0[u]; s1 += a1[u]; }
+    }
+    for (; i < chunks; i += 32) { s0 += partial[((int64_t)i * 2) * c + ch]; s1 += partial[((int64_t)i * 2 + 1) * c + ch]; }
     for (int o = 16; o > 0; o >>= 1) { s0 += __shfl_down_sync(0xffffffffu, s0, o); s1 += __shfl_down_sync(0xffffffffu, s1, o); }
     if (lane) return;
     if (mode == 0) {

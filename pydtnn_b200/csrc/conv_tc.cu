@@ -209,7 +209,7 @@ __host__ __device__ constexpr uint32_t make_idesc_tf32(int M, int N, int a_mn_ma
 // Device status word shared by all tensor-core kernels (0 = fine).
 __device__ int g_tc_status = 0;
 
-enum { TC_ERR_FULL = 1, TC_ERR_XFORM = 2, TC_ERR_EMPTY = 3, TC_ERR_TFULL = 4, TC_ERR_TEMPTY = 5 };
+enum { TC_ERR_FULL = 1, TC_ERR_XFORM = 2, TC_ERR_EMPTY = 3, TC_ERR_TFULL = 4, TC_ERR_TEMPTY = 5, TC_ERR_PARTIAL = 6 };
 
 #if defined(B2C_TC_PROFILE) || defined(B2C_TC_SWITCHES)
 #define B2C_TC_DEV 1
@@ -237,8 +237,12 @@ struct PrepParams {
     int r0, rstep, s0, sstep;        // real tap of virtual tap (r, s): (r0 + rstep*r, s0 + sstep*s)
 };
 
-__global__ void tc_prep_filter_kernel(PrepParams p, const float* __restrict__ w, float* __restrict__ hi, float* __restrict__ lo)
+// Also clears `nflags` ints at `flags` (the hand-over flags of the balanced mode of the convolution kernel that
+// follows in the stream), which saves a separate memset.
+__global__ void tc_prep_filter_kernel(PrepParams p, const float* __restrict__ w, float* __restrict__ hi, float* __restrict__ lo,
+                                      int* __restrict__ flags, int nflags)
 {
+    if (blockIdx.x == 0) for (int i = threadIdx.x; i < nflags; i += blockDim.x) flags[i] = 0;
     int64_t K = (int64_t)p.R * p.S * p.C;
     int64_t total = (int64_t)p.rows * K;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -261,6 +265,8 @@ __global__ void tc_prep_filter_kernel(PrepParams p, const float* __restrict__ w,
 // ---------------------------------------------------------------------------------------------
 struct LowerParams { int n, h, w, c, ho, wo, kh, kw, vpad, hpad, vstr, hstr, vdil, hdil, K, Kp; };
 
+// IDX = int when the float4 count fits 31 bits (the usual case): the per-element divisions are then 32-bit.
+template <typename IDX>
 __global__ void tc_lower_kernel(LowerParams p, const float* __restrict__ x, float4* __restrict__ rows)
 {
     // column k -> (row offset, column offset, channel), decoded once per block
@@ -273,10 +279,10 @@ __global__ void tc_lower_kernel(LowerParams p, const float* __restrict__ x, floa
     }
     __syncthreads();
     const int kq = p.Kp / 4;
-    const int64_t total = (int64_t)p.n * p.ho * p.wo * kq;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const IDX total = (IDX)p.n * p.ho * p.wo * kq;
+    for (IDX i = (IDX)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (IDX)gridDim.x * blockDim.x) {
         const int q4 = (int)(i % kq);
-        int64_t m = i / kq;
+        IDX m = i / kq;
         const int yy = (int)(m % p.wo); m /= p.wo;
         const int xx = (int)(m % p.ho); const int nn = (int)(m / p.ho);
         const int h0 = xx * p.vstr - p.vpad, w0 = yy * p.hstr - p.hpad;
@@ -333,6 +339,14 @@ struct TcParams {
 #ifdef B2C_TC_DEV
     int dbg;                   // development build only: 2 = issue one MMA of three, 4 = transform warps do no work
 #endif
+    // Balanced mode (FWD only): the (tile, k-block) work units are cut into equal contiguous ranges, one per CTA,
+    // so a tile may be shared by consecutive CTAs.  The CTA that starts a tile owns it; the others store their
+    // partial tile in `sk_partial` (slot = CTA index, [BN/4][128 rows][4] floats) and raise `sk_flags` (4 per slot, one per
+    // drain warp); the owner adds the partials in CTA order and runs the epilogue.
+    int sk;
+    float* sk_partial;
+    int* sk_flags;
+    float* db_partial;         // WGRAD: per-(split, transform warp) channel sums of dy, [splits][4][N], or null
     int tma_store;             // output rows are dense [M][N] (or [split][M][N]): store tiles through the output tensor map
 };
 
@@ -408,7 +422,47 @@ struct TcSmem {
     static_assert(TOTAL <= 232448, "shared memory budget");
 };
 
-template <int MODE, int BN, int STAGES>
+// The sequence of (tile, k-block range) segments one CTA works through; every warp role walks the same sequence.
+// Plain mode: whole tiles blockIdx.x, blockIdx.x + gridDim.x, ...  Balanced mode: the contiguous unit range
+// [total * b / G, total * (b + 1) / G) of CTA b, unit = tile * kblocks + kb.
+struct TileWalk {
+    int tile, kb_b, kb_e;
+    int next_tile, total_tiles, kblocks;
+    long long u, u_end;
+    __device__ __forceinline__ static long long range_begin(long long total, int cta, int ctas) { return total * cta / ctas; }
+    __device__ __forceinline__ void init(int total_tiles_, int kblocks_) {
+        total_tiles = total_tiles_; kblocks = kblocks_; next_tile = blockIdx.x;
+        const long long total = (long long)total_tiles_ * kblocks_;
+        u = range_begin(total, blockIdx.x, gridDim.x); u_end = range_begin(total, blockIdx.x + 1, gridDim.x);
+    }
+    template <bool BALANCED> __device__ __forceinline__ bool next() {
+        if (!BALANCED) {
+            if (next_tile >= total_tiles) return false;
+            tile = next_tile; next_tile += gridDim.x; kb_b = 0; kb_e = kblocks;
+            return true;
+        }
+        if (u >= u_end) return false;
+        tile = (int)(u / kblocks);
+        kb_b = (int)(u - (long long)tile * kblocks);
+        const long long rem = u_end - u;
+        kb_e = (long long)kb_b + rem < (long long)kblocks ? kb_b + (int)rem : kblocks;
+        u += kb_e - kb_b;
+        return true;
+    }
+};
+
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_gpu(int* p, int v) {
+    asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Registers are handed out per group of four warps, so the 10 warps are budgeted as 12: 168 registers per thread
+// is the most a launch of this shape gets (200 compiles but is refused at launch).
+template <int MODE, int BN, int STAGES, bool SK>
 __global__ void __launch_bounds__(320, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b0,
                const __grid_constant__ CUtensorMap tmap_b1, const __grid_constant__ CUtensorMap tmap_out, TcParams p)
@@ -432,7 +486,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     TC_PROF_DECL();
     const int mt = (p.M + 127) / 128, nt = (p.N + BN - 1) / BN;
     const int total_tiles = mt * nt * p.splits;
-    const int nchunks = (p.kblocks + TC_CHUNK - 1) / TC_CHUNK;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&xform_bar[s], 4); mbar_init(&empty_bar[s], 1); }
@@ -453,7 +506,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         // the barrier and issues the boxes of the k-block.
         int it = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        TileWalk w;
+        w.init(total_tiles, p.kblocks);
+        while (ok && w.template next<SK>()) {
+            const int tile = w.tile;
             const int ni = tile % nt, rest = tile / nt, mi = rest % mt, z = rest / mt;
             const int m0 = mi * 128, n0 = ni * BN;
             int img = 0, base_w = 0, base_h = 0;
@@ -483,7 +539,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 for (int j = 0; j < BN / 32; j++) if (n0 + 32 * j < p.N) boxes++;
             }
             const int pix_begin = (MODE == TCM_WGRAD) ? z * p.kblocks * 32 : 0;
-            for (int kb = 0; kb < p.kblocks; kb++, it++) {
+            for (int kb = w.kb_b; kb < w.kb_e; kb++, it++) {
                 const int s = it % STAGES, use = it / STAGES;
                 TC_PROF_T0();
                 bool good = true;
@@ -545,12 +601,14 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             constexpr uint64_t KADV = (MODE == TCM_WGRAD) ? (1024 >> 4) : (32 >> 4);
             bool ok = true;
             int it = 0, gc = 0;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                for (int kb = 0; kb < p.kblocks && ok; kb++, it++) {
+            TileWalk w;
+            w.init(total_tiles, p.kblocks);
+            while (ok && w.template next<SK>()) {
+                for (int kb = w.kb_b; kb < w.kb_e && ok; kb++, it++) {
                     const int s = it % STAGES, use = it / STAGES;
                     const int b = gc & 1;
-                    const bool chunk_start = (kb % TC_CHUNK) == 0;
-                    const bool chunk_end = (kb % TC_CHUNK) == TC_CHUNK - 1 || kb == p.kblocks - 1;
+                    const bool chunk_start = ((kb - w.kb_b) % TC_CHUNK) == 0;
+                    const bool chunk_end = ((kb - w.kb_b) % TC_CHUNK) == TC_CHUNK - 1 || kb == w.kb_e - 1;
                     TC_PROF_T0();
                     if (chunk_start && gc >= 2)
                         ok = mbar_wait(&tempty_bar[b], ((gc >> 1) - 1) & 1, abort_flag, &g_tc_status, TC_ERR_TEMPTY);
@@ -604,8 +662,16 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const int t = threadIdx.x - 64;              // 0..127
         int it = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-            for (int kb = 0; kb < p.kblocks; kb++, it++) {
+        TileWalk w;
+        w.init(total_tiles, p.kblocks);
+        while (ok && w.template next<SK>()) {
+            // WGRAD: the tiles of the first row block also sum their dy tile over the pixels (the bias gradient);
+            // a thread meets the same four channels of each 32-channel box in every k-block (see below)
+            float4 dbacc[B_VEC / 2 + 1];
+            const bool do_db = MODE == TCM_WGRAD && p.db_partial != nullptr && (w.tile / nt) % mt == 0;
+#pragma unroll
+            for (int i = 0; i < B_VEC / 2; i++) dbacc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int kb = w.kb_b; kb < w.kb_e; kb++, it++) {
                 const int s = it % STAGES, use = it / STAGES;
                 TC_PROF_T0();
                 if (!mbar_wait(&full_bar[s], use & 1, abort_flag, &g_tc_status, TC_ERR_FULL)) { ok = false; break; }
@@ -642,6 +708,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll
                     for (int i = 0; i < B_VEC; i++) {
                         const float4 q = b_hi[t + i * 128];
+                        if (do_db) { dbacc[i >> 1].x += q.x; dbacc[i >> 1].y += q.y; dbacc[i >> 1].z += q.z; dbacc[i >> 1].w += q.w; }
                         float4 l;
                         l.x = q.x - __uint_as_float(__float_as_uint(q.x) & 0xFFFFE000u);
                         l.y = q.y - __uint_as_float(__float_as_uint(q.y) & 0xFFFFE000u);
@@ -657,6 +724,27 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 if (lane == 0) mbar_arrive(&xform_bar[s]);
                 if (t == 0) TC_PROF_ADD(6);    // transform: work
             }
+            if (MODE == TCM_WGRAD && do_db && ok) {
+                // Float4 number t + 128 i of the B region is box i/2, pixel row t/8 + 16 (i & 1), 16-byte chunk t & 7.
+                // The box layout XORs the 32-byte atom index (chunk >> 1) with (row & 3), so the lane's channels are
+                // chunk ((c >> 1) ^ rr) * 2 + (c & 1) with c = lane & 7, rr = (lane >> 3) & 3: the four lanes that hold
+                // one chunk differ by lane ^ (m << 3 | m << 1), m = 1..3.  After the two exchange steps lanes 0-7
+                // (rr = 0: chunk = c) hold the warp's sums over its 8 pixel rows of every k-block.
+                const int ni = w.tile % nt, z = (w.tile / nt) / mt;
+#pragma unroll
+                for (int bx = 0; bx < B_VEC / 2; bx++) {
+                    float4 v = dbacc[bx];
+#pragma unroll
+                    for (int m = 1; m <= 2; m <<= 1) {
+                        const int mask = (m << 3) | (m << 1);
+                        v.x += __shfl_xor_sync(0xffffffffu, v.x, mask); v.y += __shfl_xor_sync(0xffffffffu, v.y, mask);
+                        v.z += __shfl_xor_sync(0xffffffffu, v.z, mask); v.w += __shfl_xor_sync(0xffffffffu, v.w, mask);
+                    }
+                    const int n = ni * BN + bx * 32;
+                    if (lane < 8 && n < p.N)
+                        *reinterpret_cast<float4*>(p.db_partial + ((size_t)z * 4 + (warp - 2)) * p.N + n + lane * 4) = v;
+                }
+            }
         }
     } else {
         // ---------------- drain of the partial sums, then epilogue ----------------
@@ -666,9 +754,13 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const int quad = warp & 3;                       // TMEM lane quadrant this warp may read
         bool ok = true;
         int gc = 0, ecount = 0;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        TileWalk w;
+        w.init(total_tiles, p.kblocks);
+        while (ok && w.template next<SK>()) {
+            const int tile = w.tile;
             const int ni = tile % nt, rest = tile / nt, mi = rest % mt, z = rest / mt;
             const int m0 = mi * 128, n0 = ni * BN;
+            const int nchunks = (w.kb_e - w.kb_b + TC_CHUNK - 1) / TC_CHUNK;
             float acc[BN];
             for (int c = 0; c < nchunks && ok; c++, gc++) {
                 const int b = gc & 1;
@@ -697,6 +789,50 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&tempty_bar[b]);
                 if (threadIdx.x == 192) TC_PROF_ADD(8);    // drain: TMEM load + add
+            }
+            if (SK && ok) {
+                const int row = quad * 32 + lane;
+                if (w.kb_b > 0) {
+                    // a later part of a tile another CTA started: hand the partial tile over, no epilogue
+                    float4* slot = reinterpret_cast<float4*>(p.sk_partial + (size_t)blockIdx.x * (128 * BN)) + row;
+#pragma unroll
+                    for (int j = 0; j < BN; j += 4) slot[(j >> 2) * 128] = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+                    __threadfence();
+                    __syncwarp();
+                    if (lane == 0) st_release_gpu(&p.sk_flags[blockIdx.x * 4 + quad], 1);
+                    continue;
+                }
+                if (w.kb_e < p.kblocks) {
+                    // this CTA started the tile and its range ended inside it: the following CTAs hold the rest
+                    const long long total = (long long)total_tiles * p.kblocks;
+                    const long long tile_end = (long long)(tile + 1) * p.kblocks;
+                    for (int c2 = blockIdx.x + 1; c2 < (int)gridDim.x && ok; c2++) {
+                        if (TileWalk::range_begin(total, c2, gridDim.x) >= tile_end) break;
+                        int got = 1;
+                        if (lane == 0) {
+                            const int* flag = &p.sk_flags[c2 * 4 + quad];
+                            long long t0 = 0;
+                            uint32_t tries = 0;
+                            while (ld_acquire_gpu(flag) == 0) {
+                                if ((++tries & 15u) == 0) {
+                                    const long long now = clock64();
+                                    if (*abort_flag) { got = 0; break; }
+                                    if (t0 == 0) t0 = now;
+                                    else if (now - t0 > TC_WAIT_CYCLES) { *abort_flag = 1; atomicCAS(&g_tc_status, 0, TC_ERR_PARTIAL); got = 0; break; }
+                                }
+                            }
+                        }
+                        got = __shfl_sync(0xffffffffu, got, 0);
+                        if (!got) { ok = false; break; }
+                        __threadfence();
+                        const float4* slot = reinterpret_cast<const float4*>(p.sk_partial + (size_t)c2 * (128 * BN)) + row;
+#pragma unroll
+                        for (int j = 0; j < BN; j += 4) {
+                            const float4 q = __ldcg(slot + (j >> 2) * 128);
+                            acc[j] += q.x; acc[j + 1] += q.y; acc[j + 2] += q.z; acc[j + 3] += q.w;
+                        }
+                    }
+                }
             }
             TC_PROF_T0();
             // Epilogue. A thread owns one output row, but a warp writing 32 different rows per store would
@@ -777,8 +913,17 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 // caller's filter layout.
 struct WgradReduceParams { int M, N, C, S, splits; int64_t sk, sc, sr, ss; int Mreal; };
 
-__global__ void tc_wgrad_reduce_kernel(WgradReduceParams p, const float* __restrict__ partial, float* __restrict__ dw)
+__global__ void tc_wgrad_reduce_kernel(WgradReduceParams p, const float* __restrict__ partial, float* __restrict__ dw,
+                                       const float* __restrict__ db_partial, float* __restrict__ db)
 {
+    // bias gradient: the [splits][4] per-channel sums, added in a fixed order
+    if (db) {
+        for (int n = blockIdx.x * blockDim.x + threadIdx.x; n < p.N; n += gridDim.x * blockDim.x) {
+            float v = 0.f;
+            for (int i = 0; i < p.splits * 4; i++) v += db_partial[(size_t)i * p.N + n];
+            db[n] = v;
+        }
+    }
     int64_t total = (int64_t)p.M * p.N;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         int m = (int)(i / p.N), n = (int)(i - (int64_t)m * p.N);
@@ -890,6 +1035,20 @@ bool tc_supported(const Geo& g, int pass)
     return (g.ci % 32 == 0 || lowered_ok(g)) && g.co % 32 == 0;
 }
 
+static int tc_sm_count()
+{
+    static int sm_count = 0;
+    if (!sm_count) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
+    }
+    return sm_count;
+}
+// Balanced mode scratch: 4 flags per CTA (padded to 4 KB) and one 128 x 128 float partial tile per CTA.
+static size_t sk_flag_bytes() { return align_up((size_t)tc_sm_count() * 4 * sizeof(int), 4096); }
+static size_t sk_bytes() { return sk_flag_bytes() + (size_t)tc_sm_count() * 128 * 128 * sizeof(float); }
+
 static size_t filter_split_bytes(const Geo& g, int pass)
 {
     int rows = pass == B2C_PASS_FPROP ? g.co : g.ci;
@@ -928,29 +1087,24 @@ size_t tc_workspace_bytes(const Geo& g, int pass)
     const bool low = g.ci % 32 != 0;
     const size_t lowered = low ? align_up((size_t)g.M * lowered_kp(g) * sizeof(float), 1024) : 0;
     if (pass == B2C_PASS_FPROP && low) return lowered + 2 * align_up((size_t)g.co * lowered_kp(g) * sizeof(float), 1024) + 2048;
-    if (pass == B2C_PASS_FPROP || pass == B2C_PASS_DGRAD) return 2 * filter_split_bytes(g, pass) + 1024;
+    if (pass == B2C_PASS_FPROP || pass == B2C_PASS_DGRAD) return 2 * filter_split_bytes(g, pass) + 1024 + sk_bytes();
     WgradPlan pl = wgrad_plan(g);
     const size_t Krows = low ? (size_t)lowered_kp(g) : (size_t)g.K;
     return lowered + align_up((size_t)pl.splits * Krows * g.co * sizeof(float), 1024) + 2048 +
-           channel_sum_workspace_bytes(g.n, g.co, g.ho * g.wo);
+           align_up((size_t)pl.splits * 4 * g.co * sizeof(float), 1024);
 }
 
-template <int MODE, int BN, int STAGES>
+template <int MODE, int BN, int STAGES, bool SK>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb0, const CUtensorMap& mb1, const CUtensorMap& mo, const TcParams& p, int splits, cudaStream_t st)
 {
     using L = TcSmem<BN, STAGES>;
     static bool attr_set = false;
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(conv_tc_kernel<MODE, BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+        cudaError_t e = cudaFuncSetAttribute(conv_tc_kernel<MODE, BN, STAGES, SK>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
         if (e != cudaSuccess) { set_cuda_error(e, "cudaFuncSetAttribute(conv_tc_kernel)"); return B2C_ERR_CUDA; }
         attr_set = true;
     }
-    static int sm_count = 0;
-    if (!sm_count) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
-    }
+    const int sm_count = tc_sm_count();
     int64_t tiles = (int64_t)((p.M + 127) / 128) * ((p.N + BN - 1) / BN) * splits;
     if (tiles > 0x7fffffffLL) return B2C_ERR_TOO_LARGE;
     TcParams q = p;
@@ -958,16 +1112,20 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb0, const CUtens
 #ifdef B2C_TC_DEV
     { const char* e = getenv("B2C_TC_DBG"); q.dbg = e ? atoi(e) : 0; }
 #endif
-    const int grid = (int)(tiles < sm_count ? tiles : sm_count);     // one persistent CTA per SM
-    conv_tc_kernel<MODE, BN, STAGES><<<grid, 320, L::TOTAL, st>>>(ma, mb0, mb1, mo, q);
+    const int grid = q.sk ? sm_count : (int)(tiles < sm_count ? tiles : sm_count);     // one persistent CTA per SM
+    conv_tc_kernel<MODE, BN, STAGES, SK><<<grid, 320, L::TOTAL, st>>>(ma, mb0, mb1, mo, q);
     return check_launch("conv_tc_kernel");
 }
 
 template <int MODE>
 static int dispatch_tc(int bn, const CUtensorMap& ma, const CUtensorMap& mb0, const CUtensorMap& mb1, const CUtensorMap& mo, const TcParams& p, int splits, cudaStream_t st)
 {
-    if (bn == 64) return launch_tc<MODE, 64, 6>(ma, mb0, mb1, mo, p, splits, st);
-    return launch_tc<MODE, 128, 4>(ma, mb0, mb1, mo, p, splits, st);
+    if (MODE == TCM_FWD && p.sk) {
+        if (bn == 64) return launch_tc<TCM_FWD, 64, 6, true>(ma, mb0, mb1, mo, p, splits, st);
+        return launch_tc<TCM_FWD, 128, 4, true>(ma, mb0, mb1, mo, p, splits, st);
+    }
+    if (bn == 64) return launch_tc<MODE, 64, 6, false>(ma, mb0, mb1, mo, p, splits, st);
+    return launch_tc<MODE, 128, 4, false>(ma, mb0, mb1, mo, p, splits, st);
 }
 
 // Output seen as [planes][rows][cols] floats, box = 32 cols x 32 rows (x 1 plane), 128B swizzle.
@@ -1013,14 +1171,28 @@ static int run_fwd(const FwdLaunch& f, const void* act, const void* w, const Pre
     if (((uintptr_t)act & 15) || ((uintptr_t)out & 15)) return B2C_ERR_MISALIGNED;
     float* w_hi = (float*)base;
     float* w_lo = (float*)(base + fbytes);
+    const int BN = f.N <= 64 ? 64 : 128;
+    // Balanced mode when whole tiles would leave a large part of the last round of the CTA grid idle.
+    int sk = 0;
+    int* sk_flags = (int*)(base + 2 * fbytes);
+    {
+        const int G = tc_sm_count();
+        const int64_t tiles = (((int64_t)f.n * f.P * f.Q + 127) / 128) * ((f.N + BN - 1) / BN);
+        const int64_t kblocks = (int64_t)f.kh * f.kw * (f.C / 32);
+        const int64_t rounds = (tiles + G - 1) / G;
+        const bool room = base + 2 * fbytes + sk_bytes() <= (uintptr_t)ws + ws_bytes;
+        // cost in k-block units: whole tiles take rounds x kblocks; balanced ranges take units / G plus the
+        // hand-over of one partial tile (store, flag, load, add: about four k-blocks)
+        const double plain = (double)rounds * (double)kblocks, balanced = (double)(tiles * kblocks) / G + 4.0;
+        if (!filters_ready && room && tiles * kblocks >= 4 * (int64_t)G && balanced < 0.85 * plain) sk = 1;
+    }
     if (!filters_ready) {
         int64_t total = (int64_t)f.N * K;
         int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
-        tc_prep_filter_kernel<<<blocks, 256, 0, st>>>(pp, (const float*)w, w_hi, w_lo);
+        tc_prep_filter_kernel<<<blocks, 256, 0, st>>>(pp, (const float*)w, w_hi, w_lo, sk_flags, sk ? tc_sm_count() * 4 : 0);
         int rc = check_launch("tc_prep_filter_kernel");
         if (rc) return rc;
     }
-    const int BN = f.N <= 64 ? 64 : 128;
     CUtensorMap ma, mbh, mbl;
     if (!make_map_im2col(&ma, act, f.n, f.ah, f.aw, f.C, f.low_h, f.low_w, f.cnt_h, f.cnt_w, f.str_h, f.str_w, 128)) return B2C_ERR_UNSUPPORTED;
     if (!make_map_2d(&mbh, w_hi, f.N, K, BN) || !make_map_2d(&mbl, w_lo, f.N, K, BN)) return B2C_ERR_UNSUPPORTED;
@@ -1035,6 +1207,7 @@ static int run_fwd(const FwdLaunch& f, const void* act, const void* w, const Pre
     if (f.N % 4 == 0 && !(((uintptr_t)p.bias | (uintptr_t)p.mean | (uintptr_t)p.inv_std | (uintptr_t)p.gamma | (uintptr_t)p.beta) & 15))
         p.epi |= TC_EPI_VEC;
     p.out = out; p.o_sn = f.o_sn; p.o_sh = f.o_sh; p.o_sw = f.o_sw;
+    p.sk = sk; p.sk_flags = sk_flags; p.sk_partial = (float*)((uintptr_t)sk_flags + sk_flag_bytes());
     // dense rows (plain fprop / stride-1 dgrad): rows are N floats apart in (n, i, j) order
     const bool dense = f.o_sw == f.N && f.o_sh == (int64_t)f.Q * f.N && f.o_sn == (int64_t)f.P * f.Q * f.N;
     CUtensorMap mo = mbh;
@@ -1052,7 +1225,8 @@ static int launch_lower(const Geo& g, const void* x, float* rows, cudaStream_t s
     LowerParams lp = lower_params(g);
     int64_t total = g.M * (lp.Kp / 4);
     int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-    tc_lower_kernel<<<blocks, 256, 0, st>>>(lp, (const float*)x, (float4*)rows);
+    if (total + (int64_t)blocks * 256 < 0x7fffffffLL) tc_lower_kernel<int><<<blocks, 256, 0, st>>>(lp, (const float*)x, (float4*)rows);
+    else tc_lower_kernel<int64_t><<<blocks, 256, 0, st>>>(lp, (const float*)x, (float4*)rows);
     return check_launch("tc_lower_kernel");
 }
 
@@ -1137,7 +1311,7 @@ int tc_wgrad(const Geo& g, const void* x, const void* dy, void* dw, void* db, vo
     const size_t lbytes = low ? align_up((size_t)g.M * Krows * sizeof(float), 1024) : 0;
     const size_t pbytes = align_up((size_t)pl.splits * Krows * g.co * sizeof(float), 1024);
     uintptr_t base = align_up((uintptr_t)ws, 1024);
-    const size_t cs = channel_sum_workspace_bytes(g.n, g.co, g.ho * g.wo);
+    const size_t cs = align_up((size_t)pl.splits * 4 * g.co * sizeof(float), 1024);
     if (!ws || base + lbytes + pbytes + (db ? cs : 0) > (uintptr_t)ws + ws_bytes) return B2C_ERR_WORKSPACE_TOO_SMALL;
     if (((uintptr_t)x & 15) || ((uintptr_t)dy & 15)) return B2C_ERR_MISALIGNED;
     float* partial = (float*)(base + lbytes);
@@ -1163,6 +1337,7 @@ int tc_wgrad(const Geo& g, const void* x, const void* dy, void* dw, void* db, vo
     p.M = Krows; p.N = g.co; p.P = g.ho; p.Q = g.wo; p.kblocks = pl.kblocks;
     p.Mpix = (int)g.M;
     p.out = partial;
+    p.db_partial = db ? (float*)(base + lbytes + pbytes) : nullptr;
     CUtensorMap mo = mb;
     p.tma_store = make_map_out(&mo, partial, (uint64_t)pl.splits, (uint64_t)Krows, (uint64_t)g.co) ? 1 : 0;
     int rc = dispatch_tc<TCM_WGRAD>(pl.bn, ma, mb, mb, mo, p, pl.splits, st);
@@ -1171,10 +1346,8 @@ int tc_wgrad(const Geo& g, const void* x, const void* dy, void* dw, void* db, vo
     WgradReduceParams rp{Krows, g.co, g.ci, g.kw, pl.splits, wsd.sk, wsd.sc, wsd.sr, wsd.ss, (int)g.K};
     int64_t total = (int64_t)Krows * g.co;
     int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
-    tc_wgrad_reduce_kernel<<<blocks, 256, 0, st>>>(rp, partial, (float*)dw);
-    rc = check_launch("tc_wgrad_reduce_kernel");
-    if (rc || !db) return rc;
-    return channel_sum(B2C_F32, B2C_LAYOUT_NHWC, g.n, g.co, g.ho * g.wo, dy, db, (void*)(base + lbytes + pbytes), cs, st);
+    tc_wgrad_reduce_kernel<<<blocks, 256, 0, st>>>(rp, partial, (float*)dw, p.db_partial, (float*)db);
+    return check_launch("tc_wgrad_reduce_kernel");
 }
 
 #ifdef B2C_TC_PROFILE

@@ -81,6 +81,10 @@ PARITY_SHAPES = {
     "ragged_everything": co.Geom(3, 13, 11, 7, 5, 3, 2, 1, 0, 2, 1, 1, 1),
     "single_pixel": co.Geom(1, 1, 1, 1, 1, 1, 1, 0, 0, 1, 1),
     "pad_larger_than_input": co.Geom(1, 2, 2, 3, 2, 3, 3, 2, 2, 1, 1),
+    # tile counts that do not fill the CTA grid evenly: the tensor-core kernel balances (tile, k-block) units over
+    # the CTAs and tiles are shared by 2 (first case) or about 6 (second case) consecutive CTAs
+    "balanced_160_tiles_9_kblocks": co.Geom(5, 64, 64, 32, 128, 3, 3, 1, 1, 1, 1),
+    "balanced_50_tiles_72_kblocks": co.Geom(16, 14, 14, 256, 256, 3, 3, 1, 1, 1, 1),
 }
 
 
