@@ -15,6 +15,7 @@ namespace b2c {
 template <typename F>
 __global__ void reduce2_nhwc_kernel(F f, double* __restrict__ partial, int64_t rows, int c)
 {
+    pdl_prologue();
     __shared__ double s0[8][33], s1[8][33];
     int ch = blockIdx.x * 32 + threadIdx.x;
     int64_t per = (rows + gridDim.y - 1) / gridDim.y;
@@ -35,6 +36,7 @@ __global__ void reduce2_nhwc_kernel(F f, double* __restrict__ partial, int64_t r
 template <typename F>
 __global__ void reduce2_nchw_kernel(F f, double* __restrict__ partial, int n, int c, int hw)
 {
+    pdl_prologue();
     __shared__ double s0[256], s1[256];
     int ch = blockIdx.x;
     int64_t total = (int64_t)n * hw;
@@ -65,10 +67,10 @@ static int launch_reduce2(F f, double* partial, int layout, int n, int c, int hw
     if (chunks < 1) chunks = 1;
     if (layout == B2C_LAYOUT_NHWC) {
         dim3 grid((c + 31) / 32, chunks), block(32, 8);
-        reduce2_nhwc_kernel<F><<<grid, block, 0, st>>>(f, partial, rows, c);
+        launch_pdl(reduce2_nhwc_kernel<F>, grid, block, 0, st, f, partial, rows, c);
     } else {
         dim3 grid(c, chunks);
-        reduce2_nchw_kernel<F><<<grid, 256, 0, st>>>(f, partial, n, c, hw);
+        launch_pdl(reduce2_nchw_kernel<F>, grid, 256, 0, st, f, partial, n, c, hw);
     }
     return check_launch("reduce2");
 }
@@ -92,6 +94,7 @@ __global__ void bn_stats_final_kernel(const double* __restrict__ partial, int ch
                                       double momentum, double eps, T* running_mean, T* running_var,
                                       T* save_mean, T* save_inv_std)
 {
+    pdl_prologue();
     int ch = blockIdx.x * blockDim.x + threadIdx.x;
     if (ch >= c) return;
     double s = 0.0, ss = 0.0;
@@ -110,6 +113,7 @@ __global__ void bn_apply_kernel(const T* __restrict__ x, T* __restrict__ y, cons
                                 const T* __restrict__ inv_std, const T* __restrict__ gamma, const T* __restrict__ beta,
                                 int64_t total, int c, int hw, int nchw, int relu, int ref_order)
 {
+    pdl_prologue();
     int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
         int ch = channel_of(i, c, hw, nchw);
@@ -133,6 +137,7 @@ template <typename T> struct BnBwdF {
 template <typename T>
 __global__ void bn_bwd_final_kernel(const double* __restrict__ partial, int chunks, int c, T* dgamma, T* dbeta)
 {
+    pdl_prologue();
     int ch = blockIdx.x * blockDim.x + threadIdx.x;
     if (ch >= c) return;
     double s0 = 0.0, s1 = 0.0;
@@ -147,6 +152,7 @@ __global__ void bn_bwd_dx_kernel(const T* __restrict__ x, const T* __restrict__ 
                                  const T* __restrict__ dgamma, const T* __restrict__ dbeta, T* __restrict__ dx,
                                  int64_t total, int c, int hw, int nchw, int relu, T count)
 {
+    pdl_prologue();
     int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
         int ch = channel_of(i, c, hw, nchw);
@@ -189,6 +195,7 @@ static V4Geo v4_geo(int64_t rows, int c, int max_chunks)
 template <typename F>
 __global__ void __launch_bounds__(256) reduce2_v4_kernel(F f, double* __restrict__ partial, V4Geo g)
 {
+    pdl_prologue();
     __shared__ float sm[256][9];
     const int cxi = threadIdx.x % g.cx, rxi = threadIdx.x / g.cx;
     const int grp = blockIdx.x * g.cx + cxi;
@@ -252,6 +259,7 @@ struct BnBwdV4 {
 __global__ void reduce2_final_warp_kernel(const double* __restrict__ partial, int chunks, int c, int mode, double count,
                                           double momentum, double eps, float* out0, float* out1, float* run0, float* run1)
 {
+    pdl_prologue();
     const int ch = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (ch >= c) return;
     double s0 = 0.0, s1 = 0.0;
@@ -284,6 +292,7 @@ __global__ void __launch_bounds__(256) bn_apply_v4_kernel(const float4* __restri
                                                           const float* __restrict__ inv_std, const float* __restrict__ gamma,
                                                           const float* __restrict__ beta, V4Geo g, int relu)
 {
+    pdl_prologue();
     const int cxi = threadIdx.x % g.cx, rxi = threadIdx.x / g.cx;
     const int grp = blockIdx.x * g.cx + cxi;
     const float4 m = *reinterpret_cast<const float4*>(mean + grp * 4), is = *reinterpret_cast<const float4*>(inv_std + grp * 4);
@@ -304,6 +313,7 @@ __global__ void __launch_bounds__(256) bn_bwd_dx_v4_kernel(const float4* __restr
                                                            const float* __restrict__ inv_std, const float* __restrict__ dgamma,
                                                            const float* __restrict__ dbeta, float4* __restrict__ dx, V4Geo g, int relu, float count)
 {
+    pdl_prologue();
     const int cxi = threadIdx.x % g.cx, rxi = threadIdx.x / g.cx;
     const int grp = blockIdx.x * g.cx + cxi;
     const float4 m = *reinterpret_cast<const float4*>(mean + grp * 4), is = *reinterpret_cast<const float4*>(inv_std + grp * 4);
@@ -337,7 +347,7 @@ static V4Geo v4_apply_geo(int64_t rows, int c)
 static int final_warp(const double* partial, int chunks, int c, int mode, double count, double momentum, double eps,
                       float* o0, float* o1, float* r0, float* r1, cudaStream_t st)
 {
-    reduce2_final_warp_kernel<<<(c * 32 + 255) / 256, 256, 0, st>>>(partial, chunks, c, mode, count, momentum, eps, o0, o1, r0, r1);
+    launch_pdl(reduce2_final_warp_kernel, (c * 32 + 255) / 256, 256, 0, st, partial, chunks, c, mode, count, momentum, eps, o0, o1, r0, r1);
     return check_launch("reduce2_final_warp");
 }
 
@@ -349,7 +359,7 @@ int channel_sum_v4(int n, int c, int hw, const void* src, void* dst, void* ws, s
     if (max_chunks < 1) return 1;
     V4Geo g = v4_geo((int64_t)n * hw, c, max_chunks);
     SumV4 f{(const float4*)src};
-    reduce2_v4_kernel<SumV4><<<dim3(g.gx, g.chunks), 256, 0, st>>>(f, (double*)ws, g);
+    launch_pdl(reduce2_v4_kernel<SumV4>, dim3(g.gx, g.chunks), 256, 0, st, f, (double*)ws, g);
     int rc = check_launch("reduce2_v4(sum)"); if (rc) return rc;
     return final_warp((const double*)ws, g.chunks, c, 2, 1.0, 0.0, 0.0, (float*)dst, nullptr, nullptr, nullptr, st);
 }
@@ -365,12 +375,12 @@ static int bn_train_forward_t(int layout, int n, int c, int hw, const T* x, cons
         int max_chunks = (int)(scratch_bytes / ((size_t)2 * c * sizeof(double)));
         V4Geo g = v4_geo((int64_t)n * hw, c, max_chunks);
         StatV4 f{(const float4*)x};
-        reduce2_v4_kernel<StatV4><<<dim3(g.gx, g.chunks), 256, 0, st>>>(f, scratch, g);
+        launch_pdl(reduce2_v4_kernel<StatV4>, dim3(g.gx, g.chunks), 256, 0, st, f, scratch, g);
         int rc = check_launch("reduce2_v4(stats)"); if (rc) return rc;
         rc = final_warp(scratch, g.chunks, c, 0, (double)n * hw, momentum, eps, (float*)sm, (float*)si, (float*)rm, (float*)rv, st);
         if (rc) return rc;
         V4Geo ga = v4_apply_geo((int64_t)n * hw, c);
-        bn_apply_v4_kernel<<<dim3(ga.gx, ga.chunks), 256, 0, st>>>((const float4*)x, (float4*)y, (const float*)sm, (const float*)si,
+        launch_pdl(bn_apply_v4_kernel, dim3(ga.gx, ga.chunks), 256, 0, st, (const float4*)x, (float4*)y, (const float*)sm, (const float*)si,
                                                                   (const float*)gamma, (const float*)beta, ga, relu);
         return check_launch("bn_apply_v4");
     }
@@ -378,10 +388,10 @@ static int bn_train_forward_t(int layout, int n, int c, int hw, const T* x, cons
     StatF<T> f{x};
     int rc = launch_reduce2(f, scratch, layout, n, c, hw, chunks, st);
     if (rc) return rc;
-    bn_stats_final_kernel<T><<<(c + 127) / 128, 128, 0, st>>>(scratch, chunks, c, (double)n * hw, momentum, eps, rm, rv, sm, si);
+    launch_pdl(bn_stats_final_kernel<T>, (c + 127) / 128, 128, 0, st, scratch, chunks, c, (double)n * hw, momentum, eps, rm, rv, sm, si);
     rc = check_launch("bn_stats_final"); if (rc) return rc;
     int64_t total = (int64_t)n * c * hw;
-    bn_apply_kernel<T><<<ew_blocks(total), 256, 0, st>>>(x, y, sm, si, gamma, beta, total, c, hw, layout == B2C_LAYOUT_NCHW, relu, 0);
+    launch_pdl(bn_apply_kernel<T>, ew_blocks(total), 256, 0, st, x, y, sm, si, gamma, beta, total, c, hw, layout == B2C_LAYOUT_NCHW, relu, 0);
     return check_launch("bn_apply");
 }
 
@@ -396,12 +406,12 @@ static int bn_train_backward_t(int layout, int n, int c, int hw, const T* x, con
         int max_chunks = (int)(scratch_bytes / ((size_t)2 * c * sizeof(double)));
         V4Geo g = v4_geo((int64_t)n * hw, c, max_chunks);
         BnBwdV4 f{(const float4*)x, (const float4*)dy, (const float4*)y, (const float*)sm, (const float*)si, relu};
-        reduce2_v4_kernel<BnBwdV4><<<dim3(g.gx, g.chunks), 256, 0, st>>>(f, scratch, g);
+        launch_pdl(reduce2_v4_kernel<BnBwdV4>, dim3(g.gx, g.chunks), 256, 0, st, f, scratch, g);
         int rc = check_launch("reduce2_v4(bn_bwd)"); if (rc) return rc;
         rc = final_warp(scratch, g.chunks, c, 1, 1.0, 0.0, 0.0, (float*)dgamma, (float*)dbeta, nullptr, nullptr, st);
         if (rc || !dx) return rc;
         V4Geo ga = v4_apply_geo((int64_t)n * hw, c);
-        bn_bwd_dx_v4_kernel<<<dim3(ga.gx, ga.chunks), 256, 0, st>>>((const float4*)x, (const float4*)dy, (const float4*)y, (const float*)gamma,
+        launch_pdl(bn_bwd_dx_v4_kernel, dim3(ga.gx, ga.chunks), 256, 0, st, (const float4*)x, (const float4*)dy, (const float4*)y, (const float*)gamma,
                                                                    (const float*)sm, (const float*)si, (const float*)dgamma, (const float*)dbeta,
                                                                    (float4*)dx, ga, relu, (float)((double)n * hw));
         return check_launch("bn_bwd_dx_v4");
@@ -409,11 +419,11 @@ static int bn_train_backward_t(int layout, int n, int c, int hw, const T* x, con
     BnBwdF<T> f{x, dy, y, sm, si, relu};
     int rc = launch_reduce2(f, scratch, layout, n, c, hw, chunks, st);
     if (rc) return rc;
-    bn_bwd_final_kernel<T><<<(c + 127) / 128, 128, 0, st>>>(scratch, chunks, c, dgamma, dbeta);
+    launch_pdl(bn_bwd_final_kernel<T>, (c + 127) / 128, 128, 0, st, scratch, chunks, c, dgamma, dbeta);
     rc = check_launch("bn_bwd_final"); if (rc) return rc;
     if (!dx) return B2C_OK;
     int64_t total = (int64_t)n * c * hw;
-    bn_bwd_dx_kernel<T><<<ew_blocks(total), 256, 0, st>>>(x, dy, y, gamma, sm, si, dgamma, dbeta, dx, total, c, hw,
+    launch_pdl(bn_bwd_dx_kernel<T>, ew_blocks(total), 256, 0, st, x, dy, y, gamma, sm, si, dgamma, dbeta, dx, total, c, hw,
                                                           layout == B2C_LAYOUT_NCHW, relu, (T)((double)n * hw));
     return check_launch("bn_bwd_dx");
 }
@@ -422,22 +432,26 @@ static int bn_train_backward_t(int layout, int n, int c, int hw, const T* x, con
 
 template <typename T> __global__ void relu_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t n)
 {
+    pdl_prologue();
     int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) { T v = x[i]; y[i] = v > T(0) ? v : T(0); }
 }
 template <typename T> __global__ void relu_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ y, T* __restrict__ dx, int64_t n)
 {
+    pdl_prologue();
     int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) dx[i] = y[i] > T(0) ? dy[i] : T(0);
 }
 template <typename T> __global__ void add_kernel(T* __restrict__ acc, const T* __restrict__ o, int64_t n)
 {
+    pdl_prologue();
     int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) acc[i] += o[i];
 }
 // float4 variants for the common aligned float32 case
 __global__ void relu_fwd_f4_kernel(const float4* __restrict__ x, float4* __restrict__ y, int64_t n4)
 {
+    pdl_prologue();
     int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
         float4 v = x[i]; v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f); v.z = fmaxf(v.z, 0.f); v.w = fmaxf(v.w, 0.f); y[i] = v;
@@ -445,6 +459,7 @@ __global__ void relu_fwd_f4_kernel(const float4* __restrict__ x, float4* __restr
 }
 __global__ void relu_bwd_f4_kernel(const float4* __restrict__ dy, const float4* __restrict__ y, float4* __restrict__ dx, int64_t n4)
 {
+    pdl_prologue();
     int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
         float4 g = dy[i], v = y[i];
@@ -454,6 +469,7 @@ __global__ void relu_bwd_f4_kernel(const float4* __restrict__ dy, const float4* 
 }
 __global__ void add_f4_kernel(float4* __restrict__ acc, const float4* __restrict__ o, int64_t n4)
 {
+    pdl_prologue();
     int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
         float4 a = acc[i], b = o[i]; a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w; acc[i] = a;
@@ -468,6 +484,7 @@ template <typename T>
 __global__ void sgd_kernel(T* __restrict__ w, const T* __restrict__ dw, T* __restrict__ v, int64_t n,
                            T lr, T momentum, T decay, int nesterov)
 {
+    pdl_prologue();
     int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
         T g = dw[i];
@@ -490,6 +507,7 @@ struct PoolP {
 template <typename T, bool IS_MAX>
 __global__ void pool_fwd_kernel(PoolP p, const T* __restrict__ x, T* __restrict__ y, int32_t* __restrict__ idx_max, int nchw)
 {
+    pdl_prologue();
     int64_t total = (int64_t)p.n * p.ho * p.wo * p.c;
     int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
@@ -518,6 +536,7 @@ __global__ void pool_fwd_kernel(PoolP p, const T* __restrict__ x, T* __restrict_
 template <typename T, bool IS_MAX>
 __global__ void pool_bwd_kernel(PoolP p, const T* __restrict__ dy, const int32_t* __restrict__ idx_max, T* __restrict__ dx, int nchw)
 {
+    pdl_prologue();
     int64_t total = (int64_t)p.n * p.h * p.w * p.c;
     int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
@@ -554,6 +573,7 @@ __global__ void pool_bwd_kernel(PoolP p, const T* __restrict__ dy, const int32_t
 template <bool IS_MAX>
 __global__ void __launch_bounds__(256) pool_fwd_v4_kernel(PoolP p, const float4* __restrict__ x, float4* __restrict__ y, int4* __restrict__ idx_max)
 {
+    pdl_prologue();
     const int c4 = p.c / 4;
     const int64_t total = (int64_t)p.n * p.ho * p.wo * c4;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -587,6 +607,7 @@ __global__ void __launch_bounds__(256) pool_fwd_v4_kernel(PoolP p, const float4*
 template <bool IS_MAX>
 __global__ void __launch_bounds__(256) pool_bwd_v4_kernel(PoolP p, const float4* __restrict__ dy, const int4* __restrict__ idx_max, float4* __restrict__ dx)
 {
+    pdl_prologue();
     const int c4 = p.c / 4;
     const int64_t total = (int64_t)p.n * p.h * p.w * c4;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -629,6 +650,7 @@ __global__ void __launch_bounds__(256) pool_bwd_v4_kernel(PoolP p, const float4*
 // out = max(a + b, 0)  (residual sum followed by ReLU in one pass)
 __global__ void add_relu_f4_kernel(const float4* __restrict__ a, const float4* __restrict__ b, float4* __restrict__ out, int64_t n4)
 {
+    pdl_prologue();
     int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
         float4 u = a[i], v = b[i];
@@ -637,6 +659,7 @@ __global__ void add_relu_f4_kernel(const float4* __restrict__ a, const float4* _
 }
 template <typename T> __global__ void add_relu_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, int64_t n)
 {
+    pdl_prologue();
     int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) { T v = a[i] + b[i]; out[i] = v > T(0) ? v : T(0); }
 }
@@ -658,6 +681,7 @@ template <typename T> __device__ T block_reduce(T v, T* sm, bool is_max)
 template <typename T>
 __global__ void softmax_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, int cols)
 {
+    pdl_prologue();
     __shared__ T sm[256];
     const T* xr = x + (int64_t)blockIdx.x * cols; T* yr = y + (int64_t)blockIdx.x * cols;
     T mx = sizeof(T) == 4 ? (T)(-FLT_MAX) : (T)(-DBL_MAX);
@@ -672,6 +696,7 @@ __global__ void softmax_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, i
 template <typename T>
 __global__ void softmax_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ y, T* __restrict__ dx, int cols)
 {
+    pdl_prologue();
     __shared__ T sm[256];
     const T* dr = dy + (int64_t)blockIdx.x * cols; const T* yr = y + (int64_t)blockIdx.x * cols; T* xr = dx + (int64_t)blockIdx.x * cols;
     T s = T(0);
@@ -684,6 +709,7 @@ template <typename T>
 __global__ void cce_kernel(const T* __restrict__ probs, const int32_t* __restrict__ labels, int cols, int global_batch,
                            T eps, T* __restrict__ row_loss, int32_t* __restrict__ hit, T* __restrict__ dx)
 {
+    pdl_prologue();
     __shared__ T smv[256]; __shared__ int smi[256];
     const T* pr = probs + (int64_t)blockIdx.x * cols; T* xr = dx + (int64_t)blockIdx.x * cols;
     int label = labels[blockIdx.x];
@@ -827,15 +853,15 @@ extern "C" int b2c_bn_inference(int dtype, int layout, int n, int c, int hw, con
     int64_t total = (int64_t)n * c * hw;
     if (v4_ok(dtype, layout, c, x, y, x)) {
         V4Geo ga = v4_apply_geo((int64_t)n * hw, c);
-        bn_apply_v4_kernel<<<dim3(ga.gx, ga.chunks), 256, 0, st>>>((const float4*)x, (float4*)y, (const float*)mean, (const float*)inv_std,
+        launch_pdl(bn_apply_v4_kernel, dim3(ga.gx, ga.chunks), 256, 0, st, (const float4*)x, (float4*)y, (const float*)mean, (const float*)inv_std,
                                                                   (const float*)gamma, (const float*)beta, ga, relu);
         return check_launch("bn_inference_v4");
     }
     if (dtype == B2C_F32)
-        bn_apply_kernel<float><<<ew_blocks(total), 256, 0, st>>>((const float*)x, (float*)y, (const float*)mean, (const float*)inv_std,
+        launch_pdl(bn_apply_kernel<float>, ew_blocks(total), 256, 0, st, (const float*)x, (float*)y, (const float*)mean, (const float*)inv_std,
                                                                 (const float*)gamma, (const float*)beta, total, c, hw, layout == B2C_LAYOUT_NCHW, relu, 1);
     else
-        bn_apply_kernel<double><<<ew_blocks(total), 256, 0, st>>>((const double*)x, (double*)y, (const double*)mean, (const double*)inv_std,
+        launch_pdl(bn_apply_kernel<double>, ew_blocks(total), 256, 0, st, (const double*)x, (double*)y, (const double*)mean, (const double*)inv_std,
                                                                  (const double*)gamma, (const double*)beta, total, c, hw, layout == B2C_LAYOUT_NCHW, relu, 1);
     return check_launch("bn_inference");
 }
@@ -848,9 +874,9 @@ extern "C" int b2c_relu_forward(int dtype, int64_t count, const void* x, void* y
     if (count == 0) return B2C_OK;
     cudaStream_t st = (cudaStream_t)stream;
     if (dtype == B2C_F32) {
-        if (f4_ok(count, x, y, y)) relu_fwd_f4_kernel<<<ew_blocks(count / 4), 256, 0, st>>>((const float4*)x, (float4*)y, count / 4);
-        else relu_fwd_kernel<float><<<ew_blocks(count), 256, 0, st>>>((const float*)x, (float*)y, count);
-    } else relu_fwd_kernel<double><<<ew_blocks(count), 256, 0, st>>>((const double*)x, (double*)y, count);
+        if (f4_ok(count, x, y, y)) launch_pdl(relu_fwd_f4_kernel, ew_blocks(count / 4), 256, 0, st, (const float4*)x, (float4*)y, count / 4);
+        else launch_pdl(relu_fwd_kernel<float>, ew_blocks(count), 256, 0, st, (const float*)x, (float*)y, count);
+    } else launch_pdl(relu_fwd_kernel<double>, ew_blocks(count), 256, 0, st, (const double*)x, (double*)y, count);
     return check_launch("relu_forward");
 }
 
@@ -862,9 +888,9 @@ extern "C" int b2c_relu_backward(int dtype, int64_t count, const void* dy, const
     if (count == 0) return B2C_OK;
     cudaStream_t st = (cudaStream_t)stream;
     if (dtype == B2C_F32) {
-        if (f4_ok(count, dy, y, dx)) relu_bwd_f4_kernel<<<ew_blocks(count / 4), 256, 0, st>>>((const float4*)dy, (const float4*)y, (float4*)dx, count / 4);
-        else relu_bwd_kernel<float><<<ew_blocks(count), 256, 0, st>>>((const float*)dy, (const float*)y, (float*)dx, count);
-    } else relu_bwd_kernel<double><<<ew_blocks(count), 256, 0, st>>>((const double*)dy, (const double*)y, (double*)dx, count);
+        if (f4_ok(count, dy, y, dx)) launch_pdl(relu_bwd_f4_kernel, ew_blocks(count / 4), 256, 0, st, (const float4*)dy, (const float4*)y, (float4*)dx, count / 4);
+        else launch_pdl(relu_bwd_kernel<float>, ew_blocks(count), 256, 0, st, (const float*)dy, (const float*)y, (float*)dx, count);
+    } else launch_pdl(relu_bwd_kernel<double>, ew_blocks(count), 256, 0, st, (const double*)dy, (const double*)y, (double*)dx, count);
     return check_launch("relu_backward");
 }
 
@@ -876,9 +902,9 @@ extern "C" int b2c_add_inplace(int dtype, int64_t count, void* acc, const void* 
     if (count == 0) return B2C_OK;
     cudaStream_t st = (cudaStream_t)stream;
     if (dtype == B2C_F32) {
-        if (f4_ok(count, acc, other, acc)) add_f4_kernel<<<ew_blocks(count / 4), 256, 0, st>>>((float4*)acc, (const float4*)other, count / 4);
-        else add_kernel<float><<<ew_blocks(count), 256, 0, st>>>((float*)acc, (const float*)other, count);
-    } else add_kernel<double><<<ew_blocks(count), 256, 0, st>>>((double*)acc, (const double*)other, count);
+        if (f4_ok(count, acc, other, acc)) launch_pdl(add_f4_kernel, ew_blocks(count / 4), 256, 0, st, (float4*)acc, (const float4*)other, count / 4);
+        else launch_pdl(add_kernel<float>, ew_blocks(count), 256, 0, st, (float*)acc, (const float*)other, count);
+    } else launch_pdl(add_kernel<double>, ew_blocks(count), 256, 0, st, (double*)acc, (const double*)other, count);
     return check_launch("add_inplace");
 }
 
@@ -890,9 +916,9 @@ extern "C" int b2c_add_relu(int dtype, int64_t count, const void* a, const void*
     if (count == 0) return B2C_OK;
     cudaStream_t st = (cudaStream_t)stream;
     if (dtype == B2C_F32) {
-        if (f4_ok(count, a, b, out)) add_relu_f4_kernel<<<ew_blocks(count / 4), 256, 0, st>>>((const float4*)a, (const float4*)b, (float4*)out, count / 4);
-        else add_relu_kernel<float><<<ew_blocks(count), 256, 0, st>>>((const float*)a, (const float*)b, (float*)out, count);
-    } else add_relu_kernel<double><<<ew_blocks(count), 256, 0, st>>>((const double*)a, (const double*)b, (double*)out, count);
+        if (f4_ok(count, a, b, out)) launch_pdl(add_relu_f4_kernel, ew_blocks(count / 4), 256, 0, st, (const float4*)a, (const float4*)b, (float4*)out, count / 4);
+        else launch_pdl(add_relu_kernel<float>, ew_blocks(count), 256, 0, st, (const float*)a, (const float*)b, (float*)out, count);
+    } else launch_pdl(add_relu_kernel<double>, ew_blocks(count), 256, 0, st, (const double*)a, (const double*)b, (double*)out, count);
     return check_launch("add_relu");
 }
 
@@ -920,16 +946,16 @@ extern "C" int b2c_pool_forward(int dtype, int layout, int is_max, int n, int h,
     cudaStream_t st = (cudaStream_t)stream;
     int64_t total = (int64_t)n * p.ho * p.wo * c; int nchw = layout == B2C_LAYOUT_NCHW;
     if (dtype == B2C_F32 && !nchw && c % 4 == 0 && (((uintptr_t)x | (uintptr_t)y | (uintptr_t)idx_max) & 15) == 0) {
-        if (is_max) pool_fwd_v4_kernel<true><<<ew_blocks(total / 4), 256, 0, st>>>(p, (const float4*)x, (float4*)y, (int4*)idx_max);
-        else pool_fwd_v4_kernel<false><<<ew_blocks(total / 4), 256, 0, st>>>(p, (const float4*)x, (float4*)y, (int4*)idx_max);
+        if (is_max) launch_pdl(pool_fwd_v4_kernel<true>, ew_blocks(total / 4), 256, 0, st, p, (const float4*)x, (float4*)y, (int4*)idx_max);
+        else launch_pdl(pool_fwd_v4_kernel<false>, ew_blocks(total / 4), 256, 0, st, p, (const float4*)x, (float4*)y, (int4*)idx_max);
         return check_launch("pool_forward_v4");
     }
     if (dtype == B2C_F32) {
-        if (is_max) pool_fwd_kernel<float, true><<<ew_blocks(total), 256, 0, st>>>(p, (const float*)x, (float*)y, idx_max, nchw);
-        else pool_fwd_kernel<float, false><<<ew_blocks(total), 256, 0, st>>>(p, (const float*)x, (float*)y, idx_max, nchw);
+        if (is_max) launch_pdl(pool_fwd_kernel<float, true>, ew_blocks(total), 256, 0, st, p, (const float*)x, (float*)y, idx_max, nchw);
+        else launch_pdl(pool_fwd_kernel<float, false>, ew_blocks(total), 256, 0, st, p, (const float*)x, (float*)y, idx_max, nchw);
     } else {
-        if (is_max) pool_fwd_kernel<double, true><<<ew_blocks(total), 256, 0, st>>>(p, (const double*)x, (double*)y, idx_max, nchw);
-        else pool_fwd_kernel<double, false><<<ew_blocks(total), 256, 0, st>>>(p, (const double*)x, (double*)y, idx_max, nchw);
+        if (is_max) launch_pdl(pool_fwd_kernel<double, true>, ew_blocks(total), 256, 0, st, p, (const double*)x, (double*)y, idx_max, nchw);
+        else launch_pdl(pool_fwd_kernel<double, false>, ew_blocks(total), 256, 0, st, p, (const double*)x, (double*)y, idx_max, nchw);
     }
     return check_launch("pool_forward");
 }
@@ -944,16 +970,16 @@ extern "C" int b2c_pool_backward(int dtype, int layout, int is_max, int n, int h
     cudaStream_t st = (cudaStream_t)stream;
     int64_t total = (int64_t)n * h * w * c; int nchw = layout == B2C_LAYOUT_NCHW;
     if (dtype == B2C_F32 && !nchw && c % 4 == 0 && (((uintptr_t)dy | (uintptr_t)dx | (uintptr_t)idx_max) & 15) == 0) {
-        if (is_max) pool_bwd_v4_kernel<true><<<ew_blocks(total / 4), 256, 0, st>>>(p, (const float4*)dy, (const int4*)idx_max, (float4*)dx);
-        else pool_bwd_v4_kernel<false><<<ew_blocks(total / 4), 256, 0, st>>>(p, (const float4*)dy, (const int4*)idx_max, (float4*)dx);
+        if (is_max) launch_pdl(pool_bwd_v4_kernel<true>, ew_blocks(total / 4), 256, 0, st, p, (const float4*)dy, (const int4*)idx_max, (float4*)dx);
+        else launch_pdl(pool_bwd_v4_kernel<false>, ew_blocks(total / 4), 256, 0, st, p, (const float4*)dy, (const int4*)idx_max, (float4*)dx);
         return check_launch("pool_backward_v4");
     }
     if (dtype == B2C_F32) {
-        if (is_max) pool_bwd_kernel<float, true><<<ew_blocks(total), 256, 0, st>>>(p, (const float*)dy, idx_max, (float*)dx, nchw);
-        else pool_bwd_kernel<float, false><<<ew_blocks(total), 256, 0, st>>>(p, (const float*)dy, idx_max, (float*)dx, nchw);
+        if (is_max) launch_pdl(pool_bwd_kernel<float, true>, ew_blocks(total), 256, 0, st, p, (const float*)dy, idx_max, (float*)dx, nchw);
+        else launch_pdl(pool_bwd_kernel<float, false>, ew_blocks(total), 256, 0, st, p, (const float*)dy, idx_max, (float*)dx, nchw);
     } else {
-        if (is_max) pool_bwd_kernel<double, true><<<ew_blocks(total), 256, 0, st>>>(p, (const double*)dy, idx_max, (double*)dx, nchw);
-        else pool_bwd_kernel<double, false><<<ew_blocks(total), 256, 0, st>>>(p, (const double*)dy, idx_max, (double*)dx, nchw);
+        if (is_max) launch_pdl(pool_bwd_kernel<double, true>, ew_blocks(total), 256, 0, st, p, (const double*)dy, idx_max, (double*)dx, nchw);
+        else launch_pdl(pool_bwd_kernel<double, false>, ew_blocks(total), 256, 0, st, p, (const double*)dy, idx_max, (double*)dx, nchw);
     }
     return check_launch("pool_backward");
 }
@@ -964,8 +990,8 @@ extern "C" int b2c_softmax_forward(int dtype, int rows, int cols, const void* x,
     if (!x || !y) return B2C_ERR_NULL_POINTER;
     if (rows <= 0 || cols <= 0) return B2C_ERR_BAD_GEOMETRY;
     cudaStream_t st = (cudaStream_t)stream;
-    if (dtype == B2C_F32) softmax_fwd_kernel<float><<<rows, 256, 0, st>>>((const float*)x, (float*)y, cols);
-    else softmax_fwd_kernel<double><<<rows, 256, 0, st>>>((const double*)x, (double*)y, cols);
+    if (dtype == B2C_F32) launch_pdl(softmax_fwd_kernel<float>, rows, 256, 0, st, (const float*)x, (float*)y, cols);
+    else launch_pdl(softmax_fwd_kernel<double>, rows, 256, 0, st, (const double*)x, (double*)y, cols);
     return check_launch("softmax_forward");
 }
 
@@ -975,8 +1001,8 @@ extern "C" int b2c_softmax_backward(int dtype, int rows, int cols, const void* d
     if (!dy || !y || !dx) return B2C_ERR_NULL_POINTER;
     if (rows <= 0 || cols <= 0) return B2C_ERR_BAD_GEOMETRY;
     cudaStream_t st = (cudaStream_t)stream;
-    if (dtype == B2C_F32) softmax_bwd_kernel<float><<<rows, 256, 0, st>>>((const float*)dy, (const float*)y, (float*)dx, cols);
-    else softmax_bwd_kernel<double><<<rows, 256, 0, st>>>((const double*)dy, (const double*)y, (double*)dx, cols);
+    if (dtype == B2C_F32) launch_pdl(softmax_bwd_kernel<float>, rows, 256, 0, st, (const float*)dy, (const float*)y, (float*)dx, cols);
+    else launch_pdl(softmax_bwd_kernel<double>, rows, 256, 0, st, (const double*)dy, (const double*)y, (double*)dx, cols);
     return check_launch("softmax_backward");
 }
 
@@ -987,8 +1013,8 @@ extern "C" int b2c_cce_forward_backward(int dtype, int rows, int cols, const voi
     if (!probs || !labels || !row_loss || !dx) return B2C_ERR_NULL_POINTER;
     if (rows <= 0 || cols <= 0 || global_batch <= 0) return B2C_ERR_BAD_GEOMETRY;
     cudaStream_t st = (cudaStream_t)stream;
-    if (dtype == B2C_F32) cce_kernel<float><<<rows, 256, 0, st>>>((const float*)probs, labels, cols, global_batch, (float)eps, (float*)row_loss, hit, (float*)dx);
-    else cce_kernel<double><<<rows, 256, 0, st>>>((const double*)probs, labels, cols, global_batch, eps, (double*)row_loss, hit, (double*)dx);
+    if (dtype == B2C_F32) launch_pdl(cce_kernel<float>, rows, 256, 0, st, (const float*)probs, labels, cols, global_batch, (float)eps, (float*)row_loss, hit, (float*)dx);
+    else launch_pdl(cce_kernel<double>, rows, 256, 0, st, (const double*)probs, labels, cols, global_batch, eps, (double*)row_loss, hit, (double*)dx);
     return check_launch("cce");
 }
 
@@ -1000,7 +1026,7 @@ extern "C" int b2c_sgd_update(int dtype, int64_t count, void* w, const void* dw,
     if (count < 0) return B2C_ERR_BAD_GEOMETRY;
     if (count == 0) return B2C_OK;
     cudaStream_t st = (cudaStream_t)stream;
-    if (dtype == B2C_F32) sgd_kernel<float><<<ew_blocks(count), 256, 0, st>>>((float*)w, (const float*)dw, (float*)velocity, count, (float)lr, (float)momentum, (float)decay, nesterov);
-    else sgd_kernel<double><<<ew_blocks(count), 256, 0, st>>>((double*)w, (const double*)dw, (double*)velocity, count, lr, momentum, decay, nesterov);
+    if (dtype == B2C_F32) launch_pdl(sgd_kernel<float>, ew_blocks(count), 256, 0, st, (float*)w, (const float*)dw, (float*)velocity, count, (float)lr, (float)momentum, (float)decay, nesterov);
+    else launch_pdl(sgd_kernel<double>, ew_blocks(count), 256, 0, st, (double*)w, (const double*)dw, (double*)velocity, count, lr, momentum, decay, nesterov);
     return check_launch("sgd_update");
 }

@@ -10,6 +10,29 @@ namespace b2c {
 // ---- error plumbing ---------------------------------------------------------------------
 void set_cuda_error(cudaError_t e, const char* where);
 void count_launch();
+// Programmatic dependent launch.  Every kernel of the library begins with pdl_prologue(): it waits until the
+// kernel before it in the stream has completed and its writes are visible, then lets the kernel after it be
+// scheduled early.  launch_pdl() marks the launch as allowed to start while its predecessor drains, so launch
+// latency and the start-up of the next kernel's blocks overlap with the tail of the running one; data is only
+// touched after the wait, so the stream's ordering is unchanged.
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_prologue() { pdl_wait(); pdl_launch_dependents(); }
+
+template <typename... KArgs, typename... Args>
+inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
+
 inline int check_launch(const char* where) {
     count_launch();
     cudaError_t e = cudaGetLastError();

@@ -108,6 +108,7 @@ __global__ void __launch_bounds__(256)
 igemm_kernel(IgemmParams p, const T* __restrict__ A, const T* __restrict__ B, T* __restrict__ C,
              T* __restrict__ partial, Epilogue<T> ep)
 {
+    pdl_prologue();
     constexpr int BM = 128, NT = 256, BK = TileCfg<T>::BK;
     constexpr int A_PER = BM * BK / NT, B_PER = BN * BK / NT;
     constexpr int PADW = 16 / sizeof(T);
@@ -246,6 +247,7 @@ igemm_kernel(IgemmParams p, const T* __restrict__ A, const T* __restrict__ B, T*
 template <typename T, int MODE>
 __global__ void splitk_reduce_kernel(IgemmParams p, const T* __restrict__ partial, T* __restrict__ C, Epilogue<T> ep)
 {
+    pdl_prologue();
     int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     int64_t total = (int64_t)p.M * p.N;
     if (idx >= total) return;
@@ -259,6 +261,7 @@ __global__ void splitk_reduce_kernel(IgemmParams p, const T* __restrict__ partia
 // Index map of the lowering, numbered as the reference numbers rows and columns.
 __global__ void index_map_kernel(IgemmParams p, int64_t* __restrict__ map, int nchw)
 {
+    pdl_prologue();
     int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     int64_t total = (int64_t)p.M * p.K;
     if (idx >= total) return;
@@ -360,14 +363,14 @@ static int launch_igemm(IgemmParams& p, const void* A, const void* B, void* C, v
     dim3 grid((p.M + 127) / 128, (p.N + bn - 1) / bn, p.splits);
     if (grid.y > 65535 || grid.z > 65535) return B2C_ERR_TOO_LARGE;
     if (bn == 64)
-        igemm_kernel<T, MODE, 64, 4><<<grid, 256, 0, st>>>(p, (const T*)A, (const T*)B, (T*)C, (T*)ws, ep);
+        launch_pdl(igemm_kernel<T, MODE, 64, 4>, grid, 256, 0, st, p, (const T*)A, (const T*)B, (T*)C, (T*)ws, ep);
     else
-        igemm_kernel<T, MODE, 128, 8><<<grid, 256, 0, st>>>(p, (const T*)A, (const T*)B, (T*)C, (T*)ws, ep);
+        launch_pdl(igemm_kernel<T, MODE, 128, 8>, grid, 256, 0, st, p, (const T*)A, (const T*)B, (T*)C, (T*)ws, ep);
     int rc = check_launch("igemm_kernel");
     if (rc) return rc;
     if (p.splits > 1) {
         int64_t total = (int64_t)p.M * p.N;
-        splitk_reduce_kernel<T, MODE><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(p, (const T*)ws, (T*)C, ep);
+        launch_pdl(splitk_reduce_kernel<T, MODE>, (unsigned)((total + 255) / 256), 256, 0, st, p, (const T*)ws, (T*)C, ep);
         rc = check_launch("splitk_reduce_kernel");
     }
     return rc;
@@ -421,7 +424,7 @@ int fma_index_map(const Geo& g, int64_t* map, cudaStream_t st)
     p.tap_c_fast = 0;  // the reference numbers taps channel-slowest: col = cc*kh*kw + ii*kw + jj
     int64_t total = (int64_t)p.M * p.K;
     if (total > (int64_t)0x7fffffff * 256) return B2C_ERR_TOO_LARGE;
-    index_map_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(p, map, g.layout == B2C_LAYOUT_NCHW);
+    launch_pdl(index_map_kernel, (unsigned)((total + 255) / 256), 256, 0, st, p, map, g.layout == B2C_LAYOUT_NCHW);
     return check_launch("index_map_kernel");
 }
 
@@ -433,6 +436,7 @@ int fma_index_map(const Geo& g, int64_t* map, cudaStream_t st)
 template <typename T>
 __global__ void channel_sum_nhwc_kernel(const T* __restrict__ src, double* __restrict__ partial, int64_t rows, int c)
 {
+    pdl_prologue();
     __shared__ double sm[8][33];
     int ch = blockIdx.x * 32 + threadIdx.x;
     int64_t per = (rows + gridDim.y - 1) / gridDim.y;
@@ -453,6 +457,7 @@ __global__ void channel_sum_nhwc_kernel(const T* __restrict__ src, double* __res
 template <typename T>
 __global__ void channel_sum_nchw_kernel(const T* __restrict__ src, double* __restrict__ partial, int n, int c, int hw)
 {
+    pdl_prologue();
     __shared__ double sm[256];
     int ch = blockIdx.x;
     int64_t total = (int64_t)n * hw;
@@ -472,6 +477,7 @@ __global__ void channel_sum_nchw_kernel(const T* __restrict__ src, double* __res
 template <typename T>
 __global__ void channel_sum_final_kernel(const double* __restrict__ partial, T* __restrict__ dst, int c, int chunks)
 {
+    pdl_prologue();
     int ch = blockIdx.x * blockDim.x + threadIdx.x;
     if (ch >= c) return;
     double s = 0.0;
@@ -504,18 +510,18 @@ int channel_sum(int dtype, int layout, int n, int c, int hw, const void* src, vo
     if (chunks < 1) chunks = 1;
     if (layout == B2C_LAYOUT_NHWC) {
         dim3 grid((c + 31) / 32, chunks), block(32, 8);
-        if (dtype == B2C_F32) channel_sum_nhwc_kernel<float><<<grid, block, 0, st>>>((const float*)src, partial, rows, c);
-        else channel_sum_nhwc_kernel<double><<<grid, block, 0, st>>>((const double*)src, partial, rows, c);
+        if (dtype == B2C_F32) launch_pdl(channel_sum_nhwc_kernel<float>, grid, block, 0, st, (const float*)src, partial, rows, c);
+        else launch_pdl(channel_sum_nhwc_kernel<double>, grid, block, 0, st, (const double*)src, partial, rows, c);
     } else {
         if (c > 65535 * 32) return B2C_ERR_TOO_LARGE;
         dim3 grid(c, chunks);
-        if (dtype == B2C_F32) channel_sum_nchw_kernel<float><<<grid, 256, 0, st>>>((const float*)src, partial, n, c, hw);
-        else channel_sum_nchw_kernel<double><<<grid, 256, 0, st>>>((const double*)src, partial, n, c, hw);
+        if (dtype == B2C_F32) launch_pdl(channel_sum_nchw_kernel<float>, grid, 256, 0, st, (const float*)src, partial, n, c, hw);
+        else launch_pdl(channel_sum_nchw_kernel<double>, grid, 256, 0, st, (const double*)src, partial, n, c, hw);
     }
     int rc = check_launch("channel_sum");
     if (rc) return rc;
-    if (dtype == B2C_F32) channel_sum_final_kernel<float><<<(c + 255) / 256, 256, 0, st>>>(partial, (float*)dst, c, chunks);
-    else channel_sum_final_kernel<double><<<(c + 255) / 256, 256, 0, st>>>(partial, (double*)dst, c, chunks);
+    if (dtype == B2C_F32) launch_pdl(channel_sum_final_kernel<float>, (c + 255) / 256, 256, 0, st, partial, (float*)dst, c, chunks);
+    else launch_pdl(channel_sum_final_kernel<double>, (c + 255) / 256, 256, 0, st, partial, (double*)dst, c, chunks);
     return check_launch("channel_sum_final");
 }
 

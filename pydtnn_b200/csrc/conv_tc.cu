@@ -242,6 +242,7 @@ struct PrepParams {
 __global__ void tc_prep_filter_kernel(PrepParams p, const float* __restrict__ w, float* __restrict__ hi, float* __restrict__ lo,
                                       int* __restrict__ flags, int nflags)
 {
+    pdl_prologue();
     if (blockIdx.x == 0) for (int i = threadIdx.x; i < nflags; i += blockDim.x) flags[i] = 0;
     int64_t K = (int64_t)p.R * p.S * p.C;
     int64_t total = (int64_t)p.rows * K;
@@ -269,6 +270,7 @@ struct LowerParams { int n, h, w, c, ho, wo, kh, kw, vpad, hpad, vstr, hstr, vdi
 template <typename IDX>
 __global__ void tc_lower_kernel(LowerParams p, const float* __restrict__ x, float4* __restrict__ rows)
 {
+    pdl_prologue();
     // column k -> (row offset, column offset, channel), decoded once per block
     __shared__ int tab_dh[1024], tab_dw[1024], tab_c[1024];
     for (int k = threadIdx.x; k < p.Kp; k += blockDim.x) {
@@ -302,6 +304,7 @@ __global__ void tc_lower_kernel(LowerParams p, const float* __restrict__ x, floa
 __global__ void tc_prep_filter_lowered_kernel(int rows, int K, int Kp, int C, int S, int64_t s_row, int64_t s_c, int64_t s_r,
                                               int64_t s_s, const float* __restrict__ w, float* __restrict__ hi, float* __restrict__ lo)
 {
+    pdl_prologue();
     const int64_t total = (int64_t)rows * Kp;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         const int row = (int)(i / Kp), k = (int)(i - (int64_t)row * Kp);
@@ -467,6 +470,7 @@ __global__ void __launch_bounds__(320, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b0,
                const __grid_constant__ CUtensorMap tmap_b1, const __grid_constant__ CUtensorMap tmap_out, TcParams p)
 {
+    pdl_prologue();
     // Persistent: each CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ... (column tile fastest, so
     // CTAs running at the same time share activation rows in L2).  The smem pipeline and the two TMEM
     // buffers keep running across tile boundaries: the producer prefetches the next tile while the
@@ -495,6 +499,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         fence_proxy_async();
     }
     if (warp == 1) { tmem_alloc(tmem_slot, L::TMEM_COLS); tmem_relinquish(); }
+    // barriers, tensor memory and the abort flag are on-chip state; global memory is first touched below
+    pdl_prologue();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -916,6 +922,7 @@ struct WgradReduceParams { int M, N, C, S, splits; int64_t sk, sc, sr, ss; int M
 __global__ void tc_wgrad_reduce_kernel(WgradReduceParams p, const float* __restrict__ partial, float* __restrict__ dw,
                                        const float* __restrict__ db_partial, float* __restrict__ db)
 {
+    pdl_prologue();
     // bias gradient: the [splits][4] per-channel sums, added in a fixed order
     if (db) {
         for (int n = blockIdx.x * blockDim.x + threadIdx.x; n < p.N; n += gridDim.x * blockDim.x) {
@@ -1113,7 +1120,7 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb0, const CUtens
     { const char* e = getenv("B2C_TC_DBG"); q.dbg = e ? atoi(e) : 0; }
 #endif
     const int grid = q.sk ? sm_count : (int)(tiles < sm_count ? tiles : sm_count);     // one persistent CTA per SM
-    conv_tc_kernel<MODE, BN, STAGES, SK><<<grid, 320, L::TOTAL, st>>>(ma, mb0, mb1, mo, q);
+    launch_pdl(conv_tc_kernel<MODE, BN, STAGES, SK>, grid, 320, L::TOTAL, st, ma, mb0, mb1, mo, q);
     return check_launch("conv_tc_kernel");
 }
 
@@ -1189,7 +1196,7 @@ static int run_fwd(const FwdLaunch& f, const void* act, const void* w, const Pre
     if (!filters_ready) {
         int64_t total = (int64_t)f.N * K;
         int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
-        tc_prep_filter_kernel<<<blocks, 256, 0, st>>>(pp, (const float*)w, w_hi, w_lo, sk_flags, sk ? tc_sm_count() * 4 : 0);
+        launch_pdl(tc_prep_filter_kernel, blocks, 256, 0, st, pp, (const float*)w, w_hi, w_lo, sk_flags, sk ? tc_sm_count() * 4 : 0);
         int rc = check_launch("tc_prep_filter_kernel");
         if (rc) return rc;
     }
@@ -1225,8 +1232,8 @@ static int launch_lower(const Geo& g, const void* x, float* rows, cudaStream_t s
     LowerParams lp = lower_params(g);
     int64_t total = g.M * (lp.Kp / 4);
     int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-    if (total + (int64_t)blocks * 256 < 0x7fffffffLL) tc_lower_kernel<int><<<blocks, 256, 0, st>>>(lp, (const float*)x, (float4*)rows);
-    else tc_lower_kernel<int64_t><<<blocks, 256, 0, st>>>(lp, (const float*)x, (float4*)rows);
+    if (total + (int64_t)blocks * 256 < 0x7fffffffLL) launch_pdl(tc_lower_kernel<int>, blocks, 256, 0, st, lp, (const float*)x, (float4*)rows);
+    else launch_pdl(tc_lower_kernel<int64_t>, blocks, 256, 0, st, lp, (const float*)x, (float4*)rows);
     return check_launch("tc_lower_kernel");
 }
 
@@ -1247,7 +1254,7 @@ int tc_fprop(const Geo& g, const void* x, const void* w, const void* bias, const
         int rc = launch_lower(g, x, rows, st);
         if (rc) return rc;
         int64_t total = (int64_t)g.co * Kp;
-        tc_prep_filter_lowered_kernel<<<(int)((total + 255) / 256), 256, 0, st>>>(g.co, (int)g.K, Kp, g.ci, g.kw, wsd.sk, wsd.sc, wsd.sr,
+        launch_pdl(tc_prep_filter_lowered_kernel, (int)((total + 255) / 256), 256, 0, st, g.co, (int)g.K, Kp, g.ci, g.kw, wsd.sk, wsd.sc, wsd.sr,
                                                                                  wsd.ss, (const float*)w, w_hi, w_lo);
         rc = check_launch("tc_prep_filter_lowered_kernel");
         if (rc) return rc;
@@ -1346,7 +1353,7 @@ int tc_wgrad(const Geo& g, const void* x, const void* dy, void* dw, void* db, vo
     WgradReduceParams rp{Krows, g.co, g.ci, g.kw, pl.splits, wsd.sk, wsd.sc, wsd.sr, wsd.ss, (int)g.K};
     int64_t total = (int64_t)Krows * g.co;
     int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
-    tc_wgrad_reduce_kernel<<<blocks, 256, 0, st>>>(rp, partial, (float*)dw, p.db_partial, (float*)db);
+    launch_pdl(tc_wgrad_reduce_kernel, blocks, 256, 0, st, rp, partial, (float*)dw, p.db_partial, (float*)db);
     return check_launch("tc_wgrad_reduce_kernel");
 }
 
