@@ -266,37 +266,43 @@ __global__ void tc_prep_filter_kernel(PrepParams p, const float* __restrict__ w,
 // ---------------------------------------------------------------------------------------------
 struct LowerParams { int n, h, w, c, ho, wo, kh, kw, vpad, hpad, vstr, hstr, vdil, hdil, K, Kp; };
 
-// IDX = int when the float4 count fits 31 bits (the usual case): the per-element divisions are then 32-bit.
-template <typename IDX>
+// The grid's thread count is a multiple of the float4 count of a row (Kp / 4), so a thread keeps its column
+// group for the whole grid-stride loop: the four (tap, channel) pairs are decoded once into registers and the
+// pixel advances by a constant step, carried through (w, h, n) without divisions.
 __global__ void tc_lower_kernel(LowerParams p, const float* __restrict__ x, float4* __restrict__ rows)
 {
     pdl_prologue();
-    // column k -> (row offset, column offset, channel), decoded once per block
-    __shared__ int tab_dh[1024], tab_dw[1024], tab_c[1024];
-    for (int k = threadIdx.x; k < p.Kp; k += blockDim.x) {
+    const int kq = p.Kp / 4;
+    const int64_t total = (int64_t)p.n * p.ho * p.wo * kq;
+    const int64_t threads = (int64_t)gridDim.x * blockDim.x;          // multiple of kq (see launch_lower)
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int q4 = (int)(i % kq);
+    int dh[4], dwc[4], off[4];
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+        const int k = q4 * 4 + e;
         if (k < p.K) {
             const int c = k % p.c, rs = k / p.c, r = rs / p.kw, sx = rs - r * p.kw;
-            tab_dh[k] = r * p.vdil; tab_dw[k] = sx * p.hdil; tab_c[k] = c;
-        } else { tab_dh[k] = 1 << 28; tab_dw[k] = 0; tab_c[k] = 0; }     // padding column: always out of range
+            dh[e] = r * p.vdil; dwc[e] = sx * p.hdil; off[e] = (dh[e] * p.w + dwc[e]) * p.c + c;
+        } else { dh[e] = 1 << 28; dwc[e] = 0; off[e] = 0; }          // padding column: always out of range
     }
-    __syncthreads();
-    const int kq = p.Kp / 4;
-    const IDX total = (IDX)p.n * p.ho * p.wo * kq;
-    for (IDX i = (IDX)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (IDX)gridDim.x * blockDim.x) {
-        const int q4 = (int)(i % kq);
-        IDX m = i / kq;
-        const int yy = (int)(m % p.wo); m /= p.wo;
-        const int xx = (int)(m % p.ho); const int nn = (int)(m / p.ho);
-        const int h0 = xx * p.vstr - p.vpad, w0 = yy * p.hstr - p.hpad;
-        const float* img = x + (int64_t)nn * p.h * p.w * p.c;
+    int64_t m = i / kq;
+    int ow = (int)(m % p.wo); m /= p.wo;
+    int oh = (int)(m % p.ho); int nn = (int)(m / p.ho);
+    int64_t step = threads / kq;                                     // pixels per grid stride
+    const int s_w = (int)(step % p.wo); step /= p.wo;
+    const int s_h = (int)(step % p.ho); const int s_n = (int)(step / p.ho);
+    for (; i < total; i += threads) {
+        const int h0 = oh * p.vstr - p.vpad, w0 = ow * p.hstr - p.hpad;
+        const float* base = x + (((int64_t)nn * p.h + h0) * p.w + w0) * p.c;
         float v[4];
 #pragma unroll
-        for (int e = 0; e < 4; e++) {
-            const int k = q4 * 4 + e;
-            const int ih = h0 + tab_dh[k], iw = w0 + tab_dw[k];
-            v[e] = ((unsigned)ih < (unsigned)p.h && (unsigned)iw < (unsigned)p.w) ? img[((int64_t)ih * p.w + iw) * p.c + tab_c[k]] : 0.f;
-        }
+        for (int e = 0; e < 4; e++)
+            v[e] = ((unsigned)(h0 + dh[e]) < (unsigned)p.h && (unsigned)(w0 + dwc[e]) < (unsigned)p.w) ? __ldg(base + off[e]) : 0.f;
         rows[i] = make_float4(v[0], v[1], v[2], v[3]);
+        ow += s_w; if (ow >= p.wo) { ow -= p.wo; oh++; }
+        oh += s_h; if (oh >= p.ho) { oh -= p.ho; nn++; }
+        nn += s_n;
     }
 }
 
@@ -1230,10 +1236,15 @@ static LowerParams lower_params(const Geo& g)
 static int launch_lower(const Geo& g, const void* x, float* rows, cudaStream_t st)
 {
     LowerParams lp = lower_params(g);
-    int64_t total = g.M * (lp.Kp / 4);
-    int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-    if (total + (int64_t)blocks * 256 < 0x7fffffffLL) launch_pdl(tc_lower_kernel<int>, blocks, 256, 0, st, lp, (const float*)x, (float4*)rows);
-    else launch_pdl(tc_lower_kernel<int64_t>, blocks, 256, 0, st, lp, (const float*)x, (float4*)rows);
+    const int kq = lp.Kp / 4;
+    int64_t total = g.M * kq;
+    // block count: a multiple of kq / gcd(kq, 256), so that the thread count is a multiple of kq
+    int a = kq, b = 256;
+    while (b) { int t = a % b; a = b; b = t; }
+    const int unit = kq / a;
+    int64_t blocks = (total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16;
+    blocks = (blocks + unit - 1) / unit * unit;
+    launch_pdl(tc_lower_kernel, (unsigned)blocks, 256, 0, st, lp, (const float*)x, (float4*)rows);
     return check_launch("tc_lower_kernel");
 }
 
