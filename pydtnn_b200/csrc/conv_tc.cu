@@ -416,14 +416,14 @@ __device__ __forceinline__ void tc_epilogue_math(const TcParams& p, int nbase, f
 // Shared memory per pipeline stage: the raw A tile (activations), then the hi and lo halves of the B tile.
 // Tensor memory (512 columns): two accumulator buffers of BN columns, then per stage 64 columns holding
 // the hi and lo halves of the A tile (128 rows x 32 k).
-template <int BN, int STAGES>
+template <int BN, int STAGES, int SLABS>
 struct TcSmem {
     static constexpr int A_BYTES = 128 * 128;   // 128 rows x 32 floats (FWD) or 32 pixels x 128 rows (WGRAD)
     static constexpr int B_BYTES = BN * 128;
     static constexpr int STAGE_BYTES = A_BYTES + 2 * B_BYTES;
     static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
     static constexpr int EPI_OFFSET = BAR_OFFSET + 1024;          // barriers and flags live in the first 256 bytes
-    static constexpr int EPI_BYTES = 4 * 2 * 4096;                // per drain warp: two 32 x 32 float staging slabs
+    static constexpr int EPI_BYTES = 4 * SLABS * 4096;            // per drain warp: SLABS 32 x 32 float staging slabs
     static constexpr int TOTAL = EPI_OFFSET + EPI_BYTES + 1024;   // + alignment slack
     static constexpr int TMEM_A_COL = 2 * BN;                     // first column of the A slots
     static constexpr int TMEM_COLS = 512;
@@ -471,7 +471,7 @@ __device__ __forceinline__ void st_release_gpu(int* p, int v) {
 
 // Registers are handed out per group of four warps, so the 10 warps are budgeted as 12: 168 registers per thread
 // is the most a launch of this shape gets (200 compiles but is refused at launch).
-template <int MODE, int BN, int STAGES, bool SK>
+template <int MODE, int BN, int STAGES, bool SK, int SLABS>
 __global__ void __launch_bounds__(320, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b0,
                const __grid_constant__ CUtensorMap tmap_b1, const __grid_constant__ CUtensorMap tmap_out, TcParams p)
@@ -481,7 +481,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     // CTAs running at the same time share activation rows in L2).  The smem pipeline and the two TMEM
     // buffers keep running across tile boundaries: the producer prefetches the next tile while the
     // drain warps still store the previous one.
-    using L = TcSmem<BN, STAGES>;
+    using L = TcSmem<BN, STAGES, SLABS>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* full_bar = (uint64_t*)(smem + L::BAR_OFFSET);
@@ -866,13 +866,13 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 // Dense output: each warp stages its 32 rows x 32 columns in a 128B-swizzled slab (conflict-free
                 // float4 writes) and hands it to the TMA store engine, which writes whole rows asynchronously and
                 // clips rows >= M and columns >= N; two slabs per warp alternate so the warp never waits on HBM.
-                uint8_t* ebuf = smem + L::EPI_OFFSET + (warp - 6) * 8192;
+                uint8_t* ebuf = smem + L::EPI_OFFSET + (warp - 6) * (SLABS * 4096);
 #pragma unroll
                 for (int cc = 0; cc < BN / 32; cc++) {
                     if (n0 + cc * 32 < p.N && m0 + quad * 32 < p.M) {       // slabs wholly outside the output are skipped
-                        uint8_t* buf = ebuf + (ecount & 1) * 4096;
+                        uint8_t* buf = ebuf + (ecount % SLABS) * 4096;
                         if (MODE == TCM_FWD && p.epi) tc_epilogue_math(p, n0 + cc * 32, &acc[cc * 32]);
-                        if (lane == 0) tma_store_wait_read<1>();     // the store that last read this slab is done
+                        if (lane == 0) tma_store_wait_read<SLABS - 1>();     // the store that last read this slab is done
                         __syncwarp();
 #pragma unroll
                         for (int j = 0; j < 32; j += 4)
@@ -889,7 +889,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     }
                 }
             } else if (ok) {
-                float* stage = (float*)(smem + L::EPI_OFFSET) + (warp - 6) * (8192 / 4);
+                float* stage = (float*)(smem + L::EPI_OFFSET) + (warp - 6) * (SLABS * 4096 / 4);
 #pragma unroll
                 for (int cc = 0; cc < BN / 32; cc++) {
                     if (n0 + cc * 32 < p.N) {
@@ -1107,13 +1107,13 @@ size_t tc_workspace_bytes(const Geo& g, int pass)
            align_up((size_t)pl.splits * 4 * g.co * sizeof(float), 1024);
 }
 
-template <int MODE, int BN, int STAGES, bool SK>
+template <int MODE, int BN, int STAGES, bool SK, int SLABS>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb0, const CUtensorMap& mb1, const CUtensorMap& mo, const TcParams& p, int splits, cudaStream_t st)
 {
-    using L = TcSmem<BN, STAGES>;
+    using L = TcSmem<BN, STAGES, SLABS>;
     static bool attr_set = false;
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(conv_tc_kernel<MODE, BN, STAGES, SK>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+        cudaError_t e = cudaFuncSetAttribute(conv_tc_kernel<MODE, BN, STAGES, SK, SLABS>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
         if (e != cudaSuccess) { set_cuda_error(e, "cudaFuncSetAttribute(conv_tc_kernel)"); return B2C_ERR_CUDA; }
         attr_set = true;
     }
@@ -1126,7 +1126,7 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb0, const CUtens
     { const char* e = getenv("B2C_TC_DBG"); q.dbg = e ? atoi(e) : 0; }
 #endif
     const int grid = q.sk ? sm_count : (int)(tiles < sm_count ? tiles : sm_count);     // one persistent CTA per SM
-    launch_pdl(conv_tc_kernel<MODE, BN, STAGES, SK>, grid, 320, L::TOTAL, st, ma, mb0, mb1, mo, q);
+    launch_pdl(conv_tc_kernel<MODE, BN, STAGES, SK, SLABS>, grid, 320, L::TOTAL, st, ma, mb0, mb1, mo, q);
     return check_launch("conv_tc_kernel");
 }
 
@@ -1134,11 +1134,17 @@ template <int MODE>
 static int dispatch_tc(int bn, const CUtensorMap& ma, const CUtensorMap& mb0, const CUtensorMap& mb1, const CUtensorMap& mo, const TcParams& p, int splits, cudaStream_t st)
 {
     if (MODE == TCM_FWD && p.sk) {
-        if (bn == 64) return launch_tc<TCM_FWD, 64, 6, true>(ma, mb0, mb1, mo, p, splits, st);
-        return launch_tc<TCM_FWD, 128, 4, true>(ma, mb0, mb1, mo, p, splits, st);
+        if (bn == 64) return launch_tc<TCM_FWD, 64, 6, true, 2>(ma, mb0, mb1, mo, p, splits, st);
+        return launch_tc<TCM_FWD, 128, 4, true, 2>(ma, mb0, mb1, mo, p, splits, st);
     }
-    if (bn == 64) return launch_tc<MODE, 64, 6, false>(ma, mb0, mb1, mo, p, splits, st);
-    return launch_tc<MODE, 128, 4, false>(ma, mb0, mb1, mo, p, splits, st);
+    // Short K loops (up to four k-blocks per tile) are bound by the epilogue: a shallower operand pipeline
+    // leaves room for four output slabs per drain warp, so a whole tile's stores are in flight at once.
+    if (MODE == TCM_FWD && p.kblocks <= 4 && p.tma_store) {
+        if (bn == 64) return launch_tc<TCM_FWD, 64, 4, false, 4>(ma, mb0, mb1, mo, p, splits, st);
+        return launch_tc<TCM_FWD, 128, 3, false, 4>(ma, mb0, mb1, mo, p, splits, st);
+    }
+    if (bn == 64) return launch_tc<MODE, 64, 6, false, 2>(ma, mb0, mb1, mo, p, splits, st);
+    return launch_tc<MODE, 128, 4, false, 2>(ma, mb0, mb1, mo, p, splits, st);
 }
 
 // Output seen as [planes][rows][cols] floats, box = 32 cols x 32 rows (x 1 plane), 128B swizzle.
