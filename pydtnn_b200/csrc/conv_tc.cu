@@ -97,6 +97,10 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                  ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y, int z) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z) : "memory");
+}
 __device__ __forceinline__ void tma_load_im2col_4d(void* dst, const CUtensorMap* map, uint64_t* bar, int c, int w, int h,
                                                    int n, uint16_t off_w, uint16_t off_h) {
     asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes"
@@ -235,6 +239,7 @@ struct PrepParams {
     int rows, C, R, S;               // output is [rows][(r*S+s)*C + c], r < R, s < S (virtual taps)
     int64_t s_row, s_c, s_r, s_s;    // element strides of the source filter by (row, c, r, s)
     int r0, rstep, s0, sstep;        // real tap of virtual tap (r, s): (r0 + rstep*r, s0 + sstep*s)
+    int Rreal, Sreal;                // extent of the real filter
 };
 
 // Also clears `nflags` ints at `flags` (the hand-over flags of the balanced mode of the convolution kernel that
@@ -325,6 +330,12 @@ __global__ void tc_prep_filter_lowered_kernel(int rows, int K, int Kp, int C, in
 // The kernel (one template, two modes)
 // ---------------------------------------------------------------------------------------------
 enum { TCM_FWD = 0, TCM_WGRAD = 1 };
+// Where the FWD kernel takes its B tiles (filters) from:
+//  TCB_SPLIT  hi and lo copies in the K-major GEMM layout, written by tc_prep_filter_kernel (any filter layout)
+//  TCB_RAW_K  the caller's filter itself, read through a 3-D tensor map (channel, tap, row) whose channel axis is
+//             the GEMM K axis: K-major tiles; the transform warps write the lo half in shared memory
+//  TCB_RAW_MN the same with the channel axis being the GEMM N axis: MN-major boxes as in WGRAD
+enum { TCB_SPLIT = 0, TCB_RAW_K = 1, TCB_RAW_MN = 2 };
 
 #define TC_CHUNK 8   // k-blocks accumulated in tensor memory before the partial sum is drained
 
@@ -352,6 +363,7 @@ struct TcParams {
     // so a tile may be shared by consecutive CTAs.  The CTA that starts a tile owns it; the others store their
     // partial tile in `sk_partial` (slot = CTA index, [BN/4][128 rows][4] floats) and raise `sk_flags` (4 per slot, one per
     // drain warp); the owner adds the partials in CTA order and runs the epilogue.
+    int tap_r0, tap_rstep, tap_s0, tap_sstep, tap_sreal;   // raw-filter modes: real tap of virtual tap (r, s)
     int sk;
     float* sk_partial;
     int* sk_flags;
@@ -471,7 +483,7 @@ __device__ __forceinline__ void st_release_gpu(int* p, int v) {
 
 // Registers are handed out per group of four warps, so the 10 warps are budgeted as 12: 168 registers per thread
 // is the most a launch of this shape gets (200 compiles but is refused at launch).
-template <int MODE, int BN, int STAGES, bool SK, int SLABS>
+template <int MODE, int BN, int STAGES, bool SK, int SLABS, int BSRC>
 __global__ void __launch_bounds__(320, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b0,
                const __grid_constant__ CUtensorMap tmap_b1, const __grid_constant__ CUtensorMap tmap_out, TcParams p)
@@ -569,11 +581,22 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         else
 #endif
                         {
-                            mbar_expect_tx(&full_bar[s], (uint32_t)L::STAGE_BYTES);
+                            mbar_expect_tx(&full_bar[s], (uint32_t)(BSRC == TCB_SPLIT ? L::STAGE_BYTES : L::A_BYTES + L::B_BYTES));
                             tma_load_im2col_4d(st, &tmap_a, &full_bar[s], cb * 32, base_w, base_h, img,
                                                (uint16_t)(sx * p.dil_w), (uint16_t)(r * p.dil_h));
-                            tma_load_2d(st + L::A_BYTES, &tmap_b0, &full_bar[s], kb * 32, n0);
-                            tma_load_2d(st + L::A_BYTES + L::B_BYTES, &tmap_b1, &full_bar[s], kb * 32, n0);
+                            if (BSRC == TCB_SPLIT) {
+                                tma_load_2d(st + L::A_BYTES, &tmap_b0, &full_bar[s], kb * 32, n0);
+                                tma_load_2d(st + L::A_BYTES + L::B_BYTES, &tmap_b1, &full_bar[s], kb * 32, n0);
+                            } else {
+                                const int tap_real = (p.tap_r0 + p.tap_rstep * r) * p.tap_sreal + p.tap_s0 + p.tap_sstep * sx;
+                                if (BSRC == TCB_RAW_K) {
+                                    tma_load_3d(st + L::A_BYTES, &tmap_b0, &full_bar[s], cb * 32, tap_real, n0);
+                                } else {
+#pragma unroll
+                                    for (int j = 0; j < BN / 32; j++)       // boxes past N are zero-filled by the TMA unit
+                                        tma_load_3d(st + L::A_BYTES + j * 4096, &tmap_b0, &full_bar[s], n0 + 32 * j, tap_real, cb * 32);
+                                }
+                            }
                         }
                     }
                 } else {
@@ -603,14 +626,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         // ---------------- MMA issuer ----------------
         // Converged warp, one elected lane issues (see elect_one_sync).
         {
-            constexpr uint32_t idesc = make_idesc_tf32(128, BN, 0, MODE == TCM_WGRAD);
+            constexpr bool B_MN = MODE == TCM_WGRAD || BSRC == TCB_RAW_MN;
+            constexpr uint32_t idesc = make_idesc_tf32(128, BN, 0, B_MN);
             // B tiles, K-major (FWD): rows of 128 B, 8-row groups 1024 B apart, K advances 32 B inside the row.
             // B tiles, MN-major (WGRAD): 32-row (K) boxes of 4096 B per 32 N elements, 4-row swizzle atoms of
             // 512 B, K advances by 8 rows = 1024 B.  A comes from tensor memory, K advances 8 columns.
-            constexpr uint32_t LBO = (MODE == TCM_WGRAD) ? 4096 : 0;
-            constexpr uint32_t SBO = (MODE == TCM_WGRAD) ? 512 : 1024;
-            constexpr uint32_t LAYOUT = (MODE == TCM_WGRAD) ? 1 : 2;
-            constexpr uint64_t KADV = (MODE == TCM_WGRAD) ? (1024 >> 4) : (32 >> 4);
+            constexpr uint32_t LBO = B_MN ? 4096 : 0;
+            constexpr uint32_t SBO = B_MN ? 512 : 1024;
+            constexpr uint32_t LAYOUT = B_MN ? 1 : 2;
+            constexpr uint64_t KADV = B_MN ? (1024 >> 4) : (32 >> 4);
             bool ok = true;
             int it = 0, gc = 0;
             TileWalk w;
@@ -670,7 +694,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         // in shared memory as well (only lo is written: the raw tile serves as hi).
         const int quad = warp & 3;                   // TMEM lane quadrant this warp may write
         const int row = quad * 32 + lane;            // A-tile row (GEMM M index inside the tile)
-        constexpr int B_VEC = (MODE == TCM_WGRAD) ? L::B_BYTES / 16 / 128 : 0;
+        constexpr bool SPLIT_B = MODE == TCM_WGRAD || BSRC != TCB_SPLIT;    // the lo half of B is made here
+        constexpr int B_VEC = SPLIT_B ? L::B_BYTES / 16 / 128 : 0;
         const int t = threadIdx.x - 64;              // 0..127
         int it = 0;
         bool ok = true;
@@ -714,7 +739,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll
                 for (int j = 0; j < 32; j++) v[j] = __float_as_uint(__uint_as_float(v[j]) - __uint_as_float(h[j]));
                 tmem_st_32x32(slot + 32, v);
-                if (MODE == TCM_WGRAD) {
+                if (SPLIT_B) {
                     const float4* b_hi = (const float4*)(st + L::A_BYTES);
                     float4* b_lo = (float4*)(smem + s * L::STAGE_BYTES + L::A_BYTES + L::B_BYTES);
 #pragma unroll
@@ -1107,13 +1132,13 @@ size_t tc_workspace_bytes(const Geo& g, int pass)
            align_up((size_t)pl.splits * 4 * g.co * sizeof(float), 1024);
 }
 
-template <int MODE, int BN, int STAGES, bool SK, int SLABS>
+template <int MODE, int BN, int STAGES, bool SK, int SLABS, int BSRC>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb0, const CUtensorMap& mb1, const CUtensorMap& mo, const TcParams& p, int splits, cudaStream_t st)
 {
     using L = TcSmem<BN, STAGES, SLABS>;
     static bool attr_set = false;
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(conv_tc_kernel<MODE, BN, STAGES, SK, SLABS>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+        cudaError_t e = cudaFuncSetAttribute(conv_tc_kernel<MODE, BN, STAGES, SK, SLABS, BSRC>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
         if (e != cudaSuccess) { set_cuda_error(e, "cudaFuncSetAttribute(conv_tc_kernel)"); return B2C_ERR_CUDA; }
         attr_set = true;
     }
@@ -1126,25 +1151,44 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb0, const CUtens
     { const char* e = getenv("B2C_TC_DBG"); q.dbg = e ? atoi(e) : 0; }
 #endif
     const int grid = q.sk ? sm_count : (int)(tiles < sm_count ? tiles : sm_count);     // one persistent CTA per SM
-    launch_pdl(conv_tc_kernel<MODE, BN, STAGES, SK, SLABS>, grid, 320, L::TOTAL, st, ma, mb0, mb1, mo, q);
+    launch_pdl(conv_tc_kernel<MODE, BN, STAGES, SK, SLABS, BSRC>, grid, 320, L::TOTAL, st, ma, mb0, mb1, mo, q);
     return check_launch("conv_tc_kernel");
 }
 
-template <int MODE>
-static int dispatch_tc(int bn, const CUtensorMap& ma, const CUtensorMap& mb0, const CUtensorMap& mb1, const CUtensorMap& mo, const TcParams& p, int splits, cudaStream_t st)
+template <int BSRC>
+static int dispatch_fwd(int bn, const CUtensorMap& ma, const CUtensorMap& mb0, const CUtensorMap& mb1, const CUtensorMap& mo, const TcParams& p, cudaStream_t st)
 {
-    if (MODE == TCM_FWD && p.sk) {
-        if (bn == 64) return launch_tc<TCM_FWD, 64, 6, true, 2>(ma, mb0, mb1, mo, p, splits, st);
-        return launch_tc<TCM_FWD, 128, 4, true, 2>(ma, mb0, mb1, mo, p, splits, st);
+    if (p.sk) {
+        if (bn == 64) return launch_tc<TCM_FWD, 64, 6, true, 2, BSRC>(ma, mb0, mb1, mo, p, 1, st);
+        return launch_tc<TCM_FWD, 128, 4, true, 2, BSRC>(ma, mb0, mb1, mo, p, 1, st);
     }
     // Short K loops (up to four k-blocks per tile) are bound by the epilogue: a shallower operand pipeline
     // leaves room for four output slabs per drain warp, so a whole tile's stores are in flight at once.
-    if (MODE == TCM_FWD && p.kblocks <= 4 && p.tma_store) {
-        if (bn == 64) return launch_tc<TCM_FWD, 64, 4, false, 4>(ma, mb0, mb1, mo, p, splits, st);
-        return launch_tc<TCM_FWD, 128, 3, false, 4>(ma, mb0, mb1, mo, p, splits, st);
+    if (p.kblocks <= 4 && p.tma_store) {
+        if (bn == 64) return launch_tc<TCM_FWD, 64, 4, false, 4, BSRC>(ma, mb0, mb1, mo, p, 1, st);
+        return launch_tc<TCM_FWD, 128, 3, false, 4, BSRC>(ma, mb0, mb1, mo, p, 1, st);
     }
-    if (bn == 64) return launch_tc<MODE, 64, 6, false, 2>(ma, mb0, mb1, mo, p, splits, st);
-    return launch_tc<MODE, 128, 4, false, 2>(ma, mb0, mb1, mo, p, splits, st);
+    if (bn == 64) return launch_tc<TCM_FWD, 64, 6, false, 2, BSRC>(ma, mb0, mb1, mo, p, 1, st);
+    return launch_tc<TCM_FWD, 128, 4, false, 2, BSRC>(ma, mb0, mb1, mo, p, 1, st);
+}
+
+static int dispatch_wgrad(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const TcParams& p, int splits, cudaStream_t st)
+{
+    if (bn == 64) return launch_tc<TCM_WGRAD, 64, 6, false, 2, TCB_SPLIT>(ma, mb, mb, mo, p, splits, st);
+    return launch_tc<TCM_WGRAD, 128, 4, false, 2, TCB_SPLIT>(ma, mb, mb, mo, p, splits, st);
+}
+
+// The caller's filter as a 3-D tensor [d2][d1 = taps][d0 = contiguous channel], box = 32 channels x 1 tap x box2.
+static bool make_map_filter(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1_bytes,
+                            uint64_t stride2_bytes, uint32_t box2, CUtensorMapSwizzle swz)
+{
+    cuuint64_t dims[3] = {d0, d1, d2};
+    cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
+    cuuint32_t box[3] = {32, 1, box2};
+    cuuint32_t estr[3] = {1, 1, 1};
+    return g_encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 // Output seen as [planes][rows][cols] floats, box = 32 cols x 32 rows (x 1 plane), 128B swizzle.
@@ -1205,16 +1249,35 @@ static int run_fwd(const FwdLaunch& f, const void* act, const void* w, const Pre
         const double plain = (double)rounds * (double)kblocks, balanced = (double)(tiles * kblocks) / G + 4.0;
         if (!filters_ready && room && tiles * kblocks >= 4 * (int64_t)G && balanced < 0.85 * plain) sk = 1;
     }
-    if (!filters_ready) {
+    // The filter itself serves as the B operand when its layout allows a tensor map over it (the channel axis
+    // that is contiguous decides K-major or MN-major); otherwise hi/lo copies in the GEMM layout are written first.
+    // Splitting the B tile in shared memory costs a long launch about 4 % (measured on a 0.9 ms layer), the split
+    // kernel about 5 us: the copies win beyond roughly 125 us of work (0.6 us per k-block on 148 SMs).
+    int bsrc = TCB_SPLIT;
+    CUtensorMap ma, mbh, mbl;
+    const bool long_launch = (((int64_t)f.n * f.P * f.Q + 127) / 128) * ((f.N + BN - 1) / BN) * f.kh * f.kw * (f.C / 32) > 30000;
+    if (!filters_ready && !long_launch && ((uintptr_t)w & 15) == 0 && pp.s_r == (int64_t)pp.Sreal * pp.s_s && (pp.s_s * 4) % 16 == 0) {
+        const uint64_t taps = (uint64_t)pp.Rreal * pp.Sreal;
+        if (pp.s_c == 1 && (pp.s_row * 4) % 16 == 0 &&
+            make_map_filter(&mbh, w, (uint64_t)pp.C, taps, (uint64_t)pp.rows, (uint64_t)pp.s_s * 4, (uint64_t)pp.s_row * 4, BN, CU_TENSOR_MAP_SWIZZLE_128B))
+            bsrc = TCB_RAW_K;
+        else if (pp.s_row == 1 && (pp.s_c * 4) % 16 == 0 &&
+                 make_map_filter(&mbh, w, (uint64_t)pp.rows, taps, (uint64_t)pp.C, (uint64_t)pp.s_s * 4, (uint64_t)pp.s_c * 4, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B))
+            bsrc = TCB_RAW_MN;
+        if (bsrc != TCB_SPLIT) mbl = mbh;
+    }
+    if (!filters_ready && bsrc == TCB_SPLIT) {
         int64_t total = (int64_t)f.N * K;
         int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
         launch_pdl(tc_prep_filter_kernel, blocks, 256, 0, st, pp, (const float*)w, w_hi, w_lo, sk_flags, sk ? tc_sm_count() * 4 : 0);
         int rc = check_launch("tc_prep_filter_kernel");
         if (rc) return rc;
+    } else if (sk) {
+        cudaError_t e = cudaMemsetAsync(sk_flags, 0, (size_t)tc_sm_count() * 4 * sizeof(int), st);
+        if (e != cudaSuccess) { set_cuda_error(e, "cudaMemsetAsync(balanced-mode flags)"); return B2C_ERR_CUDA; }
     }
-    CUtensorMap ma, mbh, mbl;
     if (!make_map_im2col(&ma, act, f.n, f.ah, f.aw, f.C, f.low_h, f.low_w, f.cnt_h, f.cnt_w, f.str_h, f.str_w, 128)) return B2C_ERR_UNSUPPORTED;
-    if (!make_map_2d(&mbh, w_hi, f.N, K, BN) || !make_map_2d(&mbl, w_lo, f.N, K, BN)) return B2C_ERR_UNSUPPORTED;
+    if (bsrc == TCB_SPLIT && (!make_map_2d(&mbh, w_hi, f.N, K, BN) || !make_map_2d(&mbl, w_lo, f.N, K, BN))) return B2C_ERR_UNSUPPORTED;
     TcParams p{};
     p.M = f.n * f.P * f.Q; p.N = f.N; p.P = f.P; p.Q = f.Q;
     p.C = f.C; p.cblocks = f.C / 32; p.kblocks = f.kh * f.kw * p.cblocks; p.S = f.kw;
@@ -1226,13 +1289,16 @@ static int run_fwd(const FwdLaunch& f, const void* act, const void* w, const Pre
     if (f.N % 4 == 0 && !(((uintptr_t)p.bias | (uintptr_t)p.mean | (uintptr_t)p.inv_std | (uintptr_t)p.gamma | (uintptr_t)p.beta) & 15))
         p.epi |= TC_EPI_VEC;
     p.out = out; p.o_sn = f.o_sn; p.o_sh = f.o_sh; p.o_sw = f.o_sw;
+    p.tap_r0 = pp.r0; p.tap_rstep = pp.rstep; p.tap_s0 = pp.s0; p.tap_sstep = pp.sstep; p.tap_sreal = pp.Sreal;
     p.sk = sk; p.sk_flags = sk_flags; p.sk_partial = (float*)((uintptr_t)sk_flags + sk_flag_bytes());
     // dense rows (plain fprop / stride-1 dgrad): rows are N floats apart in (n, i, j) order
     const bool dense = f.o_sw == f.N && f.o_sh == (int64_t)f.Q * f.N && f.o_sn == (int64_t)f.P * f.Q * f.N;
     CUtensorMap mo = mbh;
     p.tma_store = 0;
     if (dense && make_map_out(&mo, out, 0, (uint64_t)p.M, (uint64_t)f.N)) p.tma_store = 1;
-    return dispatch_tc<TCM_FWD>(BN, ma, mbh, mbl, mo, p, 1, st);
+    if (bsrc == TCB_RAW_K) return dispatch_fwd<TCB_RAW_K>(BN, ma, mbh, mbl, mo, p, st);
+    if (bsrc == TCB_RAW_MN) return dispatch_fwd<TCB_RAW_MN>(BN, ma, mbh, mbl, mo, p, st);
+    return dispatch_fwd<TCB_SPLIT>(BN, ma, mbh, mbl, mo, p, st);
 }
 
 static LowerParams lower_params(const Geo& g)
@@ -1280,7 +1346,7 @@ int tc_fprop(const Geo& g, const void* x, const void* w, const void* bias, const
                     (int64_t)g.ho * g.wo * g.co, (int64_t)g.wo * g.co, (int64_t)g.co};
         return run_fwd(f, rows, nullptr, none, bias, bn, relu, (float*)y, (void*)w_hi, 2 * fbytes + 1024, st, true);
     }
-    PrepParams pp{g.co, g.ci, g.kh, g.kw, wsd.sk, wsd.sc, wsd.sr, wsd.ss, 0, 1, 0, 1};
+    PrepParams pp{g.co, g.ci, g.kh, g.kw, wsd.sk, wsd.sc, wsd.sr, wsd.ss, 0, 1, 0, 1, g.kh, g.kw};
     FwdLaunch f{g.n, g.h, g.w, g.ci, g.ho, g.wo, g.co, g.kh, g.kw, -g.vpad, -g.hpad,
                 g.h + 2 * g.vpad - (g.kh - 1) * g.vdil, g.w + 2 * g.hpad - (g.kw - 1) * g.hdil,
                 g.vstr, g.hstr, g.vdil, g.hdil, (int64_t)g.ho * g.wo * g.co, (int64_t)g.wo * g.co, (int64_t)g.co};
@@ -1293,7 +1359,7 @@ int tc_dgrad(const Geo& g, const void* dy, const void* w, void* dx, void* ws, si
     if (g.vstr == 1 && g.hstr == 1) {
         // dx = convolution of dy with the flipped, transposed filter and padding (k-1)*dil - pad
         const int pv = (g.kh - 1) * g.vdil - g.vpad, ph = (g.kw - 1) * g.hdil - g.hpad;
-        PrepParams pp{g.ci, g.co, g.kh, g.kw, wsd.sc, wsd.sk, wsd.sr, wsd.ss, g.kh - 1, -1, g.kw - 1, -1};
+        PrepParams pp{g.ci, g.co, g.kh, g.kw, wsd.sc, wsd.sk, wsd.sr, wsd.ss, g.kh - 1, -1, g.kw - 1, -1, g.kh, g.kw};
         FwdLaunch f{g.n, g.ho, g.wo, g.co, g.h, g.w, g.ci, g.kh, g.kw, -pv, -ph, g.h, g.w, 1, 1, g.vdil, g.hdil,
                     (int64_t)g.h * g.w * g.ci, (int64_t)g.w * g.ci, (int64_t)g.ci};
         return run_fwd(f, dy, w, pp, nullptr, nullptr, 0, (float*)dx, ws, ws_bytes, st);
@@ -1315,7 +1381,7 @@ int tc_dgrad(const Geo& g, const void* dy, const void* w, void* dx, void* ws, si
         for (int b = 0; b < g.hstr; b++) {
             AxisClass ca = axis_class(a, g.vstr, g.vpad, g.kh, g.h), cb = axis_class(b, g.hstr, g.hpad, g.kw, g.w);
             if (ca.out_cnt == 0 || cb.out_cnt == 0 || ca.cnt == 0 || cb.cnt == 0) continue;
-            PrepParams pp{g.ci, g.co, ca.cnt, cb.cnt, wsd.sc, wsd.sk, wsd.sr, wsd.ss, ca.r0, -g.vstr, cb.r0, -g.hstr};
+            PrepParams pp{g.ci, g.co, ca.cnt, cb.cnt, wsd.sc, wsd.sk, wsd.sr, wsd.ss, ca.r0, -g.vstr, cb.r0, -g.hstr, g.kh, g.kw};
             FwdLaunch f{g.n, g.ho, g.wo, g.co, ca.out_cnt, cb.out_cnt, g.ci, ca.cnt, cb.cnt, ca.dmin, cb.dmin,
                         ca.out_cnt, cb.out_cnt, 1, 1, 1, 1,
                         (int64_t)g.h * g.w * g.ci, (int64_t)g.vstr * g.w * g.ci, (int64_t)g.hstr * g.ci};
@@ -1364,7 +1430,7 @@ int tc_wgrad(const Geo& g, const void* x, const void* dy, void* dw, void* db, vo
     p.db_partial = db ? (float*)(base + lbytes + pbytes) : nullptr;
     CUtensorMap mo = mb;
     p.tma_store = make_map_out(&mo, partial, (uint64_t)pl.splits, (uint64_t)Krows, (uint64_t)g.co) ? 1 : 0;
-    int rc = dispatch_tc<TCM_WGRAD>(pl.bn, ma, mb, mb, mo, p, pl.splits, st);
+    int rc = dispatch_wgrad(pl.bn, ma, mb, mo, p, pl.splits, st);
     if (rc) return rc;
     WStride wsd = w_stride(g.w_layout, g.ci, g.co, g.kh, g.kw);
     WgradReduceParams rp{Krows, g.co, g.ci, g.kw, pl.splits, wsd.sk, wsd.sc, wsd.sr, wsd.ss, (int)g.K};

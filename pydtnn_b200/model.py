@@ -65,6 +65,7 @@ class Model:
         self.y_batch = None
         self.loss_func = None
         self._train_fused = False
+        self._stage = None
         self._eval_layers = None
         self.fast_update = True
         self.fuse_add_relu = True
@@ -206,11 +207,42 @@ class Model:
                 layer.wait_allreduce_async()
                 layer.update_weights(optimizer)
 
-    def train_batch(self, x_batch, y_batch, optimizer, global_batch_size=None):
+    def _stage_next(self, x_batch, y_batch):
+        """Start the host -> device copy of the batch of the *next* step on a copy stream, into staging
+        buffers, so that it runs under this step's kernels. Pinned torch CPU tensors only."""
+        xin = self.layers[0].y.ary
+        if self._stage is None:
+            self._stage = {"x": torch.empty_like(xin.t), "y": torch.empty_like(self.y_batch.t),
+                           "stream": torch.cuda.Stream(device=xin.t.device), "ready": torch.cuda.Event(),
+                           "free": torch.cuda.Event(), "batch": None}
+            self._stage["free"].record()
+        st = self._stage
+        lab = self._labels(y_batch)
+        with torch.cuda.stream(st["stream"]):
+            st["stream"].wait_event(st["free"])           # the step that read the staging buffers has copied them out
+            st["x"].copy_(x_batch.view(xin.t.shape), non_blocking=True)
+            st["y"].copy_(lab.to(torch.int32), non_blocking=True)
+            st["ready"].record()
+        st["batch"] = (x_batch, y_batch)
+
+    def train_batch(self, x_batch, y_batch, optimizer, global_batch_size=None, next_batch=None):
         """One training step on a host batch; returns the loss object (``.loss()``, ``.accuracy()``
-        read the numbers back)."""
+        read the numbers back). ``next_batch=(x, y)`` (pinned torch CPU tensors) starts the upload of the
+        following step's inputs under this step's kernels; the call that then passes those same tensors
+        finds them on the device."""
         self._ensure_loss()
-        self._upload(x_batch, y_batch)
+        st = self._stage
+        if st is not None and st["batch"] is not None and st["batch"][0] is x_batch and st["batch"][1] is y_batch:
+            cur = torch.cuda.current_stream()
+            cur.wait_event(st["ready"])
+            self.layers[0].y.ary.t.copy_(st["x"], non_blocking=True)
+            self.y_batch.t.copy_(st["y"], non_blocking=True)
+            st["free"].record(cur)
+            st["batch"] = None
+        else:
+            self._upload(x_batch, y_batch)
+        if next_batch is not None and isinstance(next_batch[0], torch.Tensor):
+            self._stage_next(*next_batch)
         loss = self.forward_backward(global_batch_size)
         self.apply_update(optimizer)
         return loss

@@ -92,6 +92,28 @@ def test_per_layer_update_equals_arena_update():
             assert np.array_equal(getattr(la, k).ary.get(), getattr(lb, k).ary.get()), (la, k)
 
 
+def test_staged_upload_of_the_next_batch_gives_the_same_steps():
+    """``train_batch(..., next_batch=...)`` uploads the following step's pinned batch on a copy stream; the
+    three steps must be bit-identical to plain uploads."""
+    import torch
+    from pydtnn_b200.optimizers import SGD
+    a = _small_resnet("NHWC", np.float32)
+    b = _small_resnet("NHWC", np.float32)
+    oa, ob = SGD(0.05, 0.9), SGD(0.05, 0.9)
+    batches = []
+    for step in range(3):
+        x, labels = _batch(a, step)
+        batches.append((torch.from_numpy(x).pin_memory(), torch.from_numpy(labels.astype(np.int32)).pin_memory()))
+    for step in range(3):
+        nxt = batches[step + 1] if step + 1 < 3 else None
+        la = a.train_batch(*batches[step], oa, next_batch=nxt)
+        lb = b.train_batch(*batches[step], ob)
+        assert la.loss() == lb.loss()
+    for pa, pb in zip(a.get_all_layers(), b.get_all_layers()):
+        for k in pa.grad_vars:
+            assert np.array_equal(getattr(pa, k).ary.get(), getattr(pb, k).ary.get()), (pa, k)
+
+
 @pytest.mark.parametrize("layout", ["NHWC", "NCHW"])
 def test_inference_fusion_matches_unfused_chain(layout):
     """Conv+BN+ReLU / Conv+BN folded into the convolution epilogue for evaluation: same output as
