@@ -604,14 +604,15 @@ __global__ void __launch_bounds__(256) pool_fwd_v4_kernel(PoolP p, const float4*
     }
 }
 
-template <bool IS_MAX>
+// IDX = int when the element count fits 31 bits: the index decomposition is then done with 32-bit divisions.
+template <bool IS_MAX, typename IDX>
 __global__ void __launch_bounds__(256) pool_bwd_v4_kernel(PoolP p, const float4* __restrict__ dy, const int4* __restrict__ idx_max, float4* __restrict__ dx)
 {
     pdl_prologue();
     const int c4 = p.c / 4;
-    const int64_t total = (int64_t)p.n * p.h * p.w * c4;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-        const int cg = (int)(i % c4); int64_t r = i / c4;
+    const IDX total = (IDX)p.n * p.h * p.w * c4;
+    for (IDX i = (IDX)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (IDX)gridDim.x * blockDim.x) {
+        const int cg = (int)(i % c4); IDX r = i / c4;
         const int iw = (int)(r % p.w); r /= p.w;
         const int ih = (int)(r % p.h); const int nn = (int)(r / p.h);
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -970,8 +971,11 @@ extern "C" int b2c_pool_backward(int dtype, int layout, int is_max, int n, int h
     cudaStream_t st = (cudaStream_t)stream;
     int64_t total = (int64_t)n * h * w * c; int nchw = layout == B2C_LAYOUT_NCHW;
     if (dtype == B2C_F32 && !nchw && c % 4 == 0 && (((uintptr_t)dy | (uintptr_t)dx | (uintptr_t)idx_max) & 15) == 0) {
-        if (is_max) launch_pdl(pool_bwd_v4_kernel<true>, ew_blocks(total / 4), 256, 0, st, p, (const float4*)dy, (const int4*)idx_max, (float4*)dx);
-        else launch_pdl(pool_bwd_v4_kernel<false>, ew_blocks(total / 4), 256, 0, st, p, (const float4*)dy, (const int4*)idx_max, (float4*)dx);
+        const bool small = total / 4 + (int64_t)ew_blocks(total / 4) * 256 < 0x7fffffffLL;
+        if (is_max && small) launch_pdl(pool_bwd_v4_kernel<true, int>, ew_blocks(total / 4), 256, 0, st, p, (const float4*)dy, (const int4*)idx_max, (float4*)dx);
+        else if (is_max) launch_pdl(pool_bwd_v4_kernel<true, int64_t>, ew_blocks(total / 4), 256, 0, st, p, (const float4*)dy, (const int4*)idx_max, (float4*)dx);
+        else if (small) launch_pdl(pool_bwd_v4_kernel<false, int>, ew_blocks(total / 4), 256, 0, st, p, (const float4*)dy, (const int4*)idx_max, (float4*)dx);
+        else launch_pdl(pool_bwd_v4_kernel<false, int64_t>, ew_blocks(total / 4), 256, 0, st, p, (const float4*)dy, (const int4*)idx_max, (float4*)dx);
         return check_launch("pool_backward_v4");
     }
     if (dtype == B2C_F32) {

@@ -93,6 +93,10 @@ __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
+// Start fetching a tensor map (a kernel parameter) into the TMA unit's descriptor cache.
+__device__ __forceinline__ void tma_prefetch_map(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                  ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
@@ -311,6 +315,48 @@ __global__ void tc_lower_kernel(LowerParams p, const float* __restrict__ x, floa
     }
 }
 
+// The same matrix, one block per output row (n, oh): the kh input rows the row of windows touches are copied into
+// shared memory once (coalesced, zero outside the image), then every float4 of the matrix row block is put
+// together from four shared-memory reads.  Threads are laid out as (pixel sub-index, column group), so a thread
+// again keeps its column group and decodes its four (tap, channel) pairs once.
+__global__ void tc_lower_rows_kernel(LowerParams p, const float* __restrict__ x, float4* __restrict__ rows, int wp)
+{
+    pdl_prologue();
+    extern __shared__ float patch[];                      // [kh][wp][c], column j is input column j - hpad
+    const int nn = blockIdx.x / p.ho, oh = blockIdx.x - nn * p.ho;
+    const int rowlen = wp * p.c;
+    for (int r = 0; r < p.kh; r++) {
+        const int ih = oh * p.vstr - p.vpad + r * p.vdil;
+        const float* src = x + ((int64_t)nn * p.h + ih) * p.w * p.c;
+        for (int j = threadIdx.x; j < rowlen; j += blockDim.x) {
+            const int iw = j / p.c - p.hpad;
+            patch[r * rowlen + j] = ((unsigned)ih < (unsigned)p.h && (unsigned)iw < (unsigned)p.w) ? __ldg(src + j - p.hpad * p.c) : 0.f;
+        }
+    }
+    __syncthreads();
+    const int kq = p.Kp / 4;
+    const int sub = threadIdx.x / kq, q4 = threadIdx.x - sub * kq, nsub = blockDim.x / kq;
+    if (sub >= nsub) return;
+    int off[4];
+    bool real[4];
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+        const int k = q4 * 4 + e;
+        real[e] = k < p.K;
+        const int kk = real[e] ? k : 0;
+        const int c = kk % p.c, rs = kk / p.c, r = rs / p.kw, sx = rs - r * p.kw;
+        off[e] = r * rowlen + sx * p.hdil * p.c + c;
+    }
+    float4* dst = rows + ((int64_t)nn * p.ho + oh) * p.wo * kq + q4;
+    for (int ow = sub; ow < p.wo; ow += nsub) {
+        const float* base = patch + ow * p.hstr * p.c;
+        float4 v;
+        v.x = real[0] ? base[off[0]] : 0.f; v.y = real[1] ? base[off[1]] : 0.f;
+        v.z = real[2] ? base[off[2]] : 0.f; v.w = real[3] ? base[off[3]] : 0.f;
+        dst[(int64_t)ow * kq] = v;
+    }
+}
+
 // hi/lo split of the filter in the lowered column order, zero in the padding columns
 __global__ void tc_prep_filter_lowered_kernel(int rows, int K, int Kp, int C, int S, int64_t s_row, int64_t s_c, int64_t s_r,
                                               int64_t s_s, const float* __restrict__ w, float* __restrict__ hi, float* __restrict__ lo)
@@ -509,6 +555,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const int mt = (p.M + 127) / 128, nt = (p.N + BN - 1) / BN;
     const int total_tiles = mt * nt * p.splits;
 
+    if (threadIdx.x == 32) {      // the tensor maps are kernel parameters: their fetch can start before anything else
+        tma_prefetch_map(&tmap_a); tma_prefetch_map(&tmap_b0);
+        if (BSRC == TCB_SPLIT && MODE == TCM_FWD) tma_prefetch_map(&tmap_b1);
+        if (p.tma_store) tma_prefetch_map(&tmap_out);
+    }
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&xform_bar[s], 4); mbar_init(&empty_bar[s], 1); }
         for (int b = 0; b < 2; b++) { mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], 4); }
@@ -1309,6 +1360,19 @@ static int launch_lower(const Geo& g, const void* x, float* rows, cudaStream_t s
 {
     LowerParams lp = lower_params(g);
     const int kq = lp.Kp / 4;
+    // one block per output row when its input rows fit in shared memory
+    const int wp = (g.wo - 1) * g.hstr + (g.kw - 1) * g.hdil + 1;
+    const size_t patch_bytes = (size_t)g.kh * wp * g.ci * sizeof(float);
+    if (kq <= 256 && patch_bytes <= 200 * 1024 && (int64_t)g.n * g.ho < 0x7fffffffLL) {
+        static bool attr_set = false;
+        if (!attr_set) {
+            cudaFuncSetAttribute(tc_lower_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            attr_set = true;
+        }
+        const int threads = 256 / kq * kq < 64 ? kq : 256 / kq * kq;       // a whole number of column-group sets
+        launch_pdl(tc_lower_rows_kernel, (unsigned)(g.n * g.ho), threads, patch_bytes, st, lp, (const float*)x, (float4*)rows, wp);
+        return check_launch("tc_lower_rows_kernel");
+    }
     int64_t total = g.M * kq;
     // block count: a multiple of kq / gcd(kq, 256), so that the thread count is a multiple of kq
     int a = kq, b = 256;
