@@ -270,5 +270,18 @@ class Model:
         loss, _ = self.loss_func(x, self.y_batch, self.batch_size * self.nprocs)
         return x, loss
 
+    def store_weights_and_bias(self, filename, layout="cpu"):
+        """Write the reference's NPZ checkpoint (pydtnn/model.py:380-384); see ``checkpoint.py`` for layouts."""
+        from . import checkpoint
+        self.synchronize()
+        checkpoint.store_weights_and_bias(self, filename, layout)
+
+    def load_weights_and_bias(self, filename, layout=None):
+        """Read a checkpoint written by the reference or by ``store_weights_and_bias`` (pydtnn/model.py:376-378)."""
+        from . import checkpoint
+        missing = checkpoint.load_weights_and_bias(self, filename, layout)
+        self._eval_layers = None          # fused inference layers fold the parameters they were built from
+        return missing
+
     def synchronize(self):
         torch.cuda.synchronize(self.device)
