@@ -36,6 +36,20 @@ METRIC = "resnet50_train_images_per_s"
 UNIT = "img/s"
 PER_GPU_BATCH = 64
 
+# The default workload is the configuration the headline metric is quoted on (ResNet-50 training); the other two
+# benchmark configurations that run whole networks are selectable with --workload.
+WORKLOADS = {
+    "resnet50": dict(metric=METRIC, name="resnet50_imagenet_train", batch=64, layout="NHWC", hw=224, train=True,
+                     build="create_resnet50_imagenet", model_kw=dict(enable_fused_bn_relu=True),
+                     input="3x224x224 f32 N(0,1)"),
+    "vgg16bn": dict(metric="vgg16bn_train_images_per_s", name="vgg16_bn_imagenet_train", batch=32, layout="NHWC", hw=224,
+                    train=True, build="create_vgg16bn_imagenet", model_kw=dict(enable_fused_bn_relu=True),
+                    input="3x224x224 f32 N(0,1)"),
+    "alexnet": dict(metric="alexnet_inference_images_per_s", name="alexnet_imagenet_inference", batch=64, layout="NCHW",
+                    hw=227, train=False, build="create_alexnet_imagenet", model_kw=dict(enable_fused_conv_relu=True),
+                    input="3x227x227 uint8 uniform /255 -> f32"),
+}
+
 
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -178,16 +192,22 @@ def run_ours(args):
     dev = torch.device("cuda", local_rank)
     L = _lib.lib()
 
+    wl = WORKLOADS[args.workload]
+    batch, hw, train = wl["batch"], wl["hw"], wl["train"]
     np.random.seed(0)                       # identical replicas
-    model = Model(batch_size=PER_GPU_BATCH, tensor_format="NHWC", dtype=np.float32, comm=True if world > 1 else None,
-                  non_blocking_mpi=True, enable_fused_bn_relu=True, device=dev)
-    nets.create_resnet50_imagenet(model)
+    model = Model(batch_size=batch, tensor_format=wl["layout"], dtype=np.float32, comm=True if world > 1 else None,
+                  non_blocking_mpi=True, device=dev, **wl["model_kw"])
+    getattr(nets, wl["build"])(model)
     opt = SGD(learning_rate=0.01 * world, momentum=0.9)
     model._ensure_loss()
 
     rng = np.random.Generator(np.random.PCG64(1000 + rank))
-    x_host = torch.from_numpy(rng.standard_normal((PER_GPU_BATCH, 224, 224, 3)).astype(np.float32)).pin_memory()
-    y_host = torch.from_numpy(rng.integers(0, 1000, PER_GPU_BATCH).astype(np.int32)).pin_memory()
+    if args.workload == "alexnet":
+        xs = (rng.integers(0, 256, (batch, 3, hw, hw)).astype(np.float32) / 255.0).astype(np.float32)
+    else:
+        xs = rng.standard_normal((batch, hw, hw, 3)).astype(np.float32)
+    x_host = torch.from_numpy(xs).pin_memory()
+    y_host = torch.from_numpy(rng.integers(0, 1000, batch).astype(np.int32)).pin_memory()
     model._upload(x_host, y_host)
     torch.cuda.synchronize()
 
@@ -196,14 +216,26 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def device_step():
-        model.forward_backward()
-        model.apply_update(opt)
+    if train:
+        def device_step():
+            model.forward_backward()
+            model.apply_update(opt)
 
-    def e2e_step():
-        # the next step's batch (here the same pinned tensors) is uploaded under this step's kernels
-        loss = model.train_batch(x_host, y_host, opt, next_batch=(x_host, y_host))
-        return loss.loss()                 # device -> host read of the per-row losses
+        def e2e_step():
+            # the next step's batch (here the same pinned tensors) is uploaded under this step's kernels
+            loss = model.train_batch(x_host, y_host, opt, next_batch=(x_host, y_host))
+            return loss.loss()                 # device -> host read of the per-row losses
+    else:
+        out_host = torch.empty((batch, 1000), dtype=torch.float32).pin_memory()
+
+        def device_step():
+            model.evaluate_batch(None)
+
+        def e2e_step():
+            y = model.evaluate_batch(x_host)
+            out_host.copy_(y.ary.t.view(batch, 1000), non_blocking=True)       # device -> host read of the class scores
+            torch.cuda.current_stream().synchronize()
+            return float(out_host[0, 0])
 
     def timed(step_fn, steps):
         barrier()
@@ -263,7 +295,7 @@ def run_ours(args):
     achieved = conv_flops / (conv_ms * 1e-3) / 1e12 if conv_ms > 0 else 0.0
     engines = {}
     for layer in model.get_all_layers():
-        if type(layer).__name__ == "Conv2DGPU":
+        if type(layer).__name__ in ("Conv2DGPU", "Conv2DReluGPU", "Conv2DBatchNormalizationGPU", "Conv2DBatchNormalizationReluGPU"):
             import ctypes
             for p, pname in enumerate(("fprop", "dgrad", "wgrad")):
                 e = L.b2c_conv_engine_for(ctypes.byref(layer.desc), p)
@@ -293,27 +325,28 @@ def run_ours(args):
 
     if rank != 0:
         return
-    imgs = PER_GPU_BATCH * world * args.steps
+    imgs = batch * world * args.steps
     value = imgs / (ms_total * 1e-3)
     e2e_value = imgs / (ms_e2e * 1e-3)
     line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "metric": wl["metric"], "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "resnet50_imagenet_train", "per_gpu_batch": PER_GPU_BATCH,
-                   "global_batch": PER_GPU_BATCH * world, "tensor_format": "NHWC", "input": "3x224x224 f32 N(0,1)",
-                   "optimizer": "SGD momentum 0.9", "parallelism": f"dp{world}",
-                   "grad_exchange": "bucketed NCCL all-reduce overlapped with backward" if world > 1 else "none",
+        "config": {"workload": wl["name"], "per_gpu_batch": batch,
+                   "global_batch": batch * world, "tensor_format": wl["layout"], "input": wl["input"],
+                   "optimizer": "SGD momentum 0.9" if train else "none (forward only, Conv+ReLU fused)",
+                   "parallelism": f"dp{world}",
+                   "grad_exchange": "bucketed NCCL all-reduce overlapped with backward" if world > 1 and train else "none",
                    "l2": "per-step activations (several GB) exceed the 126 MB L2; no flush needed"},
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
-                "h2d_bytes_per_step": int(x_host.numel() * 4 + y_host.numel() * 4) * world,
-                "d2h_bytes_per_step": int(PER_GPU_BATCH * 4) * world},
+                "h2d_bytes_per_step": int(x_host.numel() * 4 + (y_host.numel() * 4 if train else 0)) * world,
+                "d2h_bytes_per_step": int(batch * 4 if train else batch * 1000 * 4) * world},
         "gpu_launches": int(launches),
         "roofline": roofline,
         "final_loss": final_loss,
     }
-    if world == 1 and not args.no_cpu_baseline:
+    if world == 1 and not args.no_cpu_baseline and args.workload == "resnet50":
         threads = _cpu_threads()
         ips, kind, times = cpu_resnet50_images_per_s(8, 1, 0)
         line["cpu_baseline"] = {"value": ips, "unit": UNIT, "cores": threads, "kind": kind,
@@ -399,6 +432,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="resnet50",
+                    help="whole-network configuration to time (default: the one the headline metric is quoted on)")
     ap.add_argument("--layers", action="store_true", help="add per-layer convolution timings to the JSON line")
     ap.add_argument("--conv", default=None, help="n,h,w,ci,co,k,stride,pad: time one Conv2D pass instead of the model")
     ap.add_argument("--conv-pass", default="fprop", choices=["fprop", "dgrad", "wgrad"])

@@ -124,10 +124,10 @@ class _FusedConvInference(Conv2DGPU):
         if self._with_bn:
             self._refresh_bn()
         L = _lib.lib()
-        _lib.check(L.b2c_conv_fprop(ctypes.byref(self.desc), x.ptr, self.weights.ptr,
-                                    self.biases.ptr if self.use_bias else None,
-                                    ctypes.byref(self._bn) if self._with_bn else None, int(self._with_relu),
-                                    self.y.ptr, wsp.ptr(), wsp.size(), self.model.stream_handle))
+        self._timed("fprop", lambda: L.b2c_conv_fprop(
+            ctypes.byref(self.desc), x.ptr, self.weights.ptr, self.biases.ptr if self.use_bias else None,
+            ctypes.byref(self._bn) if self._with_bn else None, int(self._with_relu),
+            self.y.ptr, wsp.ptr(), wsp.size(), self.model.stream_handle))
         return self.y
 
     def backward(self, dy):

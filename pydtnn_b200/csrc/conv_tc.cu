@@ -1110,7 +1110,7 @@ static bool lowered_ok(const Geo& g)
     return (int64_t)g.M * lowered_kp(g) * 4 <= (int64_t)3 << 30;
 }
 
-bool tc_supported(const Geo& g, int pass)
+static bool tc_supported_nhwc(const Geo& g, int pass)
 {
     if (g.dtype != B2C_F32 || g.layout != B2C_LAYOUT_NHWC || g.engine == B2C_ENGINE_FMA) return false;
     if (g.vstr > 8 || g.hstr > 8) return false;
@@ -1171,7 +1171,7 @@ static WgradPlan wgrad_plan(const Geo& g)
     return pl;
 }
 
-size_t tc_workspace_bytes(const Geo& g, int pass)
+static size_t tc_workspace_bytes_nhwc(const Geo& g, int pass)
 {
     const bool low = g.ci % 32 != 0;
     const size_t lowered = low ? align_up((size_t)g.M * lowered_kp(g) * sizeof(float), 1024) : 0;
@@ -1384,7 +1384,7 @@ static int launch_lower(const Geo& g, const void* x, float* rows, cudaStream_t s
     return check_launch("tc_lower_kernel");
 }
 
-int tc_fprop(const Geo& g, const void* x, const void* w, const void* bias, const b2c_bn_params* bn, int relu,
+static int tc_fprop_nhwc(const Geo& g, const void* x, const void* w, const void* bias, const b2c_bn_params* bn, int relu,
              void* y, void* ws, size_t ws_bytes, cudaStream_t st)
 {
     WStride wsd = w_stride(g.w_layout, g.ci, g.co, g.kh, g.kw);
@@ -1417,7 +1417,7 @@ int tc_fprop(const Geo& g, const void* x, const void* w, const void* bias, const
     return run_fwd(f, x, w, pp, bias, bn, relu, (float*)y, ws, ws_bytes, st);
 }
 
-int tc_dgrad(const Geo& g, const void* dy, const void* w, void* dx, void* ws, size_t ws_bytes, cudaStream_t st)
+static int tc_dgrad_nhwc(const Geo& g, const void* dy, const void* w, void* dx, void* ws, size_t ws_bytes, cudaStream_t st)
 {
     WStride wsd = w_stride(g.w_layout, g.ci, g.co, g.kh, g.kw);
     if (g.vstr == 1 && g.hstr == 1) {
@@ -1456,7 +1456,7 @@ int tc_dgrad(const Geo& g, const void* dy, const void* w, void* dx, void* ws, si
     return B2C_OK;
 }
 
-int tc_wgrad(const Geo& g, const void* x, const void* dy, void* dw, void* db, void* ws, size_t ws_bytes, cudaStream_t st)
+static int tc_wgrad_nhwc(const Geo& g, const void* x, const void* dy, void* dw, void* db, void* ws, size_t ws_bytes, cudaStream_t st)
 {
     if (!load_driver_entry_points()) return B2C_ERR_UNSUPPORTED;
     const bool low = g.ci % 32 != 0;
@@ -1502,6 +1502,119 @@ int tc_wgrad(const Geo& g, const void* x, const void* dy, void* dw, void* db, vo
     int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
     launch_pdl(tc_wgrad_reduce_kernel, blocks, 256, 0, st, rp, partial, (float*)dw, p.db_partial, (float*)db);
     return check_launch("tc_wgrad_reduce_kernel");
+}
+
+// ---------------------------------------------------------------------------------------------
+// NCHW float32: the same kernels on channel-last copies.  The activations are transposed into the workspace
+// (and the result back), as the reference's own NCHW path transposes around its GEMM
+// (pydtnn/backends/cpu/layers/conv_2d_cpu.py:264-291, 447-481); filters stay where they are (every filter layout
+// is read through strides).  Taken when the transposes cost less than the FMA engine would lose.
+// ---------------------------------------------------------------------------------------------
+// src [n][rows][cols] -> dst [n][cols][rows]; block (32, 8), grid (cols/32, rows/32, n)
+__global__ void transpose_inner_kernel(const float* __restrict__ src, float* __restrict__ dst, int rows, int cols)
+{
+    pdl_prologue();
+    __shared__ float tile[32][33];
+    const int64_t plane = (int64_t)rows * cols;
+    const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32, tx = threadIdx.x, ty = threadIdx.y;
+    {
+        const int img = blockIdx.z;
+        const float* s = src + img * plane;
+        float* d = dst + img * plane;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int r = r0 + ty + 8 * j, c = c0 + tx;
+            if (r < rows && c < cols) tile[ty + 8 * j][tx] = s[(int64_t)r * cols + c];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int c = c0 + ty + 8 * j, r = r0 + tx;
+            if (r < rows && c < cols) d[(int64_t)c * rows + r] = tile[tx][ty + 8 * j];
+        }
+    }
+}
+
+static int transpose_inner(const void* src, void* dst, int n, int rows, int cols, cudaStream_t st)
+{
+    if (n > 65535) return B2C_ERR_TOO_LARGE;
+    launch_pdl(transpose_inner_kernel, dim3((cols + 31) / 32, (rows + 31) / 32, n), dim3(32, 8), 0, st,
+               (const float*)src, (float*)dst, rows, cols);
+    return check_launch("transpose_inner_kernel");
+}
+
+static Geo as_nhwc(const Geo& g) { Geo q = g; q.layout = B2C_LAYOUT_NHWC; return q; }
+static size_t act_bytes(int64_t n, int64_t h, int64_t w, int64_t c) { return align_up((size_t)(n * h * w * c) * sizeof(float), 1024); }
+
+bool tc_supported(const Geo& g, int pass)
+{
+    if (g.layout == B2C_LAYOUT_NHWC) return tc_supported_nhwc(g, pass);
+    if (g.dtype != B2C_F32 || g.engine == B2C_ENGINE_FMA || g.n > 65535) return false;
+    const Geo q = as_nhwc(g);
+    if (!tc_supported_nhwc(q, pass)) return false;
+    if (g.engine == B2C_ENGINE_TENSOR) return true;
+    // two tensors are copied there and/or back (read + write each) at about 2.5 TB/s; the FMA engine runs the
+    // pass at about 26 TFLOP/s, this engine at about 130
+    const double flops = 2.0 * (double)g.M * (double)g.K * g.co;
+    const double xb = 4.0 * g.n * g.h * g.w * g.ci, yb = 4.0 * (double)g.M * g.co;
+    const double moved = 2.0 * (xb + yb);
+    return flops / 130e12 + moved / 2.5e12 < flops / 26e12;
+}
+
+size_t tc_workspace_bytes(const Geo& g, int pass)
+{
+    if (g.layout == B2C_LAYOUT_NHWC) return tc_workspace_bytes_nhwc(g, pass);
+    return act_bytes(g.n, g.h, g.w, g.ci) + act_bytes(g.n, g.ho, g.wo, g.co) + 1024 + tc_workspace_bytes_nhwc(as_nhwc(g), pass);
+}
+
+// workspace of an NCHW call: [x or dx, channel-last][y or dy, channel-last][workspace of the channel-last pass]
+struct NchwWs { float *a, *b; void* inner; size_t inner_bytes; };
+static bool nchw_ws(const Geo& g, void* ws, size_t ws_bytes, NchwWs& o)
+{
+    if (!ws) return false;
+    const uintptr_t base = align_up((uintptr_t)ws, 1024);
+    const size_t xa = act_bytes(g.n, g.h, g.w, g.ci), ya = act_bytes(g.n, g.ho, g.wo, g.co);
+    if (base + xa + ya > (uintptr_t)ws + ws_bytes) return false;
+    o.a = (float*)base; o.b = (float*)(base + xa); o.inner = (void*)(base + xa + ya);
+    o.inner_bytes = (uintptr_t)ws + ws_bytes - (base + xa + ya);
+    return true;
+}
+
+int tc_fprop(const Geo& g, const void* x, const void* w, const void* bias, const b2c_bn_params* bn, int relu,
+             void* y, void* ws, size_t ws_bytes, cudaStream_t st)
+{
+    if (g.layout == B2C_LAYOUT_NHWC) return tc_fprop_nhwc(g, x, w, bias, bn, relu, y, ws, ws_bytes, st);
+    NchwWs t;
+    if (!nchw_ws(g, ws, ws_bytes, t)) return B2C_ERR_WORKSPACE_TOO_SMALL;
+    int rc = transpose_inner(x, t.a, g.n, g.ci, g.h * g.w, st);                 // (c, hw) -> (hw, c)
+    if (rc) return rc;
+    rc = tc_fprop_nhwc(as_nhwc(g), t.a, w, bias, bn, relu, t.b, t.inner, t.inner_bytes, st);
+    if (rc) return rc;
+    return transpose_inner(t.b, y, g.n, g.ho * g.wo, g.co, st);                 // (hw, c) -> (c, hw)
+}
+
+int tc_dgrad(const Geo& g, const void* dy, const void* w, void* dx, void* ws, size_t ws_bytes, cudaStream_t st)
+{
+    if (g.layout == B2C_LAYOUT_NHWC) return tc_dgrad_nhwc(g, dy, w, dx, ws, ws_bytes, st);
+    NchwWs t;
+    if (!nchw_ws(g, ws, ws_bytes, t)) return B2C_ERR_WORKSPACE_TOO_SMALL;
+    int rc = transpose_inner(dy, t.b, g.n, g.co, g.ho * g.wo, st);
+    if (rc) return rc;
+    rc = tc_dgrad_nhwc(as_nhwc(g), t.b, w, t.a, t.inner, t.inner_bytes, st);
+    if (rc) return rc;
+    return transpose_inner(t.a, dx, g.n, g.h * g.w, g.ci, st);
+}
+
+int tc_wgrad(const Geo& g, const void* x, const void* dy, void* dw, void* db, void* ws, size_t ws_bytes, cudaStream_t st)
+{
+    if (g.layout == B2C_LAYOUT_NHWC) return tc_wgrad_nhwc(g, x, dy, dw, db, ws, ws_bytes, st);
+    NchwWs t;
+    if (!nchw_ws(g, ws, ws_bytes, t)) return B2C_ERR_WORKSPACE_TOO_SMALL;
+    int rc = transpose_inner(x, t.a, g.n, g.ci, g.h * g.w, st);
+    if (rc) return rc;
+    rc = transpose_inner(dy, t.b, g.n, g.co, g.ho * g.wo, st);
+    if (rc) return rc;
+    return tc_wgrad_nhwc(as_nhwc(g), t.a, t.b, dw, db, t.inner, t.inner_bytes, st);
 }
 
 #ifdef B2C_TC_PROFILE
