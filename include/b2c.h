@@ -152,10 +152,14 @@ int b2c_bn_train_forward_static(int dtype, int layout, int n, int c, int hw, con
                                 const void *beta, void *running_mean, void *running_var, double momentum,
                                 double eps, int fuse_relu, void *y, void *save_mean, void *save_inv_std,
                                 void *stream);
-/* dgamma, dbeta, dx (dx may be NULL). If fuse_relu, dy is first masked by y > 0.
+/* dgamma, dbeta, dx (dx may be NULL). If the forward pass fused the ReLU, dy is first masked by y > 0: pass
+ * the forward output as y_for_relu_mask, and/or the forward beta as beta_for_relu_mask.  With beta the float32
+ * NHWC path recomputes the mask from x (the same instruction sequence as the forward pass, bit for bit) and
+ * does not read y; every other path reads y, so callers pass both.  Both NULL: no ReLU.
  * Replaces cudnnBatchNormalizationBackward, batch_normalization_gpu.py:146-156. scratch: as for the forward pass. */
 int b2c_bn_train_backward(int dtype, int layout, int n, int c, int hw, const void *x, const void *dy,
-                          const void *y_for_relu_mask, const void *gamma, const void *save_mean,
+                          const void *y_for_relu_mask, const void *beta_for_relu_mask, const void *gamma,
+                          const void *save_mean,
                           const void *save_inv_std, void *dgamma, void *dbeta, void *dx,
                           void *scratch, size_t scratch_bytes, void *stream);
 /* y = relu?(((x-mean)*inv_std)*gamma+beta); pydtnn/cython_modules/bn_inference_cython.pyx:71-72. */

@@ -85,7 +85,8 @@ class BatchNormalizationGPU(LayerGPU, BatchNormalization):
         m = self.model
         _lib.check(_lib.lib().b2c_bn_train_backward(
             self._dt, _layout(m), m.batch_size, self.ci, self._hw, self.x.ptr, dy.ptr,
-            self.y.ptr if self.fuse_relu else None, self.gamma.ptr, self.save_mean.ptr, self.save_inv_var.ptr,
+            self.y.ptr if self.fuse_relu else None, self.beta.ptr if self.fuse_relu else None, self.gamma.ptr,
+            self.save_mean.ptr, self.save_inv_var.ptr,
             self.dgamma.ptr, self.dbeta.ptr, self.dx.ptr if self.need_dx else None,
             wsp.reduction_scratch().data_ptr(), wsp.reduction_scratch().numel() * 8, m.stream_handle))
         if self.need_dx:

@@ -225,6 +225,14 @@ __global__ void __launch_bounds__(256) reduce2_v4_kernel(F f, double* __restrict
     }
 }
 
+// The batch-norm output before the ReLU, in one fixed instruction sequence: the forward kernel stores
+// max(bn_affine(..), 0) and the backward kernels recompute bn_affine(..) > 0 as the ReLU mask from x instead of
+// reading y back, so both must round identically.
+__device__ __forceinline__ float bn_affine(float v, float m, float is, float ga, float be)
+{
+    return __fmaf_rn(ga, __fmul_rn(__fsub_rn(v, m), is), be);
+}
+
 struct StatV4 {
     const float4* x;
     __device__ void operator()(int64_t j, int, float (&v0)[4], float (&v1)[4]) const {
@@ -242,11 +250,21 @@ struct SumV4 {   // plain per-channel sum (bias gradient)
     }
 };
 struct BnBwdV4 {
-    const float4 *x, *dy, *y; const float *mean, *inv_std; int relu;
+    const float4 *x, *dy, *y; const float *mean, *inv_std, *gamma, *beta; int relu;     // beta != null: mask from x
     __device__ void operator()(int64_t j, int grp, float (&v0)[4], float (&v1)[4]) const {
         float4 xv = x[j], g = dy[j];
-        if (relu) { float4 yv = y[j]; if (!(yv.x > 0.f)) g.x = 0.f; if (!(yv.y > 0.f)) g.y = 0.f; if (!(yv.z > 0.f)) g.z = 0.f; if (!(yv.w > 0.f)) g.w = 0.f; }
         const float4 m = *reinterpret_cast<const float4*>(mean + grp * 4), is = *reinterpret_cast<const float4*>(inv_std + grp * 4);
+        if (relu) {
+            if (beta) {
+                const float4 ga = *reinterpret_cast<const float4*>(gamma + grp * 4), be = *reinterpret_cast<const float4*>(beta + grp * 4);
+                if (!(bn_affine(xv.x, m.x, is.x, ga.x, be.x) > 0.f)) g.x = 0.f;
+                if (!(bn_affine(xv.y, m.y, is.y, ga.y, be.y) > 0.f)) g.y = 0.f;
+                if (!(bn_affine(xv.z, m.z, is.z, ga.z, be.z) > 0.f)) g.z = 0.f;
+                if (!(bn_affine(xv.w, m.w, is.w, ga.w, be.w) > 0.f)) g.w = 0.f;
+            } else {
+                float4 yv = y[j]; if (!(yv.x > 0.f)) g.x = 0.f; if (!(yv.y > 0.f)) g.y = 0.f; if (!(yv.z > 0.f)) g.z = 0.f; if (!(yv.w > 0.f)) g.w = 0.f;
+            }
+        }
         v0[0] = g.x * ((xv.x - m.x) * is.x); v0[1] = g.y * ((xv.y - m.y) * is.y);
         v0[2] = g.z * ((xv.z - m.z) * is.z); v0[3] = g.w * ((xv.w - m.w) * is.w);
         v1[0] = g.x; v1[1] = g.y; v1[2] = g.z; v1[3] = g.w;
@@ -301,8 +319,8 @@ __global__ void __launch_bounds__(256) bn_apply_v4_kernel(const float4* __restri
     const int64_t r0 = (int64_t)blockIdx.y * per, r1 = r0 + per < g.rows ? r0 + per : g.rows;
     for (int64_t r = r0 + rxi; r < r1; r += g.rx) {
         float4 v = x[r * g.c4 + grp], o;
-        o.x = ga.x * ((v.x - m.x) * is.x) + be.x; o.y = ga.y * ((v.y - m.y) * is.y) + be.y;
-        o.z = ga.z * ((v.z - m.z) * is.z) + be.z; o.w = ga.w * ((v.w - m.w) * is.w) + be.w;
+        o.x = bn_affine(v.x, m.x, is.x, ga.x, be.x); o.y = bn_affine(v.y, m.y, is.y, ga.y, be.y);
+        o.z = bn_affine(v.z, m.z, is.z, ga.z, be.z); o.w = bn_affine(v.w, m.w, is.w, ga.w, be.w);
         if (relu) { o.x = fmaxf(o.x, 0.f); o.y = fmaxf(o.y, 0.f); o.z = fmaxf(o.z, 0.f); o.w = fmaxf(o.w, 0.f); }
         y[r * g.c4 + grp] = o;
     }
@@ -311,7 +329,8 @@ __global__ void __launch_bounds__(256) bn_apply_v4_kernel(const float4* __restri
 __global__ void __launch_bounds__(256) bn_bwd_dx_v4_kernel(const float4* __restrict__ x, const float4* __restrict__ dy, const float4* __restrict__ y,
                                                            const float* __restrict__ gamma, const float* __restrict__ mean,
                                                            const float* __restrict__ inv_std, const float* __restrict__ dgamma,
-                                                           const float* __restrict__ dbeta, float4* __restrict__ dx, V4Geo g, int relu, float count)
+                                                           const float* __restrict__ dbeta, float4* __restrict__ dx, V4Geo g, int relu, float count,
+                                                           const float* __restrict__ beta)
 {
     pdl_prologue();
     const int cxi = threadIdx.x % g.cx, rxi = threadIdx.x / g.cx;
@@ -325,7 +344,13 @@ __global__ void __launch_bounds__(256) bn_bwd_dx_v4_kernel(const float4* __restr
     for (int64_t r = r0 + rxi; r < r1; r += g.rx) {
         const int64_t j = r * g.c4 + grp;
         float4 xv = x[j], gd = dy[j], o;
-        if (relu) { float4 yv = y[j]; if (!(yv.x > 0.f)) gd.x = 0.f; if (!(yv.y > 0.f)) gd.y = 0.f; if (!(yv.z > 0.f)) gd.z = 0.f; if (!(yv.w > 0.f)) gd.w = 0.f; }
+        if (relu && beta) {       // ReLU mask recomputed from x (see bn_affine)
+            const float4 be = *reinterpret_cast<const float4*>(beta + grp * 4);
+            if (!(bn_affine(xv.x, m.x, is.x, ga.x, be.x) > 0.f)) gd.x = 0.f;
+            if (!(bn_affine(xv.y, m.y, is.y, ga.y, be.y) > 0.f)) gd.y = 0.f;
+            if (!(bn_affine(xv.z, m.z, is.z, ga.z, be.z) > 0.f)) gd.z = 0.f;
+            if (!(bn_affine(xv.w, m.w, is.w, ga.w, be.w) > 0.f)) gd.w = 0.f;
+        } else if (relu) { float4 yv = y[j]; if (!(yv.x > 0.f)) gd.x = 0.f; if (!(yv.y > 0.f)) gd.y = 0.f; if (!(yv.z > 0.f)) gd.z = 0.f; if (!(yv.w > 0.f)) gd.w = 0.f; }
         o.x = sc.x * (count * gd.x - ((xv.x - m.x) * is.x) * dg.x - db.x);
         o.y = sc.y * (count * gd.y - ((xv.y - m.y) * is.y) * dg.y - db.y);
         o.z = sc.z * (count * gd.z - ((xv.z - m.z) * is.z) * dg.z - db.z);
@@ -396,16 +421,17 @@ static int bn_train_forward_t(int layout, int n, int c, int hw, const T* x, cons
 }
 
 template <typename T>
-static int bn_train_backward_t(int layout, int n, int c, int hw, const T* x, const T* dy, const T* y, const T* gamma,
+static int bn_train_backward_t(int layout, int n, int c, int hw, const T* x, const T* dy, const T* y, const T* beta, const T* gamma,
                                const T* sm, const T* si, T* dgamma, T* dbeta, T* dx, double* scratch, size_t scratch_bytes,
                                cudaStream_t st)
 {
     int chunks;
-    int relu = y != nullptr;
-    if (sizeof(T) == 4 && v4_ok(B2C_F32, layout, c, x, dy, dx ? (const void*)dx : (const void*)x) && (!y || ((uintptr_t)y & 15) == 0)) {
+    int relu = y != nullptr || beta != nullptr;
+    if (sizeof(T) == 4 && v4_ok(B2C_F32, layout, c, x, dy, dx ? (const void*)dx : (const void*)x) && (beta || !y || ((uintptr_t)y & 15) == 0)) {
         int max_chunks = (int)(scratch_bytes / ((size_t)2 * c * sizeof(double)));
         V4Geo g = v4_geo((int64_t)n * hw, c, max_chunks);
-        BnBwdV4 f{(const float4*)x, (const float4*)dy, (const float4*)y, (const float*)sm, (const float*)si, relu};
+        BnBwdV4 f{(const float4*)x, (const float4*)dy, (const float4*)y, (const float*)sm, (const float*)si, (const float*)gamma,
+                  (const float*)beta, relu};
         launch_pdl(reduce2_v4_kernel<BnBwdV4>, dim3(g.gx, g.chunks), 256, 0, st, f, scratch, g);
         int rc = check_launch("reduce2_v4(bn_bwd)"); if (rc) return rc;
         rc = final_warp(scratch, g.chunks, c, 1, 1.0, 0.0, 0.0, (float*)dgamma, (float*)dbeta, nullptr, nullptr, st);
@@ -413,9 +439,10 @@ static int bn_train_backward_t(int layout, int n, int c, int hw, const T* x, con
         V4Geo ga = v4_apply_geo((int64_t)n * hw, c);
         launch_pdl(bn_bwd_dx_v4_kernel, dim3(ga.gx, ga.chunks), 256, 0, st, (const float4*)x, (const float4*)dy, (const float4*)y, (const float*)gamma,
                                                                    (const float*)sm, (const float*)si, (const float*)dgamma, (const float*)dbeta,
-                                                                   (float4*)dx, ga, relu, (float)((double)n * hw));
+                                                                   (float4*)dx, ga, relu, (float)((double)n * hw), (const float*)beta);
         return check_launch("bn_bwd_dx_v4");
     }
+    if (relu && !y) return B2C_ERR_NULL_POINTER;        // this path reads the mask from y
     BnBwdF<T> f{x, dy, y, sm, si, relu};
     int rc = launch_reduce2(f, scratch, layout, n, c, hw, chunks, st);
     if (rc) return rc;
@@ -828,7 +855,7 @@ extern "C" int b2c_bn_train_forward_static(int dtype, int layout, int n, int c, 
 }
 
 extern "C" int b2c_bn_train_backward(int dtype, int layout, int n, int c, int hw, const void* x, const void* dy,
-                                     const void* y_for_relu_mask, const void* gamma, const void* save_mean,
+                                     const void* y_for_relu_mask, const void* beta_for_relu_mask, const void* gamma, const void* save_mean,
                                      const void* save_inv_std, void* dgamma, void* dbeta, void* dx,
                                      void* scratch, size_t scratch_bytes, void* stream)
 {
@@ -838,9 +865,11 @@ extern "C" int b2c_bn_train_backward(int dtype, int layout, int n, int c, int hw
     if (scratch_bytes < reduce2_bytes(c)) return B2C_ERR_WORKSPACE_TOO_SMALL;
     cudaStream_t st = (cudaStream_t)stream;
     if (dtype == B2C_F32)
-        return bn_train_backward_t<float>(layout, n, c, hw, (const float*)x, (const float*)dy, (const float*)y_for_relu_mask, (const float*)gamma,
+        return bn_train_backward_t<float>(layout, n, c, hw, (const float*)x, (const float*)dy, (const float*)y_for_relu_mask,
+                                          (const float*)beta_for_relu_mask, (const float*)gamma,
                                           (const float*)save_mean, (const float*)save_inv_std, (float*)dgamma, (float*)dbeta, (float*)dx, (double*)scratch, scratch_bytes, st);
-    return bn_train_backward_t<double>(layout, n, c, hw, (const double*)x, (const double*)dy, (const double*)y_for_relu_mask, (const double*)gamma,
+    return bn_train_backward_t<double>(layout, n, c, hw, (const double*)x, (const double*)dy, (const double*)y_for_relu_mask,
+                                       (const double*)beta_for_relu_mask, (const double*)gamma,
                                        (const double*)save_mean, (const double*)save_inv_std, (double*)dgamma, (double*)dbeta, (double*)dx, (double*)scratch, scratch_bytes, st);
 }
 

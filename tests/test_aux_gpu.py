@@ -26,7 +26,7 @@ def _nchw_dims(x, layout):
     return n, h, w, c
 
 
-def _bn_train(x, dy, gamma, beta, layout, fuse_relu=False):
+def _bn_train(x, dy, gamma, beta, layout, fuse_relu=False, mask_from="both"):
     L = _lib.lib()
     dt = _lib.dtype_code(x.dtype)
     n, h, w, c = _nchw_dims(x, layout)
@@ -40,7 +40,9 @@ def _bn_train(x, dy, gamma, beta, layout, fuse_relu=False):
                                       rm.data_ptr(), rv.data_ptr(), 0.9, 1e-5, int(fuse_relu), y.data_ptr(),
                                       sm.data_ptr(), si.data_ptr(), scratch.data_ptr(), scratch.numel() * 8, stream()))
     _lib.check(L.b2c_bn_train_backward(dt, _lay(layout), n, c, h * w, xd.data_ptr(), dyd.data_ptr(),
-                                       y.data_ptr() if fuse_relu else None, gd.data_ptr(), sm.data_ptr(),
+                                       y.data_ptr() if fuse_relu and mask_from in ("both", "y") else None,
+                                       bd.data_ptr() if fuse_relu and mask_from in ("both", "beta") else None,
+                                       gd.data_ptr(), sm.data_ptr(),
                                        si.data_ptr(), dg.data_ptr(), db.data_ptr(), dx.data_ptr(),
                                        scratch.data_ptr(), scratch.numel() * 8, stream()))
     torch.cuda.synchronize()
@@ -117,6 +119,12 @@ def test_batch_norm_at_resnet_sizes_and_fused_relu(layout):
     y, _, _, dg, db, dx = _bn_train(x, dy, gamma, beta, layout, fuse_relu=True)
     for nm, got, want in (("y", y, ry_ref), ("dgamma", dg, dg2), ("dbeta", db, db2), ("dx", dx, dx2)):
         assert_parity(got, want, np.float32, f"bn+relu {layout} {nm}")
+    if layout == "NHWC":
+        # the ReLU mask recomputed from x (beta given) is the mask read from y, bit for bit
+        a = _bn_train(x, dy, gamma, beta, layout, fuse_relu=True, mask_from="y")
+        b = _bn_train(x, dy, gamma, beta, layout, fuse_relu=True, mask_from="beta")
+        for nm, u, v in zip(("y", "rm", "rv", "dgamma", "dbeta", "dx"), a, b):
+            assert np.array_equal(u, v), f"mask from y vs from beta: {nm}"
 
 
 @pytest.mark.parametrize("dtype", ["float32", "float64"])
