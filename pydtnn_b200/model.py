@@ -13,7 +13,7 @@ import itertools
 import numpy as np
 import torch
 
-from . import _lib
+from . import _lib, tracer
 from .arena import ParamArena
 from .comm import GradientBucketer
 from .layers import (BatchNormalization, Conv2D, Conv2DBatchNormalization, Conv2DBatchNormalizationRelu, Conv2DRelu,
@@ -66,6 +66,7 @@ class Model:
         self.loss_func = None
         self._train_fused = False
         self._stage = None
+        self.tracer = tracer.StepTracer()        # off until enable_tracing()
         self._eval_layers = None
         self.fast_update = True
         self.fuse_add_relu = True
@@ -182,30 +183,40 @@ class Model:
         self._fuse_training()
         if global_batch_size is None:
             global_batch_size = self.batch_size * self.nprocs
+        tr = self.tracer
         x = self.layers[0].y
         for layer in self.layers[1:]:
-            x = layer.forward(x)
+            with tr.region(layer, tracer.PYDTNN_MDL_FORWARD):
+                x = layer.forward(x)
         loss, dx = self.loss_func(x, self.y_batch, global_batch_size)
         if self.comm is not None:
             self.bucketer.reset()
         for layer in reversed(self.layers[1:]):
-            dx = layer.backward(dx)
+            with tr.region(layer, tracer.PYDTNN_MDL_BACKWARD):
+                dx = layer.backward(dx)
             if not self.blocking_mpi:
-                layer.reduce_weights_async()
+                with tr.region(layer, tracer.PYDTNN_MDL_ALLREDUCE_DW):
+                    layer.reduce_weights_async()
         if self.blocking_mpi:
             for layer in reversed(self.layers[1:]):
-                layer.reduce_weights_sync()
+                with tr.region(layer, tracer.PYDTNN_MDL_ALLREDUCE_DW):
+                    layer.reduce_weights_sync()
         return loss
 
     def apply_update(self, optimizer):
+        tr = self.tracer
         if self.comm is not None:
             self.bucketer.wait_all()
         if self.fast_update and hasattr(optimizer, "update_arena"):
-            optimizer.update_arena(self)
+            # one launch over the whole arena: booked on the first parameterised layer
+            with tr.region(self.layers[1], tracer.PYDTNN_MDL_UPDATE_DW):
+                optimizer.update_arena(self)
         else:
             for layer in reversed(self.layers[1:]):
-                layer.wait_allreduce_async()
-                layer.update_weights(optimizer)
+                with tr.region(layer, tracer.PYDTNN_MDL_WAIT_DW):
+                    layer.wait_allreduce_async()
+                with tr.region(layer, tracer.PYDTNN_MDL_UPDATE_DW):
+                    layer.update_weights(optimizer)
 
     def _stage_next(self, x_batch, y_batch):
         """Start the host -> device copy of the batch of the *next* step on a copy stream, into staging

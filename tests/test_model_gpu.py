@@ -92,6 +92,28 @@ def test_per_layer_update_equals_arena_update():
             assert np.array_equal(getattr(la, k).ary.get(), getattr(lb, k).ary.get()), (la, k)
 
 
+def test_step_tracer_books_every_layer_once_per_step(tmp_path):
+    from pydtnn_b200 import tracer as tr
+    from pydtnn_b200.optimizers import SGD
+    m = _small_resnet("NHWC", np.float32)
+    opt = SGD(0.05, 0.9)
+    x, labels = _batch(m, 0)
+    m.train_batch(x, labels, opt)                 # untraced
+    m.tracer.enable_tracing()
+    for step in range(2):
+        m.train_batch(x, labels, opt)
+    m.tracer.disable_tracing()
+    m.synchronize()
+    s = m.tracer.summary()
+    for layer in m.layers[1:]:
+        for kind in (tr.PYDTNN_MDL_FORWARD, tr.PYDTNN_MDL_BACKWARD):
+            name, calls, total, median = s[tr.event_value(layer.id, kind)]
+            assert calls == 2 and total >= 0.0 and name.startswith(f"{layer.id}_")
+    out = tmp_path / "trace.csv"
+    m.tracer.write_output(out)
+    assert out.read_text().splitlines()[0].startswith("Event type;Event value;Event name")
+
+
 def test_staged_upload_of_the_next_batch_gives_the_same_steps():
     """``train_batch(..., next_batch=...)`` uploads the following step's pinned batch on a copy stream; the
     three steps must be bit-identical to plain uploads."""
