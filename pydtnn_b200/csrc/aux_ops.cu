@@ -203,14 +203,15 @@ __global__ void __launch_bounds__(256) reduce2_v4_kernel(F f, double* __restrict
     const int64_t r0 = (int64_t)blockIdx.y * per, r1 = r0 + per < g.rows ? r0 + per : g.rows;
     float a0[4] = {0.f, 0.f, 0.f, 0.f}, a1[4] = {0.f, 0.f, 0.f, 0.f};
     int64_t r = r0 + rxi;
-    if (F::UNROLL) {
-        // four rows per trip, their loads issued together; the additions keep the row order
-        for (; r + 3 * (int64_t)g.rx < r1; r += 4 * (int64_t)g.rx) {
-            float v0[4][4], v1[4][4];
+    if (F::UNROLL > 1) {
+        // several rows per trip, their loads issued together; the additions keep the row order
+        constexpr int U = F::UNROLL;
+        for (; r + (U - 1) * (int64_t)g.rx < r1; r += U * (int64_t)g.rx) {
+            float v0[U][4], v1[U][4];
 #pragma unroll
-            for (int u = 0; u < 4; u++) f((r + u * (int64_t)g.rx) * g.c4 + grp, grp, v0[u], v1[u]);
+            for (int u = 0; u < U; u++) f((r + u * (int64_t)g.rx) * g.c4 + grp, grp, v0[u], v1[u]);
 #pragma unroll
-            for (int u = 0; u < 4; u++)
+            for (int u = 0; u < U; u++)
 #pragma unroll
                 for (int e = 0; e < 4; e++) { a0[e] += v0[u][e]; a1[e] += v1[u][e]; }
         }
@@ -247,7 +248,7 @@ __device__ __forceinline__ float bn_affine(float v, float m, float is, float ga,
 }
 
 struct StatV4 {
-    static constexpr bool UNROLL = true;
+    static constexpr int UNROLL = 4;
     const float4* x;
     __device__ void operator()(int64_t j, int, float (&v0)[4], float (&v1)[4]) const {
         float4 v = x[j];
@@ -256,7 +257,7 @@ struct StatV4 {
     }
 };
 struct SumV4 {   // plain per-channel sum (bias gradient)
-    static constexpr bool UNROLL = true;
+    static constexpr int UNROLL = 4;
     const float4* x;
     __device__ void operator()(int64_t j, int, float (&v0)[4], float (&v1)[4]) const {
         float4 v = x[j];
@@ -265,7 +266,7 @@ struct SumV4 {   // plain per-channel sum (bias gradient)
     }
 };
 struct BnBwdV4 {
-    static constexpr bool UNROLL = false;
+    static constexpr int UNROLL = 1;      // more rows in flight cost this one registers and made the step slower
     const float4 *x, *dy, *y; const float *mean, *inv_std, *gamma, *beta; int relu;     // beta != null: mask from x
     __device__ void operator()(int64_t j, int grp, float (&v0)[4], float (&v1)[4]) const {
         float4 xv = x[j], g = dy[j];
