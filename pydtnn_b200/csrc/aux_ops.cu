@@ -200,7 +200,11 @@ __global__ void __launch_bounds__(256) reduce2_v4_kernel(F f, double* __restrict
     const int cxi = threadIdx.x % g.cx, rxi = threadIdx.x / g.cx;
     const int grp = blockIdx.x * g.cx + cxi;
     const int64_t per = (g.rows + gridDim.y - 1) / gridDim.y;
-    const int64_t r0 = (int64_t)blockIdx.y * per, r1 = r0 + per < g.rows ? r0 + per : g.rows;
+    // Blocks start in index order; the first ones take the *last* rows. The tensor was just written front to back
+    // by the kernel before, so its tail is what L2 still holds, and the pass that follows this one (apply / dx)
+    // walks front to back and finds the rows this pass read last.
+    const int chunk = gridDim.y - 1 - blockIdx.y;
+    const int64_t r0 = (int64_t)chunk * per, r1 = r0 + per < g.rows ? r0 + per : g.rows;
     float a0[4] = {0.f, 0.f, 0.f, 0.f}, a1[4] = {0.f, 0.f, 0.f, 0.f};
     int64_t r = r0 + rxi;
     if (F::UNROLL > 1) {
@@ -233,8 +237,8 @@ __global__ void __launch_bounds__(256) reduce2_v4_kernel(F f, double* __restrict
         const int c = g.c4 * 4;
 #pragma unroll
         for (int e = 0; e < 4; e++) {
-            partial[((int64_t)blockIdx.y * 2 + 0) * c + grp * 4 + e] = t[e];
-            partial[((int64_t)blockIdx.y * 2 + 1) * c + grp * 4 + e] = t[4 + e];
+            partial[((int64_t)chunk * 2 + 0) * c + grp * 4 + e] = t[e];
+            partial[((int64_t)chunk * 2 + 1) * c + grp * 4 + e] = t[4 + e];
         }
     }
 }
