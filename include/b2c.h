@@ -135,6 +135,16 @@ int b2c_bn_train_forward(int dtype, int layout, int n, int c, int hw, const void
                          const void *beta, void *running_mean, void *running_var, double momentum,
                          double eps, int fuse_relu, void *y, void *save_mean, void *save_inv_std,
                          void *scratch, size_t scratch_bytes, void *stream);
+/* The same with the residual sum of an addition block folded in: y = relu?(bn(x) + addend), the sum taken on the
+ * rounded batch-norm output exactly as a separate add kernel would take it.  For the last batch norm of a residual
+ * branch (pydtnn/backends/gpu/layers/addition_block_gpu.py:49-66 sums the branch outputs, the ReLU follows): the
+ * batch-norm output and the sum never travel through memory.  Backward is b2c_bn_train_backward on the masked
+ * gradient of the sum (no y needed). */
+int b2c_bn_train_forward_residual(int dtype, int layout, int n, int c, int hw, const void *x, const void *gamma,
+                                  const void *beta, void *running_mean, void *running_var, double momentum,
+                                  double eps, const void *addend, int relu, void *y, void *save_mean,
+                                  void *save_inv_std, void *scratch, size_t scratch_bytes, void *stream);
+
 /* b2c_bn_train_forward for callers that must not allocate and have no scratch buffer to lend: hosts
  * that give all device memory to their own pool at start-up and then forbid allocation (a late
  * cudaMalloc stalls the device and may fail once the pool owns the card).  Same arguments and results

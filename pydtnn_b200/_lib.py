@@ -58,6 +58,9 @@ PROTOTYPES = {
                                      c_size_t, c_void_p]),
     "b2c_bn_train_forward_static": (c_int, [c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                             c_void_p, c_double, c_double, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "b2c_bn_train_forward_residual": (c_int, [c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                              c_void_p, c_double, c_double, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                              c_void_p, c_size_t, c_void_p]),
     "b2c_bn_train_backward": (c_int, [c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                       c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
     "b2c_bn_inference": (c_int, [c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

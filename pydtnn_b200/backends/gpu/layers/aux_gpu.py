@@ -53,6 +53,7 @@ class BatchNormalizationGPU(LayerGPU, BatchNormalization):
         if self.need_dx:
             self.dx = TensorGPU(empty(x.ary.shape, m.dtype), m.tensor_format)
         self.fuse_relu = False           # set by the model's fusion pass (BN followed by ReLU)
+        self.residual = None             # (other branch, output) while an addition block folds its sum + ReLU in here
         self._dt = _lib.dtype_code(m.dtype)
         self._hw = self.hi * self.wi if self.spatial else 1
         self.updated_running_var = True
@@ -61,6 +62,16 @@ class BatchNormalizationGPU(LayerGPU, BatchNormalization):
         m = self.model
         L = _lib.lib()
         self.x = x
+        if m.mode == TRAIN_MODE and self.residual is not None:
+            # last batch norm of a residual branch: out = relu(bn(x) + other branch), written to the block's ReLU
+            addend, out = self.residual
+            _lib.check(L.b2c_bn_train_forward_residual(
+                self._dt, _layout(m), m.batch_size, self.ci, self._hw, x.ptr, self.gamma.ptr, self.beta.ptr,
+                self.running_mean.ptr, self.running_var.ptr, float(self.momentum), float(self.epsilon), addend.ptr, 1,
+                out.ptr, self.save_mean.ptr, self.save_inv_var.ptr, wsp.reduction_scratch().data_ptr(),
+                wsp.reduction_scratch().numel() * 8, m.stream_handle))
+            self.updated_running_var = True
+            return out
         if m.mode == TRAIN_MODE:
             _lib.check(L.b2c_bn_train_forward(self._dt, _layout(m), m.batch_size, self.ci, self._hw, x.ptr,
                                               self.gamma.ptr, self.beta.ptr, self.running_mean.ptr,
@@ -247,9 +258,33 @@ class AdditionBlockGPU(LayerGPU, AdditionBlock):
         self.y = self.paths[0][-1].y
         self._dt = _lib.dtype_code(m.dtype)
         self.relu_after = None           # set by the model: the Relu layer that directly follows this block
+        self.fold_sum = True             # let the first branch's last batch norm do the sum and that ReLU
+
+    def _fold_sum_into_last_bn(self):
+        """Training step, two branches, the block feeds a ReLU and the first branch ends in a plain batch norm:
+        that batch norm can add the other branch and apply the ReLU while it writes (one pass less over the block's
+        largest tensors, and the batch-norm output itself is never stored)."""
+        if self.model.mode != TRAIN_MODE or self.relu_after is None or len(self.paths) != 2 or not self.fold_sum:
+            return None
+        bn = self.paths[0][-1]
+        if type(bn).__name__ != "BatchNormalizationGPU" or bn.fuse_relu:
+            return None
+        return bn
 
     def forward(self, x):
         L = _lib.lib()
+        bn = self._fold_sum_into_last_bn()
+        if bn is not None:
+            other = x
+            for layer in self.paths[1]:
+                other = layer.forward(other)
+            bn.residual = (other, self.relu_after.y)
+            y = x
+            for layer in self.paths[0]:
+                y = layer.forward(y)
+            bn.residual = None
+            self.y = y
+            return self.y
         last = len(self.paths) - 1
         for i, p in enumerate(self.paths):
             y_i = x

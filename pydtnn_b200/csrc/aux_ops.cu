@@ -111,7 +111,7 @@ __global__ void bn_stats_final_kernel(const double* __restrict__ partial, int ch
 template <typename T>
 __global__ void bn_apply_kernel(const T* __restrict__ x, T* __restrict__ y, const T* __restrict__ mean,
                                 const T* __restrict__ inv_std, const T* __restrict__ gamma, const T* __restrict__ beta,
-                                int64_t total, int c, int hw, int nchw, int relu, int ref_order)
+                                int64_t total, int c, int hw, int nchw, int relu, int ref_order, const T* __restrict__ addend)
 {
     pdl_prologue();
     int64_t stride = (int64_t)gridDim.x * blockDim.x;
@@ -119,6 +119,7 @@ __global__ void bn_apply_kernel(const T* __restrict__ x, T* __restrict__ y, cons
         int ch = channel_of(i, c, hw, nchw);
         T xn = (x[i] - mean[ch]) * inv_std[ch];
         T v = ref_order ? (xn * gamma[ch] + beta[ch]) : (gamma[ch] * xn + beta[ch]);
+        if (addend) v = v + addend[i];        // residual sum: the rounded BN output plus the other branch
         if (relu) v = v > T(0) ? v : T(0);
         y[i] = v;
     }
@@ -329,7 +330,8 @@ __global__ void reduce2_final_warp_kernel(const double* __restrict__ partial, in
 
 __global__ void __launch_bounds__(256) bn_apply_v4_kernel(const float4* __restrict__ x, float4* __restrict__ y, const float* __restrict__ mean,
                                                           const float* __restrict__ inv_std, const float* __restrict__ gamma,
-                                                          const float* __restrict__ beta, V4Geo g, int relu)
+                                                          const float* __restrict__ beta, V4Geo g, int relu,
+                                                          const float4* __restrict__ addend)
 {
     pdl_prologue();
     const int cxi = threadIdx.x % g.cx, rxi = threadIdx.x / g.cx;
@@ -342,6 +344,10 @@ __global__ void __launch_bounds__(256) bn_apply_v4_kernel(const float4* __restri
         float4 v = x[r * g.c4 + grp], o;
         o.x = bn_affine(v.x, m.x, is.x, ga.x, be.x); o.y = bn_affine(v.y, m.y, is.y, ga.y, be.y);
         o.z = bn_affine(v.z, m.z, is.z, ga.z, be.z); o.w = bn_affine(v.w, m.w, is.w, ga.w, be.w);
+        if (addend) {        // residual sum on the rounded BN output, as the separate add kernel would do
+            const float4 a = addend[r * g.c4 + grp];
+            o.x = __fadd_rn(o.x, a.x); o.y = __fadd_rn(o.y, a.y); o.z = __fadd_rn(o.z, a.z); o.w = __fadd_rn(o.w, a.w);
+        }
         if (relu) { o.x = fmaxf(o.x, 0.f); o.y = fmaxf(o.y, 0.f); o.z = fmaxf(o.z, 0.f); o.w = fmaxf(o.w, 0.f); }
         y[r * g.c4 + grp] = o;
     }
@@ -415,9 +421,9 @@ static unsigned ew_blocks(int64_t total) { int64_t b = (total + 255) / 256; retu
 template <typename T>
 static int bn_train_forward_t(int layout, int n, int c, int hw, const T* x, const T* gamma, const T* beta,
                               T* rm, T* rv, double momentum, double eps, int relu, T* y, T* sm, T* si,
-                              double* scratch, size_t scratch_bytes, cudaStream_t st)
+                              double* scratch, size_t scratch_bytes, cudaStream_t st, const T* addend = nullptr)
 {
-    if (sizeof(T) == 4 && v4_ok(B2C_F32, layout, c, x, y, x)) {
+    if (sizeof(T) == 4 && v4_ok(B2C_F32, layout, c, x, y, addend ? (const void*)addend : (const void*)x)) {
         int max_chunks = (int)(scratch_bytes / ((size_t)2 * c * sizeof(double)));
         V4Geo g = v4_geo((int64_t)n * hw, c, max_chunks);
         StatV4 f{(const float4*)x};
@@ -427,7 +433,7 @@ static int bn_train_forward_t(int layout, int n, int c, int hw, const T* x, cons
         if (rc) return rc;
         V4Geo ga = v4_apply_geo((int64_t)n * hw, c);
         launch_pdl(bn_apply_v4_kernel, dim3(ga.gx, ga.chunks), 256, 0, st, (const float4*)x, (float4*)y, (const float*)sm, (const float*)si,
-                                                                  (const float*)gamma, (const float*)beta, ga, relu);
+                                                                  (const float*)gamma, (const float*)beta, ga, relu, (const float4*)addend);
         return check_launch("bn_apply_v4");
     }
     int chunks;
@@ -437,7 +443,7 @@ static int bn_train_forward_t(int layout, int n, int c, int hw, const T* x, cons
     launch_pdl(bn_stats_final_kernel<T>, (c + 127) / 128, 128, 0, st, scratch, chunks, c, (double)n * hw, momentum, eps, rm, rv, sm, si);
     rc = check_launch("bn_stats_final"); if (rc) return rc;
     int64_t total = (int64_t)n * c * hw;
-    launch_pdl(bn_apply_kernel<T>, ew_blocks(total), 256, 0, st, x, y, sm, si, gamma, beta, total, c, hw, layout == B2C_LAYOUT_NCHW, relu, 0);
+    launch_pdl(bn_apply_kernel<T>, ew_blocks(total), 256, 0, st, x, y, sm, si, gamma, beta, total, c, hw, layout == B2C_LAYOUT_NCHW, relu, 0, addend);
     return check_launch("bn_apply");
 }
 
@@ -816,6 +822,24 @@ extern "C" int b2c_bn_train_forward(int dtype, int layout, int n, int c, int hw,
                                       (double*)running_var, momentum, eps, fuse_relu, (double*)y, (double*)save_mean, (double*)save_inv_std, (double*)scratch, scratch_bytes, st);
 }
 
+extern "C" int b2c_bn_train_forward_residual(int dtype, int layout, int n, int c, int hw, const void* x, const void* gamma,
+                                             const void* beta, void* running_mean, void* running_var, double momentum,
+                                             double eps, const void* addend, int relu, void* y, void* save_mean,
+                                             void* save_inv_std, void* scratch, size_t scratch_bytes, void* stream)
+{
+    CHECK_DTYPE(dtype); CHECK_LAYOUT(layout);
+    if (!x || !gamma || !beta || !running_mean || !running_var || !addend || !y || !save_mean || !save_inv_std || !scratch) return B2C_ERR_NULL_POINTER;
+    if (n <= 0 || c <= 0 || hw <= 0) return B2C_ERR_BAD_GEOMETRY;
+    if (scratch_bytes < reduce2_bytes(c)) return B2C_ERR_WORKSPACE_TOO_SMALL;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == B2C_F32)
+        return bn_train_forward_t<float>(layout, n, c, hw, (const float*)x, (const float*)gamma, (const float*)beta, (float*)running_mean,
+                                         (float*)running_var, momentum, eps, relu, (float*)y, (float*)save_mean, (float*)save_inv_std,
+                                         (double*)scratch, scratch_bytes, st, (const float*)addend);
+    return bn_train_forward_t<double>(layout, n, c, hw, (const double*)x, (const double*)gamma, (const double*)beta, (double*)running_mean,
+                                      (double*)running_var, momentum, eps, relu, (double*)y, (double*)save_mean, (double*)save_inv_std,
+                                      (double*)scratch, scratch_bytes, st, (const double*)addend);
+}
 
 // ---- batch-norm forward without caller-supplied scratch ----------------------------------------
 // Some hosts of this library hand all device memory to their own pool when they start and from then
@@ -905,15 +929,15 @@ extern "C" int b2c_bn_inference(int dtype, int layout, int n, int c, int hw, con
     if (v4_ok(dtype, layout, c, x, y, x)) {
         V4Geo ga = v4_apply_geo((int64_t)n * hw, c);
         launch_pdl(bn_apply_v4_kernel, dim3(ga.gx, ga.chunks), 256, 0, st, (const float4*)x, (float4*)y, (const float*)mean, (const float*)inv_std,
-                                                                  (const float*)gamma, (const float*)beta, ga, relu);
+                                                                  (const float*)gamma, (const float*)beta, ga, relu, (const float4*)nullptr);
         return check_launch("bn_inference_v4");
     }
     if (dtype == B2C_F32)
         launch_pdl(bn_apply_kernel<float>, ew_blocks(total), 256, 0, st, (const float*)x, (float*)y, (const float*)mean, (const float*)inv_std,
-                                                                (const float*)gamma, (const float*)beta, total, c, hw, layout == B2C_LAYOUT_NCHW, relu, 1);
+                                                                (const float*)gamma, (const float*)beta, total, c, hw, layout == B2C_LAYOUT_NCHW, relu, 1, (const float*)nullptr);
     else
         launch_pdl(bn_apply_kernel<double>, ew_blocks(total), 256, 0, st, (const double*)x, (double*)y, (const double*)mean, (const double*)inv_std,
-                                                                 (const double*)gamma, (const double*)beta, total, c, hw, layout == B2C_LAYOUT_NCHW, relu, 1);
+                                                                 (const double*)gamma, (const double*)beta, total, c, hw, layout == B2C_LAYOUT_NCHW, relu, 1, (const double*)nullptr);
     return check_launch("bn_inference");
 }
 

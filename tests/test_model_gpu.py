@@ -92,6 +92,26 @@ def test_per_layer_update_equals_arena_update():
             assert np.array_equal(getattr(la, k).ary.get(), getattr(lb, k).ary.get()), (la, k)
 
 
+def test_residual_sum_folded_into_the_last_batch_norm_is_bit_identical():
+    """AdditionBlock + ReLU: the last batch norm of the first branch adds the other branch and applies the ReLU
+    while it writes; the steps must equal the ones with the separate add+ReLU kernel bit for bit."""
+    from pydtnn_b200.optimizers import SGD
+    a = _small_resnet("NHWC", np.float32, enable_fused_bn_relu=True)
+    b = _small_resnet("NHWC", np.float32, enable_fused_bn_relu=True)
+    blocks = [l for l in b.layers if type(l).__name__ == "AdditionBlockGPU"]
+    assert blocks
+    for blk in blocks:
+        blk.fold_sum = False
+    oa, ob = SGD(0.05, 0.9), SGD(0.05, 0.9)
+    for step in range(2):
+        x, labels = _batch(a, step)
+        la, lb = a.train_batch(x, labels, oa), b.train_batch(x, labels, ob)
+        assert la.loss() == lb.loss()
+    for pa, pb in zip(a.get_all_layers(), b.get_all_layers()):
+        for k in pa.grad_vars:
+            assert np.array_equal(getattr(pa, k).ary.get(), getattr(pb, k).ary.get()), (pa, k)
+
+
 def test_step_tracer_books_every_layer_once_per_step(tmp_path):
     from pydtnn_b200 import tracer as tr
     from pydtnn_b200.optimizers import SGD
