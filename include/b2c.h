@@ -184,6 +184,9 @@ int b2c_add_inplace(int dtype, int64_t count, void *acc, const void *other, void
 
 /* out = max(a + b, 0): the residual sum and the ReLU that follows an addition block, in one pass. */
 int b2c_add_relu(int dtype, int64_t count, const void *a, const void *b, void *out, void *stream);
+/* dx = (y > 0) ? a + b : 0: the sum of the branch gradients at an addition block's input and the backward of the
+ * ReLU that feeds the block (y = that ReLU's output), in one pass. */
+int b2c_add_relu_backward(int dtype, int64_t count, const void *a, const void *b, const void *y, void *dx, void *stream);
 
 /* Pooling over in-bounds taps only (pydtnn/cython_modules/max_pool_2d_nhwc_cython.pyx:96-113,
  * average_pool_2d_nhwc_cython.pyx:93-111); idx_max is int32 tap number ii*kw+jj.

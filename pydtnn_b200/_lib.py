@@ -69,6 +69,7 @@ PROTOTYPES = {
     "b2c_relu_backward": (c_int, [c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
     "b2c_add_inplace": (c_int, [c_int, c_int64, c_void_p, c_void_p, c_void_p]),
     "b2c_add_relu": (c_int, [c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "b2c_add_relu_backward": (c_int, [c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "b2c_pool_forward": (c_int, [c_int] * 15 + [c_void_p, c_void_p, c_void_p, c_void_p]),
     "b2c_pool_backward": (c_int, [c_int] * 15 + [c_void_p, c_void_p, c_void_p, c_void_p]),
     "b2c_softmax_forward": (c_int, [c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),

@@ -116,6 +116,7 @@ class ReluGPU(LayerGPU, Relu):
         self._dt = _lib.dtype_code(m.dtype)
         self.absorbed = False            # True when the preceding BatchNormalization applies the ReLU itself
         self.fed_by_block = False        # True when the preceding AdditionBlock writes max(sum, 0) into self.y
+        self.bwd_by_block = False        # True when the following AdditionBlock writes the masked gradient into self.dx
 
     def forward(self, x):
         if self.absorbed:
@@ -128,6 +129,8 @@ class ReluGPU(LayerGPU, Relu):
     def backward(self, dy):
         if self.absorbed:
             return dy
+        if self.bwd_by_block and self.model.mode == TRAIN_MODE:
+            return self.dx
         if self.need_dx:
             _lib.check(_lib.lib().b2c_relu_backward(self._dt, self.y.size, dy.ptr, self.y.ptr, self.dx.ptr,
                                                     self.model.stream_handle))
@@ -259,6 +262,7 @@ class AdditionBlockGPU(LayerGPU, AdditionBlock):
         self._dt = _lib.dtype_code(m.dtype)
         self.relu_after = None           # set by the model: the Relu layer that directly follows this block
         self.fold_sum = True             # let the first branch's last batch norm do the sum and that ReLU
+        self.relu_before = None          # set by the model: the Relu layer whose output is this block's input
 
     def _fold_sum_into_last_bn(self):
         """Training step, two branches, the block feeds a ReLU and the first branch ends in a plain batch norm:
@@ -309,6 +313,11 @@ class AdditionBlockGPU(LayerGPU, AdditionBlock):
                 dx_i = layer.backward(dx_i)
             if i == 0:
                 dx0 = dx_i
+            elif i == len(self.paths) - 1 and self.relu_before is not None:
+                # the sum of the branch gradients and the backward of the ReLU that feeds this block in one pass
+                r = self.relu_before
+                _lib.check(L.b2c_add_relu_backward(self._dt, dx0.size, dx0.ptr, dx_i.ptr, r.y.ptr, r.dx.ptr,
+                                                   self.model.stream_handle))
             else:
                 _lib.check(L.b2c_add_inplace(self._dt, dx0.size, dx0.ptr, dx_i.ptr, self.model.stream_handle))
         self.dx = dx0

@@ -719,6 +719,26 @@ template <typename T> __global__ void add_relu_kernel(const T* __restrict__ a, c
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) { T v = a[i] + b[i]; out[i] = v > T(0) ? v : T(0); }
 }
 
+// dx = (y > 0) ? a + b : 0  (the input-gradient sum of an addition block and the backward of the ReLU before it)
+__global__ void add_relu_bwd_f4_kernel(const float4* __restrict__ a, const float4* __restrict__ b, const float4* __restrict__ y,
+                                       float4* __restrict__ dx, int64_t n4)
+{
+    pdl_prologue();
+    int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+        const float4 u = a[i], v = b[i], m = y[i];
+        dx[i] = make_float4(m.x > 0.f ? __fadd_rn(u.x, v.x) : 0.f, m.y > 0.f ? __fadd_rn(u.y, v.y) : 0.f,
+                            m.z > 0.f ? __fadd_rn(u.z, v.z) : 0.f, m.w > 0.f ? __fadd_rn(u.w, v.w) : 0.f);
+    }
+}
+template <typename T> __global__ void add_relu_bwd_kernel(const T* __restrict__ a, const T* __restrict__ b, const T* __restrict__ y,
+                                                          T* __restrict__ dx, int64_t n)
+{
+    pdl_prologue();
+    int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) dx[i] = y[i] > T(0) ? a[i] + b[i] : T(0);
+}
+
 // ---- softmax / cross-entropy -------------------------------------------------------------------
 
 template <typename T> __device__ T block_reduce(T v, T* sm, bool is_max)
@@ -995,6 +1015,21 @@ extern "C" int b2c_add_relu(int dtype, int64_t count, const void* a, const void*
         else launch_pdl(add_relu_kernel<float>, ew_blocks(count), 256, 0, st, (const float*)a, (const float*)b, (float*)out, count);
     } else launch_pdl(add_relu_kernel<double>, ew_blocks(count), 256, 0, st, (const double*)a, (const double*)b, (double*)out, count);
     return check_launch("add_relu");
+}
+
+extern "C" int b2c_add_relu_backward(int dtype, int64_t count, const void* a, const void* b, const void* y, void* dx, void* stream)
+{
+    CHECK_DTYPE(dtype);
+    if (!a || !b || !y || !dx) return B2C_ERR_NULL_POINTER;
+    if (count < 0) return B2C_ERR_BAD_GEOMETRY;
+    if (count == 0) return B2C_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == B2C_F32) {
+        if (f4_ok(count, a, b, dx) && ((uintptr_t)y & 15) == 0)
+            launch_pdl(add_relu_bwd_f4_kernel, ew_blocks(count / 4), 256, 0, st, (const float4*)a, (const float4*)b, (const float4*)y, (float4*)dx, count / 4);
+        else launch_pdl(add_relu_bwd_kernel<float>, ew_blocks(count), 256, 0, st, (const float*)a, (const float*)b, (const float*)y, (float*)dx, count);
+    } else launch_pdl(add_relu_bwd_kernel<double>, ew_blocks(count), 256, 0, st, (const double*)a, (const double*)b, (const double*)y, (double*)dx, count);
+    return check_launch("add_relu_backward");
 }
 
 static int make_pool(PoolP& p, int layout, int n, int h, int w, int c, int kh, int kw, int vpad, int hpad, int vstr,

@@ -114,6 +114,11 @@ class Model:
                 if self.fuse_add_relu and a.is_block_layer and len(a.paths) > 1 and isinstance(b, Relu) \
                         and type(a).__name__ == "AdditionBlockGPU":
                     a.relu_after, b.fed_by_block = b, True
+                # a ReLU followed by an addition block: the block's input-gradient sum applies that ReLU's mask
+                if self.fuse_add_relu and isinstance(a, Relu) and type(a).__name__ == "ReluGPU" and b.is_block_layer \
+                        and len(b.paths) > 1 and type(b).__name__ == "AdditionBlockGPU" and a.need_dx \
+                        and not getattr(a, "absorbed", False):
+                    b.relu_before, a.bwd_by_block = a, True
             for layer in seq:
                 for p in layer.paths:
                     walk(p)

@@ -102,14 +102,21 @@ def test_residual_sum_folded_into_the_last_batch_norm_is_bit_identical():
     assert blocks
     for blk in blocks:
         blk.fold_sum = False
-    oa, ob = SGD(0.05, 0.9), SGD(0.05, 0.9)
+    # c: no block-level fusion at all (separate add, ReLU forward and ReLU backward kernels)
+    c = _small_resnet("NHWC", np.float32, enable_fused_bn_relu=True)
+    c.fuse_add_relu = False
+    oa, ob, oc = SGD(0.05, 0.9), SGD(0.05, 0.9), SGD(0.05, 0.9)
     for step in range(2):
         x, labels = _batch(a, step)
-        la, lb = a.train_batch(x, labels, oa), b.train_batch(x, labels, ob)
-        assert la.loss() == lb.loss()
-    for pa, pb in zip(a.get_all_layers(), b.get_all_layers()):
+        la, lb, lc = a.train_batch(x, labels, oa), b.train_batch(x, labels, ob), c.train_batch(x, labels, oc)
+        assert la.loss() == lb.loss() == lc.loss()
+    assert any(getattr(l, "relu_before", None) is not None for l in a.layers)
+    assert all(getattr(l, "relu_before", None) is None for l in c.layers)
+    for pa, pb, pc in zip(a.get_all_layers(), b.get_all_layers(), c.get_all_layers()):
         for k in pa.grad_vars:
-            assert np.array_equal(getattr(pa, k).ary.get(), getattr(pb, k).ary.get()), (pa, k)
+            ga = getattr(pa, k).ary.get()
+            assert np.array_equal(ga, getattr(pb, k).ary.get()), (pa, k)
+            assert np.array_equal(ga, getattr(pc, k).ary.get()), (pa, k)
 
 
 def test_step_tracer_books_every_layer_once_per_step(tmp_path):
