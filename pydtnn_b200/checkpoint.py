@@ -97,6 +97,8 @@ def load_state_dict(model, d, layout=None):
     missing = []
     for layer in _walk(model.layers):
         name = layer.canonical_name
+        if name == "BatchNormalization":
+            layer.updated_running_var = True       # as the reference: inv_std is refreshed at the next evaluation
         for key in _keys(layer):
             base = f"{layer.id}_{name}_{key}"
             if base not in d:

@@ -52,6 +52,7 @@ def test_reference_checkpoint_loads_and_reproduces_the_reference_output(layout, 
     out2 = os.path.join(tmp_path, "native.npz")
     m.store_weights_and_bias(out2, layout="gpu")
     m2 = _net(layout, 2)
+    m2.evaluate_batch(io[f"x_{layout}"])          # an evaluation before the load must not leave stale statistics behind
     assert m2.load_weights_and_bias(out2) == []
     y2 = m2.evaluate_batch(io[f"x_{layout}"]).ary.get()
     assert np.array_equal(y, y2)
