@@ -79,6 +79,11 @@ uint64_t b2c_launch_count(void);
  * receives the raw code. The reference has no counterpart (cuDNN reports through its status). */
 int b2c_check_device_status(int *detail);
 
+/* Launches one warp that waits, for at most limit_cycles SM clock cycles (1 .. 2e9), on a barrier nothing arrives
+ * at: the wait runs out, the status word is set (detail 7) and the kernel returns.  Lets a host check, on a healthy
+ * device, that a timed-out wait is reported by b2c_check_device_status and leaves the context usable. */
+int b2c_selftest_bounded_wait(int64_t limit_cycles, void *stream);
+
 /* Scratch bytes a pass needs for this geometry (0 = none).
  * Replaces the process-global cuDNN workspace sizing, pydtnn/backends/gpu/layers/memory_allocation.py:28-49
  * and ConvGemm's pack buffers, pydtnn/backends/cpu/libs/conv_gemm.py:88-94. */

@@ -68,6 +68,7 @@ PROTOTYPES = {
     "b2c_relu_forward": (c_int, [c_int, c_int64, c_void_p, c_void_p, c_void_p]),
     "b2c_relu_backward": (c_int, [c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
     "b2c_add_inplace": (c_int, [c_int, c_int64, c_void_p, c_void_p, c_void_p]),
+    "b2c_selftest_bounded_wait": (c_int, [c_int64, c_void_p]),
     "b2c_add_relu": (c_int, [c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
     "b2c_add_relu_backward": (c_int, [c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "b2c_pool_forward": (c_int, [c_int] * 15 + [c_void_p, c_void_p, c_void_p, c_void_p]),

@@ -58,6 +58,10 @@ extern "C" int b2c_check_device_status(int* detail) {
     return v ? B2C_ERR_DEVICE_TIMEOUT : B2C_OK;
 }
 
+extern "C" int b2c_selftest_bounded_wait(int64_t limit_cycles, void* stream) {
+    return tc_wait_selftest((long long)limit_cycles, (cudaStream_t)stream);
+}
+
 extern "C" int b2c_conv_engine_for(const b2c_conv_desc* desc, int pass) {
     Geo g; int rc = make_geo(desc, g); if (rc) return rc;
     if (pass < 0 || pass > 2) return B2C_ERR_BAD_ENUM;

@@ -108,6 +108,7 @@ int channel_sum_v4(int n, int c, int hw, const void* src, void* dst, void* ws, s
 
 // tensor-core engine (conv_tc.cu)
 bool tc_supported(const Geo& g, int pass);
+int tc_wait_selftest(long long limit_cycles, cudaStream_t st);
 size_t tc_workspace_bytes(const Geo& g, int pass);
 int tc_fprop(const Geo& g, const void* x, const void* w, const void* bias, const b2c_bn_params* bn, int relu,
              void* y, void* ws, size_t ws_bytes, cudaStream_t st);

@@ -69,7 +69,8 @@ __device__ __forceinline__ bool elect_one_sync() {
 // mbarrier.try_wait suspends the thread in hardware for a short while, so the loop is not hot; the abort
 // flag and the clock are looked at only every 32 failed tries to keep waiting warps off the LSU and the
 // issue ports the working warps need.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
+                                          long long limit_cycles = TC_WAIT_CYCLES) {
     if (mbar_try_wait(bar, parity)) return true;
     long long t0 = 0;
     uint32_t tries = 0;
@@ -79,7 +80,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
             if (*abort_flag) return false;
             const long long now = clock64();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > TC_WAIT_CYCLES) {
+            else if (now - t0 > limit_cycles) {
                 *abort_flag = 1;
                 atomicCAS(status, 0, code);
                 return false;
@@ -217,7 +218,7 @@ __host__ __device__ constexpr uint32_t make_idesc_tf32(int M, int N, int a_mn_ma
 // Device status word shared by all tensor-core kernels (0 = fine).
 __device__ int g_tc_status = 0;
 
-enum { TC_ERR_FULL = 1, TC_ERR_XFORM = 2, TC_ERR_EMPTY = 3, TC_ERR_TFULL = 4, TC_ERR_TEMPTY = 5, TC_ERR_PARTIAL = 6 };
+enum { TC_ERR_FULL = 1, TC_ERR_XFORM = 2, TC_ERR_EMPTY = 3, TC_ERR_TFULL = 4, TC_ERR_TEMPTY = 5, TC_ERR_PARTIAL = 6, TC_ERR_SELFTEST = 7 };
 
 #if defined(B2C_TC_PROFILE) || defined(B2C_TC_SWITCHES)
 #define B2C_TC_DEV 1
@@ -1626,6 +1627,26 @@ extern "C" int b2c_debug_prof(long long* out, int reset)
     return 0;
 }
 #endif
+
+// Self-test of the bounded wait: one warp waits on a barrier nothing arrives at, with a short limit; the wait gives
+// up, records TC_ERR_SELFTEST in the status word and the kernel returns.  Exercises the path the convolution
+// kernels take when a wait runs out, without anything being wrong.
+__global__ void tc_wait_selftest_kernel(long long limit_cycles)
+{
+    pdl_prologue();
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) { mbar_init(&bar, 1); abort_flag = 0; fence_barrier_init(); }
+    __syncthreads();
+    mbar_wait(&bar, 0, &abort_flag, &g_tc_status, TC_ERR_SELFTEST, limit_cycles);
+}
+
+int tc_wait_selftest(long long limit_cycles, cudaStream_t st)
+{
+    if (limit_cycles < 1 || limit_cycles > TC_WAIT_CYCLES) return B2C_ERR_BAD_GEOMETRY;
+    launch_pdl(tc_wait_selftest_kernel, 1, 32, 0, st, limit_cycles);
+    return check_launch("tc_wait_selftest_kernel");
+}
 
 int tc_read_status(int* out)
 {

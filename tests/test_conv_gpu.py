@@ -245,3 +245,23 @@ def test_errors_are_status_codes_not_faults():
     assert L.b2c_conv_wgrad(ctypes.byref(desc), x.data_ptr(), dy.data_ptr(), dw.data_ptr(), None, tiny.data_ptr(), 64,
                             stream()) == -4
     torch.cuda.synchronize()
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_context_stays_usable():
+    """Every in-kernel wait of the tensor-core engine is bounded. Nothing is broken here: a self-test kernel waits on
+    a barrier nothing arrives at, for at most 20 M cycles (about 10 ms); the wait gives up, the kernel returns, the
+    status word reports it once, and the next convolution runs as usual."""
+    L = _lib.lib()
+    L.b2c_check_device_status(None)                       # clear whatever an earlier test may have left
+    _lib.check(L.b2c_selftest_bounded_wait(20_000_000, stream()))
+    detail = ctypes.c_int(0)
+    assert L.b2c_check_device_status(ctypes.byref(detail)) == -9          # B2C_ERR_DEVICE_TIMEOUT
+    assert detail.value == 7
+    assert L.b2c_check_device_status(ctypes.byref(detail)) == 0 and detail.value == 0     # read once, then cleared
+    assert L.b2c_selftest_bounded_wait(0, stream()) == -2                 # limits outside 1..2e9 are refused
+    g = PARITY_SHAPES["cfg1_3x3_64_64_n64"]
+    x, w, b, dy = _inputs(g, np.float32)
+    y = co.conv2d_forward(x, w, b, g, "NHWC", keep={})
+    out = run_conv(g, "NHWC", np.float32, x, w, b, dy, w_layout="KRSC")
+    assert_parity(out["y"], y, np.float32, "conv after a timed-out wait")
+    assert L.b2c_check_device_status(None) == 0
