@@ -1,17 +1,20 @@
 #!/usr/bin/env python
 """Benchmark of the convolution hot path inside a ResNet-50 training step.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload resnet50|vgg16bn|alexnet]
 
 Prints ONE JSON line (rank 0).  ``value`` = images/s of the whole job with the batch already
 resident in HBM, timed on the device with CUDA events (max over ranks); ``e2e`` = the same through
 the public ``Model.train_batch`` call with pinned host buffers, host->device copy and loss read-back
-inside the timed region.  ``roofline`` describes the convolution kernels (the dominant kernels),
-timed live with CUDA events around each launch during the timed steps; ``cpu_baseline`` is the CPU
-path (the reference's compiled Cython kernels + NumPy where ``oracle/_ref`` holds them, else the
-restatement) on a bounded sample of the same workload.
+inside the timed region.  ``roofline`` describes the convolution kernels (the dominant kernels): the
+same K steps are run once more with a CUDA event pair around every Conv2D pass (kept out of the loop
+that gives ``value``: an event between two kernels keeps the second from starting while the first
+drains); ``cpu_baseline`` is the CPU path (the reference's compiled Cython kernels + NumPy where
+``oracle/_ref`` holds them, else the restatement) on a bounded sample of the same workload.
 
 ``--impl reference`` times that CPU path alone, on the host cores, as the reference arm.
+``--conv n,h,w,ci,co,k,stride,pad --conv-pass ...`` times one convolution pass through the C ABI (the
+fixed small cases of the kernel profiles).
 
 Synthetic data: x ~ N(0,1) float32 (64, 224, 224, 3) per GPU, labels uniform in [0, 1000), seeded;
 weights he-uniform from seed 0 (identical replicas).  A step touches several GB of activations, so
