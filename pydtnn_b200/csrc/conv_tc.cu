@@ -8,16 +8,21 @@
 //
 //   fprop : y[pixel][co]  = sum_{tap,c} x[pixel+tap][c]  * w[co][tap][c]
 //   dgrad : dx[pixel][ci] = sum_{tap,c} dy[pixel+tap'][c] * w[c][flip(tap')][ci]   (stride 1)
-//           -- the same kernel run on dy with padding (k-1)*dil - pad and a flipped, transposed
-//              filter copy
+//           -- the same kernel run on dy with padding (k-1)*dil - pad; the flipped tap is a TMA coordinate
+//              into the caller's filter, not a copy
 //   wgrad : dw[co][tap][ci] = sum_pixel x[pixel+tap][ci] * dy[pixel][co]           (split over pixels)
 //
 // 3xTF32: every float32 operand a is split as a = hi + lo with hi = a with the low 13 mantissa bits
 // cleared (what the tensor core reads of a float32 anyway) and lo = a - hi (exact in float32).  Three
 // tensor-core products lo*hi + hi*lo + hi*hi accumulate in the float32 TMEM tile (small terms first).
-// Filters are split once per call by a small kernel.  The A tile (activations; x^T in wgrad) is split by
-// the transform warps, which read it once from shared memory and write hi and lo into tensor memory with
-// tcgen05.st; the MMAs take A from tensor memory and only B from shared memory.
+// The A tile (activations; x^T in wgrad) is split by the transform warps, which read it once from shared
+// memory and write hi and lo into tensor memory with tcgen05.st; the MMAs take A from tensor memory and only B
+// from shared memory.  The B tile (filters; dy in wgrad) is loaded by TMA straight from the caller's tensor and
+// its lo half is written in shared memory by the same warps; long launches and filter layouts without a
+// contiguous channel axis use hi/lo copies written once per call by a small kernel instead.
+//
+// Variants (template parameters): whole tiles or balanced (tile, k-block) ranges with a hand-over of partial
+// tiles between consecutive CTAs; 2 or 4 output slabs per drain warp; NCHW tensors run on channel-last copies.
 //
 // Warp roles (320 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer (both stay
 // converged and issue through one elected lane), warps 2-5 = operand transform,
