@@ -262,13 +262,13 @@ def run_ours(args):
     launches0 = L.b2c_launch_count()
     ms_total = timed(device_step, args.steps)
     launches = L.b2c_launch_count() - launches0
-    clocks = sampler.stop() if rank == 0 else None
     # The same steps once more with a CUDA event pair around every Conv2D pass (the roofline figures). They are
     # kept out of the loop timed above: an event between two kernels stops the second from starting while the
     # first drains, which the unprofiled step is free to do.
     model.conv_profile = []
     ms_profiled = timed(device_step, args.steps)
     prof, model.conv_profile = model.conv_profile, None
+    clocks = sampler.stop() if rank == 0 else None      # sampled over both loops: the same steps, the same load
 
     for _ in range(max(args.warmup, 3)):
         e2e_step()
@@ -431,7 +431,7 @@ def run_single_conv(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
