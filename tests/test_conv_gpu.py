@@ -186,7 +186,11 @@ def test_fc_against_reference_golden_and_oracle(dtype):
 
 @pytest.mark.parametrize("engine", ["auto", "fma"])
 @pytest.mark.parametrize("shape", [(64, 56, 56, 64, 64, 3, 1, 1), (64, 56, 56, 256, 64, 1, 0, 1),
-                                   (64, 28, 28, 128, 128, 3, 1, 2), (64, 14, 14, 256, 1024, 1, 0, 1)])
+                                   (64, 28, 28, 128, 128, 3, 1, 2), (64, 14, 14, 256, 1024, 1, 0, 1),
+                                   # 196 and 100 output tiles on 148 SMs: the balanced (tile, k-block) split
+                                   (64, 14, 14, 256, 256, 3, 1, 1), (64, 7, 7, 512, 512, 3, 1, 1),
+                                   # the network stem: 3 channels, written-out im2row matrix
+                                   (64, 224, 224, 3, 64, 7, 3, 2)])
 def test_full_batch_properties(shape, engine):
     """At the benchmark's batch size the oracle is too slow, so check what holds at any size:
     the three passes are mutually adjoint, <fprop(x,w),dy> = <x,dgrad(dy,w)> = <w,wgrad(x,dy)>,
