@@ -374,18 +374,22 @@ def run_single_conv(args):
     L = _lib.lib()
     torch.cuda.set_device(0)
     ho, wo = (h + 2 * pad - k) // stride + 1, (w + 2 * pad - k) // stride + 1
-    desc = _lib.ConvDesc(_lib.LAYOUT_NHWC, _lib.F32, _lib.W_KRSC, _lib.ENGINE_AUTO, n, h, w, ci, co, k, k, pad, pad,
-                         stride, stride, 1, 1)
+    f64, nchw = args.conv_dtype == "f64", args.conv_layout == "NCHW"
+    tdt, esz = (torch.float64, 8) if f64 else (torch.float32, 4)
+    eng = {"auto": _lib.ENGINE_AUTO, "fma": _lib.ENGINE_FMA, "tensor": _lib.ENGINE_TENSOR}[args.conv_engine]
+    desc = _lib.ConvDesc(_lib.LAYOUT_NCHW if nchw else _lib.LAYOUT_NHWC, _lib.F64 if f64 else _lib.F32,
+                         _lib.W_KCRS if nchw else _lib.W_KRSC, eng, n, h, w, ci, co, k, k, pad, pad, stride, stride, 1, 1)
     pidx = {"fprop": 0, "dgrad": 1, "wgrad": 2}[args.conv_pass]
     engine = L.b2c_conv_engine_for(ctypes.byref(desc), pidx)
     nb = max(L.b2c_conv_workspace_bytes(ctypes.byref(desc), p) for p in range(3))
     ws = torch.empty(max(int(nb), 256), dtype=torch.uint8, device="cuda")
-    bytes_x, bytes_y = n * h * w * ci * 4, n * ho * wo * co * 4
+    bytes_x, bytes_y = n * h * w * ci * esz, n * ho * wo * co * esz
     nbuf = max(2, int(256e6 // max(bytes_x + bytes_y, 1)) + 1)          # rotate through > 2x L2
     gen = torch.Generator(device="cuda").manual_seed(0)
-    xs = [torch.randn((n, h, w, ci), device="cuda", generator=gen) for _ in range(nbuf)]
-    ys = [torch.randn((n, ho, wo, co), device="cuda", generator=gen) for _ in range(nbuf)]
-    wt = torch.randn((co, k, k, ci), device="cuda", generator=gen) * (2.0 / (ci * k * k)) ** 0.5
+    xshape, yshape = ((n, ci, h, w), (n, co, ho, wo)) if nchw else ((n, h, w, ci), (n, ho, wo, co))
+    xs = [torch.randn(xshape, device="cuda", generator=gen, dtype=tdt) for _ in range(nbuf)]
+    ys = [torch.randn(yshape, device="cuda", generator=gen, dtype=tdt) for _ in range(nbuf)]
+    wt = torch.randn((co, ci, k, k) if nchw else (co, k, k, ci), device="cuda", generator=gen, dtype=tdt) * (2.0 / (ci * k * k)) ** 0.5
     dw = torch.empty_like(wt)
     st = torch.cuda.current_stream().cuda_stream
 
@@ -413,17 +417,21 @@ def run_single_conv(args):
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / args.steps
     flops = 2.0 * n * ho * wo * co * ci * k * k
-    min_bytes = 4.0 * (n * h * w * ci + k * k * ci * co + n * ho * wo * co)
+    min_bytes = float(esz) * (n * h * w * ci + k * k * ci * co + n * ho * wo * co)
     peaks = measured_peaks()
-    peak = peaks["bf16"] / 6.0
+    on_tc = engine == _lib.ENGINE_TENSOR
+    # tensor-core engine: measured bf16 / 2 / 3.  FMA engine: nominal FMA peaks of the part (148 SMs x 128 lanes x 2
+    # flops x 1.965 GHz = 74.4 TFLOP/s float32, half of that float64); no measured figure for these exists here.
+    peak = peaks["bf16"] / 6.0 if on_tc else (37.2 if f64 else 74.4)
     tflops = flops / (ms * 1e-3) / 1e12
     print(json.dumps({
         "metric": "conv_pass_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"conv2d_{args.conv_pass}", "shape": args.conv, "tensor_format": "NHWC",
-                   "engine": "tensor" if engine == _lib.ENGINE_TENSOR else "fma", "l2": f"{nbuf} rotating buffer sets"},
-        "roofline": {"bound": "tensor", "achieved": tflops, "peak": peak, "unit": "TFLOP/s", "frac": tflops / peak,
-                     "peak_basis": f"{peaks['source']} bf16 burst {peaks['bf16']:.1f} / 2 / 3 (kernel timed alone)",
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "dtype": args.conv_dtype, "data": "synthetic",
+        "config": {"workload": f"conv2d_{args.conv_pass}", "shape": args.conv, "tensor_format": args.conv_layout,
+                   "engine": "tensor" if on_tc else "fma", "l2": f"{nbuf} rotating buffer sets"},
+        "roofline": {"bound": "tensor" if on_tc else "fma", "achieved": tflops, "peak": peak, "unit": "TFLOP/s", "frac": tflops / peak,
+                     "peak_basis": (f"{peaks['source']} bf16 burst {peaks['bf16']:.1f} / 2 / 3 (kernel timed alone)" if on_tc
+                                    else "nominal FMA peak: 148 SMs x 128 lanes x 2 x 1.965 GHz" + (" / 2 (float64)" if f64 else "")),
                      "min_bytes": min_bytes, "hbm_gbs_at_min_bytes": min_bytes / (ms * 1e-3) / 1e9,
                      "arithmetic_intensity": flops / min_bytes}}), flush=True)
 
@@ -440,6 +448,9 @@ def main():
     ap.add_argument("--layers", action="store_true", help="add per-layer convolution timings to the JSON line")
     ap.add_argument("--conv", default=None, help="n,h,w,ci,co,k,stride,pad: time one Conv2D pass instead of the model")
     ap.add_argument("--conv-pass", default="fprop", choices=["fprop", "dgrad", "wgrad"])
+    ap.add_argument("--conv-dtype", default="f32", choices=["f32", "f64"])
+    ap.add_argument("--conv-layout", default="NHWC", choices=["NHWC", "NCHW"])
+    ap.add_argument("--conv-engine", default="auto", choices=["auto", "fma", "tensor"])
     args = ap.parse_args()
     if args.conv:
         run_single_conv(args)
