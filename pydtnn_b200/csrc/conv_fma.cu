@@ -202,13 +202,24 @@ igemm_kernel(IgemmParams p, const T* __restrict__ A, const T* __restrict__ B, T*
             lds4<T>(&As[cur][k][BM / 2 + ty * 4], t4);
 #pragma unroll
             for (int i = 0; i < 4; i++) a[4 + i] = t4[i];
-            lds4<T>(&Bs[cur][k][tx * 4], t4);
+            if (sizeof(T) == 8) {
+                // doubles: two columns per 16-byte load, column pairs 32 apart, so that the 16 lanes of a row of the
+                // thread grid read consecutive 16-byte words (four columns per thread would stride them 32 bytes
+                // apart: a 4-way bank conflict)
 #pragma unroll
-            for (int j = 0; j < 4; j++) b[j] = t4[j];
-            if (TN == 8) {
-                lds4<T>(&Bs[cur][k][BN / 2 + tx * 4], t4);
+                for (int g = 0; g < TN / 2; g++) {
+                    const double2 v = *reinterpret_cast<const double2*>(&Bs[cur][k][g * 32 + tx * 2]);
+                    b[2 * g] = (T)v.x; b[2 * g + 1] = (T)v.y;
+                }
+            } else {
+                lds4<T>(&Bs[cur][k][tx * 4], t4);
 #pragma unroll
-                for (int j = 0; j < 4; j++) b[(TN == 8 ? 4 : 0) + j] = t4[j];
+                for (int j = 0; j < 4; j++) b[j] = t4[j];
+                if (TN == 8) {
+                    lds4<T>(&Bs[cur][k][BN / 2 + tx * 4], t4);
+#pragma unroll
+                    for (int j = 0; j < 4; j++) b[(TN == 8 ? 4 : 0) + j] = t4[j];
+                }
             }
 #pragma unroll
             for (int i = 0; i < 8; i++)
@@ -234,7 +245,7 @@ igemm_kernel(IgemmParams p, const T* __restrict__ A, const T* __restrict__ B, T*
         const int64_t row_off = rowinfo[rl].b_off;
 #pragma unroll
         for (int j = 0; j < TN; j++) {
-            int cl = (j < 4) ? (tx * 4 + j) : (BN / 2 + tx * 4 + j - 4);
+            int cl = sizeof(T) == 8 ? ((j >> 1) * 32 + tx * 2 + (j & 1)) : ((j < 4) ? (tx * 4 + j) : (BN / 2 + tx * 4 + j - 4));
             int n = n0 + cl;
             if (n >= p.N) continue;
             if (p.splits > 1) partial[((int64_t)blockIdx.z * p.M + m) * p.N + n] = acc[i][j];
