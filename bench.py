@@ -436,6 +436,115 @@ def run_single_conv(args):
                      "arithmetic_intensity": flops / min_bytes}}), flush=True)
 
 
+SWEEP_AXES = ((7, 14, 28, 56, 112), (64, 128, 256, 512), (64, 128, 256, 512), (1, 3, 5, 7), (1, 2))
+
+
+def sweep_points():
+    """The shape sweep: batch 32, H=W x Ci x Co x kernel x stride, 'same' padding, dilation 1 (640 geometries)."""
+    import itertools
+    return [(32, hw, hw, ci, co, k, s, (k - 1) // 2) for hw, ci, co, k, s in itertools.product(*SWEEP_AXES)]
+
+
+def run_sweep(args):
+    """Every geometry of the shape sweep x {float32, float64} x {NHWC, NCHW} x {fprop, dgrad, wgrad} through the
+    C ABI on device-resident synthetic tensors.  Each point: 2 warm-up calls, then `--sweep-iters` calls between one
+    CUDA-event pair, operands rotating through more than 2x the L2 size (one set when a tensor alone is larger).
+    Writes one CSV row per point to `--out` and prints one JSON line with the distribution of the roofline
+    fractions.  The bound of a point is min(compute peak, arithmetic intensity x measured HBM bandwidth); the
+    compute peak is measured bf16 burst / 2 / 3 for float32 and the nominal FMA figure for float64."""
+    import ctypes
+    import statistics
+    import torch
+    from pydtnn_b200 import _lib
+    L = _lib.lib()
+    torch.cuda.set_device(0)
+    peaks = measured_peaks()
+    st = torch.cuda.current_stream().cuda_stream
+    pts = sweep_points()
+    if args.sweep_limit:
+        pts = pts[:: max(1, len(pts) // args.sweep_limit)][: args.sweep_limit]
+    combos = [(d, l) for d in args.sweep_dtypes.split(",") for l in args.sweep_layouts.split(",")]
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    rows, launches0 = [], L.b2c_launch_count()
+    for dname, layout in combos:
+        f64, nchw = dname == "f64", layout == "NCHW"
+        tdt, esz = (torch.float64, 8) if f64 else (torch.float32, 4)
+        biggest = max(max(n * h * w * ci, n * ((h + 2 * p - k) // s + 1) ** 2 * co) for n, h, w, ci, co, k, s, p in pts)
+        pool_el = max(biggest, int(320e6) // esz)
+        # inputs come from two pools that no call writes, results go to a third: values never feed back
+        xin = torch.randn(pool_el, device="cuda", generator=gen, dtype=tdt)
+        yin = torch.randn(pool_el, device="cuda", generator=gen, dtype=tdt)
+        out = torch.empty(pool_el, device="cuda", dtype=tdt)
+        peak = 37.2 if f64 else peaks["bf16"] / 6.0
+        for n, h, w, ci, co, k, s, p in pts:
+            ho = wo = (h + 2 * p - k) // s + 1
+            desc = _lib.ConvDesc(_lib.LAYOUT_NCHW if nchw else _lib.LAYOUT_NHWC, _lib.F64 if f64 else _lib.F32,
+                                 _lib.W_KCRS if nchw else _lib.W_KRSC, _lib.ENGINE_AUTO, n, h, w, ci, co, k, k, p, p, s, s, 1, 1)
+            nb = max(L.b2c_conv_workspace_bytes(ctypes.byref(desc), q) for q in range(3))
+            ws = torch.empty(max(int(nb), 256), dtype=torch.uint8, device="cuda")
+            xel, yel, wel = n * h * w * ci, n * ho * wo * co, co * k * k * ci
+            nbuf = max(1, min(pool_el // max(xel, yel), int(256e6 // ((xel + yel) * esz)) + 1))
+            wt = torch.randn(wel, device="cuda", generator=gen, dtype=tdt) * (2.0 / (ci * k * k)) ** 0.5
+            dw = torch.empty_like(wt)
+            flops = 2.0 * n * ho * wo * co * ci * k * k
+            min_bytes = float(esz) * (xel + wel + yel)
+            bound = min(peak, flops / min_bytes * peaks["hbm_gbs"] / 1e3)
+            for pidx, pname in enumerate(("fprop", "dgrad", "wgrad")):
+                engine = L.b2c_conv_engine_for(ctypes.byref(desc), pidx)
+
+                def call(i):
+                    j = i % nbuf
+                    xa, ya = xin.data_ptr() + j * xel * esz, yin.data_ptr() + j * yel * esz
+                    if pidx == 0:
+                        rc = L.b2c_conv_fprop(ctypes.byref(desc), xa, wt.data_ptr(), None, None, 0,
+                                              out.data_ptr() + j * yel * esz, ws.data_ptr(), ws.numel(), st)
+                    elif pidx == 1:
+                        rc = L.b2c_conv_dgrad(ctypes.byref(desc), ya, wt.data_ptr(), out.data_ptr() + j * xel * esz,
+                                              ws.data_ptr(), ws.numel(), st)
+                    else:
+                        rc = L.b2c_conv_wgrad(ctypes.byref(desc), xa, ya, dw.data_ptr(), None, ws.data_ptr(), ws.numel(), st)
+                    _lib.check(rc)
+
+                for i in range(2):
+                    call(i)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for i in range(args.sweep_iters):
+                    call(2 + i)
+                e1.record()
+                e1.synchronize()
+                ms = e0.elapsed_time(e1) / args.sweep_iters
+                tf = flops / (ms * 1e-3) / 1e12
+                rows.append((dname, layout, pname, h, ci, co, k, s, "tensor" if engine == _lib.ENGINE_TENSOR else "fma",
+                             ms, tf, flops / min_bytes, bound, tf / bound))
+        torch.cuda.synchronize()
+        _lib.check(L.b2c_check_device_status(ctypes.byref(ctypes.c_int(0))))
+        del xin, yin, out
+        torch.cuda.empty_cache()
+    if args.out:
+        with open(args.out, "w") as f:
+            f.write("dtype,layout,pass,hw,ci,co,k,stride,engine,ms,tflops,flop_per_byte,bound_tflops,frac_of_bound\n")
+            for r in rows:
+                f.write("%s,%s,%s,%d,%d,%d,%d,%d,%s,%.5f,%.3f,%.2f,%.2f,%.4f\n" % r)
+    summary = {}
+    for dname, layout in combos:
+        for pname in ("fprop", "dgrad", "wgrad"):
+            sel = [r for r in rows if r[0] == dname and r[1] == layout and r[2] == pname]
+            fr = sorted(r[13] for r in sel)
+            summary[f"{dname} {layout} {pname}"] = {
+                "points": len(sel), "median_tflops": statistics.median(r[10] for r in sel),
+                "max_tflops": max(r[10] for r in sel), "median_frac": statistics.median(fr),
+                "p10_frac": fr[len(fr) // 10], "min_frac": fr[0], "share_at_or_above_0.6": sum(v >= 0.6 for v in fr) / len(fr),
+                "on_tensor_engine": sum(r[8] == "tensor" for r in sel)}
+    print(json.dumps({
+        "metric": "conv_sweep_roofline_frac", "unit": "fraction of min(compute peak, intensity x HBM)", "n_gpus": 1,
+        "data": "synthetic", "higher_is_better": True, "points": len(rows), "iters_per_point": args.sweep_iters,
+        "gpu_launches": L.b2c_launch_count() - launches0,
+        "peaks": {"f32_tflops": peaks["bf16"] / 6.0, "f64_tflops": 37.2, "hbm_gbs": peaks["hbm_gbs"], "source": peaks["source"]},
+        "config": {"workload": "conv2d shape sweep, batch 32", "l2": "operands rotate through > 2x L2"},
+        "summary": summary}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -451,7 +560,16 @@ def main():
     ap.add_argument("--conv-dtype", default="f32", choices=["f32", "f64"])
     ap.add_argument("--conv-layout", default="NHWC", choices=["NHWC", "NCHW"])
     ap.add_argument("--conv-engine", default="auto", choices=["auto", "fma", "tensor"])
+    ap.add_argument("--sweep", action="store_true", help="time the whole Conv2D shape sweep instead of the model")
+    ap.add_argument("--sweep-dtypes", default="f32,f64")
+    ap.add_argument("--sweep-layouts", default="NHWC,NCHW")
+    ap.add_argument("--sweep-iters", type=int, default=3)
+    ap.add_argument("--sweep-limit", type=int, default=0, help="time only about this many evenly spaced geometries")
+    ap.add_argument("--out", default=None, help="CSV file for the per-point rows of --sweep")
     args = ap.parse_args()
+    if args.sweep:
+        run_sweep(args)
+        return
     if args.conv:
         run_single_conv(args)
         return

@@ -36,6 +36,11 @@ struct IgemmParams {
     int a_lanes_k, b_lanes_k;     // which index runs fastest across lanes when loading A / B
     int k_chunk, splits;
     int relu;
+    // Sub-lattices (strided dgrad runs one launch per residue class of the output pixels, each with the taps that
+    // reach it): pixel (pp, qq) of the grid is row pix_h0 + pp*pix_hs, column pix_w0 + qq*pix_ws of the tensor;
+    // tap (r, s) of the (R, S) grid is filter tap (tap_r0 + r*tap_rs, tap_s0 + s*tap_ss).  Identity elsewhere.
+    int pix_h0, pix_hs, pix_w0, pix_ws;
+    int tap_r0, tap_rs, tap_s0, tap_ss;
 };
 
 template <typename T> struct Epilogue { const T *bias, *mean, *inv_std, *gamma, *beta; int relu; };
@@ -44,6 +49,7 @@ template <int MODE> __device__ __forceinline__ Info decode_pix(const IgemmParams
     Info f;
     if (idx >= limit) { f.a_off = 0; f.b_off = 0; f.d0 = -B2C_SENTINEL; f.d1 = 0; return f; }
     int n = idx / p.PQ; int rem = idx - n * p.PQ; int pp = rem / p.Q; int qq = rem - pp * p.Q;
+    pp = p.pix_h0 + pp * p.pix_hs; qq = p.pix_w0 + qq * p.pix_ws;
     f.a_off = (int64_t)n * p.a_sn;
     f.b_off = (int64_t)n * p.pb_sn + (int64_t)pp * p.pb_sh + (int64_t)qq * p.pb_sw;
     if (MODE == MODE_DGRAD) { f.d0 = pp + p.vpad; f.d1 = qq + p.hpad; }
@@ -57,6 +63,7 @@ template <int MODE> __device__ __forceinline__ Info decode_tap(const IgemmParams
     int c, r, s;
     if (p.tap_c_fast) { c = idx % p.C; int rs = idx / p.C; r = rs / p.S; s = rs - r * p.S; }
     else { int RS = p.R * p.S; c = idx / RS; int rs = idx - c * RS; r = rs / p.S; s = rs - r * p.S; }
+    r = p.tap_r0 + r * p.tap_rs; s = p.tap_s0 + s * p.tap_ss;
     f.a_off = (int64_t)c * p.a_sc;
     f.b_off = (int64_t)c * p.tb_sc + (int64_t)r * p.tb_sr + (int64_t)s * p.tb_ss;
     f.d0 = r * p.vdil; f.d1 = s * p.hdil;
@@ -298,6 +305,8 @@ static IgemmParams make_params(const Geo& g, int mode)
     p.R = g.kh; p.S = g.kw;
     p.vstr = g.vstr; p.hstr = g.hstr; p.vpad = g.vpad; p.hpad = g.hpad; p.vdil = g.vdil; p.hdil = g.hdil;
     p.relu = 0; p.splits = 1;
+    p.pix_h0 = 0; p.pix_hs = 1; p.pix_w0 = 0; p.pix_ws = 1;
+    p.tap_r0 = 0; p.tap_rs = 1; p.tap_s0 = 0; p.tap_ss = 1;
     if (mode == MODE_FPROP) {
         p.M = (int)g.M; p.N = g.co; p.K = (int)g.K;
         p.P = g.ho; p.Q = g.wo; p.C = g.ci; p.H = g.h; p.W = g.w;
@@ -346,6 +355,7 @@ static int choose_splits(const IgemmParams& p, int bk)
 static void finish_params(IgemmParams& p, int dtype)
 {
     int bk = dtype == B2C_F32 ? 16 : 8;
+    if (p.K <= 0) { p.splits = 1; p.k_chunk = bk; return; }        // no taps reach these pixels: the launch writes zeros
     p.splits = choose_splits(p, bk);
     int chunk = (p.K + p.splits - 1) / p.splits;
     chunk = (chunk + bk - 1) / bk * bk;
@@ -353,11 +363,44 @@ static void finish_params(IgemmParams& p, int dtype)
     p.splits = (p.K + chunk - 1) / chunk;
 }
 
+// Strided dgrad, dilation 1: input pixel (h, w) only receives taps with r = (h + vpad) mod vstr, s = (w + hpad) mod hstr
+// (mod the strides).  Class (a, b) of those residues is a dense problem over its own pixels and taps; gathering all
+// taps for all pixels instead would spend (vstr*hstr - 1) / (vstr*hstr) of the inner loop on zeros.
+static bool dgrad_by_class(const Geo& g) { return (g.vstr > 1 || g.hstr > 1) && g.vdil == 1 && g.hdil == 1; }
+
+static IgemmParams dgrad_class_params(const Geo& g, int a, int b)
+{
+    IgemmParams p = make_params(g, MODE_DGRAD);
+    const int h0 = ((a - g.vpad) % g.vstr + g.vstr) % g.vstr, w0 = ((b - g.hpad) % g.hstr + g.hstr) % g.hstr;
+    p.pix_h0 = h0; p.pix_hs = g.vstr; p.pix_w0 = w0; p.pix_ws = g.hstr;
+    p.P = h0 < g.h ? (g.h - h0 + g.vstr - 1) / g.vstr : 0;
+    p.Q = w0 < g.w ? (g.w - w0 + g.hstr - 1) / g.hstr : 0;
+    p.PQ = p.P * p.Q;
+    p.M = g.n * p.PQ;
+    p.tap_r0 = a; p.tap_rs = g.vstr; p.tap_s0 = b; p.tap_ss = g.hstr;
+    p.R = a < g.kh ? (g.kh - a + g.vstr - 1) / g.vstr : 0;
+    p.S = b < g.kw ? (g.kw - b + g.hstr - 1) / g.hstr : 0;
+    p.K = g.co * p.R * p.S;
+    return p;
+}
+
 size_t fma_workspace_bytes(const Geo& g, int pass)
 {
+    size_t es = g.dtype == B2C_F32 ? 4 : 8;
+    if (pass == B2C_PASS_DGRAD && dgrad_by_class(g)) {
+        size_t most = 0;
+        for (int a = 0; a < g.vstr; a++)
+            for (int b = 0; b < g.hstr; b++) {
+                IgemmParams p = dgrad_class_params(g, a, b);
+                if (p.M == 0) continue;
+                finish_params(p, g.dtype);
+                size_t bytes = p.splits > 1 ? (size_t)p.splits * p.M * p.N * es : 0;
+                if (bytes > most) most = bytes;
+            }
+        return most;
+    }
     IgemmParams p = make_params(g, pass);
     finish_params(p, g.dtype);
-    size_t es = g.dtype == B2C_F32 ? 4 : 8;
     size_t bytes = p.splits > 1 ? (size_t)p.splits * p.M * p.N * es : 0;
     if (pass == B2C_PASS_WGRAD) bytes = align_up(bytes, 256) + channel_sum_workspace_bytes(g.n, g.co, g.ho * g.wo);
     return bytes;
@@ -407,6 +450,18 @@ int fma_fprop(const Geo& g, const void* x, const void* w, const void* bias, cons
 
 int fma_dgrad(const Geo& g, const void* dy, const void* w, void* dx, void* ws, size_t ws_bytes, cudaStream_t st)
 {
+    if (dgrad_by_class(g)) {
+        for (int a = 0; a < g.vstr; a++)
+            for (int b = 0; b < g.hstr; b++) {
+                IgemmParams p = dgrad_class_params(g, a, b);
+                if (p.M == 0) continue;
+                int rc = g.dtype == B2C_F32
+                    ? launch_igemm<float, MODE_DGRAD>(p, dy, w, dx, ws, ws_bytes, Epilogue<float>{}, st)
+                    : launch_igemm<double, MODE_DGRAD>(p, dy, w, dx, ws, ws_bytes, Epilogue<double>{}, st);
+                if (rc) return rc;
+            }
+        return B2C_OK;
+    }
     IgemmParams p = make_params(g, MODE_DGRAD);
     if (g.dtype == B2C_F32) return launch_igemm<float, MODE_DGRAD>(p, dy, w, dx, ws, ws_bytes, Epilogue<float>{}, st);
     return launch_igemm<double, MODE_DGRAD>(p, dy, w, dx, ws, ws_bytes, Epilogue<double>{}, st);

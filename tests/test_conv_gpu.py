@@ -79,6 +79,9 @@ PARITY_SHAPES = {
     "sweep_7x7_28": co.Geom(2, 28, 28, 64, 64, 7, 7, 3, 3, 1, 1),
     "dilated_3x3": co.Geom(2, 20, 20, 16, 24, 3, 3, 2, 2, 1, 1, 2, 2),
     "ragged_everything": co.Geom(3, 13, 11, 7, 5, 3, 2, 1, 0, 2, 1, 1, 1),
+    # strides that differ, extents the strides do not divide, a kernel narrower than the stride in one direction:
+    # some residue classes of the input pixels have no tap at all (their gradient is zero)
+    "stride_3x2_odd_extent": co.Geom(2, 17, 13, 8, 12, 2, 5, 1, 2, 3, 2),
     "single_pixel": co.Geom(1, 1, 1, 1, 1, 1, 1, 0, 0, 1, 1),
     "pad_larger_than_input": co.Geom(1, 2, 2, 3, 2, 3, 3, 2, 2, 1, 1),
     # tile counts that do not fill the CTA grid evenly: the tensor-core kernel balances (tile, k-block) units over
@@ -119,7 +122,8 @@ def test_float32_nhwc_against_oracle(name, engine):
 
 @pytest.mark.parametrize("layout,dtype", [("NCHW", "float32"), ("NHWC", "float64"), ("NCHW", "float64")])
 @pytest.mark.parametrize("name", ["cfg1_3x3_64_64_n64", "resnet_3x3s2_128", "resnet_1x1_64_256", "sweep_5x5s2_14",
-                                  "dilated_3x3", "ragged_everything", "alexnet_conv1_11x11s4"])
+                                  "dilated_3x3", "ragged_everything", "alexnet_conv1_11x11s4", "resnet_1x1s2_256_512",
+                                  "stride_3x2_odd_extent"])
 def test_other_layouts_and_float64_against_oracle(name, layout, dtype):
     g = PARITY_SHAPES[name]
     if name == "cfg1_3x3_64_64_n64":
