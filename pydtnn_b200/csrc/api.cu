@@ -10,9 +10,21 @@ void set_cuda_error(cudaError_t e, const char* where) {
     snprintf(g_cuda_err, sizeof(g_cuda_err), "%s: %s", where, cudaGetErrorString(e));
 }
 
+// Shapes the tensor-core kernels accept but the FMA engine runs faster (measured on fully connected layers at
+// batch 32-64): a weight gradient summed over a handful of pixels is an outer product bound by writing dw, which the
+// FMA engine's dense kernel does at HBM speed; a GEMM with one 128-row tile and at most eight column tiles leaves
+// each tile to ~18 CTAs of the balanced mode, whose partial tiles the owner adds one after the other.
+static bool fma_is_faster(const Geo& g, int pass) {
+    const bool one_pixel_images = g.h == 1 && g.w == 1 && g.kh == 1 && g.kw == 1 && g.vpad == 0 && g.hpad == 0;
+    if (!one_pixel_images || g.n > 128) return false;
+    if (pass == B2C_PASS_WGRAD) return true;
+    return (pass == B2C_PASS_FPROP ? g.co : g.ci) <= 1024;
+}
+
 // FMA for everything unless the tensor-core engine takes the shape (AUTO) or is forced.
 static int pick_engine(const Geo& g, int pass, int& engine) {
     bool tc = tc_supported(g, pass);
+    if (g.engine == B2C_ENGINE_AUTO && tc && fma_is_faster(g, pass)) tc = false;
     if (g.engine == B2C_ENGINE_TENSOR) { if (!tc) return B2C_ERR_UNSUPPORTED; engine = B2C_ENGINE_TENSOR; }
     else if (g.engine == B2C_ENGINE_FMA) engine = B2C_ENGINE_FMA;
     else engine = tc ? B2C_ENGINE_TENSOR : B2C_ENGINE_FMA;

@@ -293,6 +293,112 @@ __global__ void index_map_kernel(IgemmParams p, int64_t* __restrict__ map, int n
     map[idx] = ok ? off : -1;
 }
 
+// ---- fully connected layer: weight gradient as an outer-product sum ---------------------------------
+// dw[i][o] = sum_b x[b][i] * dy[b][o] for a (batch, in) input, a (batch, out) output gradient and an (in, out)
+// row-major weight matrix (pydtnn/backends/cpu/layers/fc_cpu.py:66-71).  The sum is over the batch only (32-64
+// terms), so the pass is bound by writing dw; the general kernel above spends its time on gather arithmetic that a
+// dense matrix does not need.  One CTA = one 128 x 128 tile of dw, all of the batch, 8 x 8 outputs per thread.
+template <typename T> __device__ __forceinline__ void ldg4(const T* p, T (&o)[4]);
+template <> __device__ __forceinline__ void ldg4<float>(const float* p, float (&o)[4]) {
+    float4 v = __ldg(reinterpret_cast<const float4*>(p)); o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
+}
+template <> __device__ __forceinline__ void ldg4<double>(const double* p, double (&o)[4]) {
+    double2 a = __ldg(reinterpret_cast<const double2*>(p)), b = __ldg(reinterpret_cast<const double2*>(p) + 1);
+    o[0] = a.x; o[1] = a.y; o[2] = b.x; o[3] = b.y;
+}
+template <typename T> __device__ __forceinline__ void sts4(T* p, const T (&v)[4]);
+template <> __device__ __forceinline__ void sts4<float>(float* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+template <> __device__ __forceinline__ void sts4<double>(double* p, const double (&v)[4]) {
+    *reinterpret_cast<double2*>(p) = make_double2(v[0], v[1]); *reinterpret_cast<double2*>(p + 2) = make_double2(v[2], v[3]);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+fc_wgrad_kernel(const T* __restrict__ x, const T* __restrict__ dy, T* __restrict__ dw, int batch, int in_f, int out_f)
+{
+    pdl_prologue();
+    constexpr int BT = 128, KC = TileCfg<T>::BK, PER = KC * BT / 4 / 256;     // 4-element vectors per thread per tile
+    __shared__ __align__(16) T xs[2][KC][BT];
+    __shared__ __align__(16) T ds[2][KC][BT];
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const int o0 = blockIdx.x * BT, i0 = blockIdx.y * BT;
+    T rx[PER][4], rd[PER][4];
+    auto fetch = [&](int b0) {
+#pragma unroll
+        for (int j = 0; j < PER; j++) {
+            const int v = tid + j * 256, k = v / (BT / 4), col = (v % (BT / 4)) * 4;
+            const bool row_ok = b0 + k < batch;
+            if (row_ok && i0 + col < in_f) ldg4<T>(x + (int64_t)(b0 + k) * in_f + i0 + col, rx[j]);
+            else { rx[j][0] = rx[j][1] = rx[j][2] = rx[j][3] = T(0); }
+            if (row_ok && o0 + col < out_f) ldg4<T>(dy + (int64_t)(b0 + k) * out_f + o0 + col, rd[j]);
+            else { rd[j][0] = rd[j][1] = rd[j][2] = rd[j][3] = T(0); }
+        }
+    };
+    auto stash = [&](int buf) {
+#pragma unroll
+        for (int j = 0; j < PER; j++) {
+            const int v = tid + j * 256, k = v / (BT / 4), col = (v % (BT / 4)) * 4;
+            sts4<T>(&xs[buf][k][col], rx[j]);
+            sts4<T>(&ds[buf][k][col], rd[j]);
+        }
+    };
+    T acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[i][j] = T(0);
+    const int nchunk = (batch + KC - 1) / KC;
+    fetch(0);
+    stash(0);
+    __syncthreads();
+    for (int c = 0; c < nchunk; c++) {
+        const int cur = c & 1;
+        if (c + 1 < nchunk) fetch((c + 1) * KC);
+#pragma unroll
+        for (int k = 0; k < KC; k++) {
+            T a[8], b[8], t4[4];
+            lds4<T>(&xs[cur][k][ty * 4], t4);
+#pragma unroll
+            for (int i = 0; i < 4; i++) a[i] = t4[i];
+            lds4<T>(&xs[cur][k][BT / 2 + ty * 4], t4);
+#pragma unroll
+            for (int i = 0; i < 4; i++) a[4 + i] = t4[i];
+            lds4<T>(&ds[cur][k][tx * 4], t4);
+#pragma unroll
+            for (int j = 0; j < 4; j++) b[j] = t4[j];
+            lds4<T>(&ds[cur][k][BT / 2 + tx * 4], t4);
+#pragma unroll
+            for (int j = 0; j < 4; j++) b[4 + j] = t4[j];
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+#pragma unroll
+                for (int j = 0; j < 8; j++) acc[i][j] = fma(a[i], b[j], acc[i][j]);
+        }
+        if (c + 1 < nchunk) stash(cur ^ 1);
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int row = i0 + ((i < 4) ? (ty * 4 + i) : (BT / 2 + ty * 4 + i - 4));
+        if (row >= in_f) continue;
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int col = o0 + h * (BT / 2) + tx * 4;
+            if (col >= out_f) continue;
+            const T v[4] = {acc[i][4 * h], acc[i][4 * h + 1], acc[i][4 * h + 2], acc[i][4 * h + 3]};
+            sts4<T>(dw + (int64_t)row * out_f + col, v);
+        }
+    }
+}
+
+static bool is_dense_fc(const Geo& g)
+{
+    return g.layout == B2C_LAYOUT_NHWC && g.w_layout == B2C_W_CRSK && g.h == 1 && g.w == 1 && g.kh == 1 && g.kw == 1 &&
+           g.vpad == 0 && g.hpad == 0 && g.ci % 4 == 0 && g.co % 4 == 0;
+}
+
 // ---- host side ----------------------------------------------------------------------------
 
 static IgemmParams make_params(const Geo& g, int mode)
@@ -470,6 +576,18 @@ int fma_dgrad(const Geo& g, const void* dy, const void* w, void* dx, void* ws, s
 int fma_wgrad(const Geo& g, const void* x, const void* dy, void* dw, void* db, void* ws, size_t ws_bytes,
               cudaStream_t st)
 {
+    const size_t align = g.dtype == B2C_F32 ? 15 : 31;
+    if (is_dense_fc(g) && !(((uintptr_t)x | (uintptr_t)dy | (uintptr_t)dw) & align)) {
+        dim3 grid((g.co + 127) / 128, (g.ci + 127) / 128);
+        if (grid.y > 65535) return B2C_ERR_TOO_LARGE;
+        if (g.dtype == B2C_F32) launch_pdl(fc_wgrad_kernel<float>, grid, 256, 0, st, (const float*)x, (const float*)dy, (float*)dw, g.n, g.ci, g.co);
+        else launch_pdl(fc_wgrad_kernel<double>, grid, 256, 0, st, (const double*)x, (const double*)dy, (double*)dw, g.n, g.ci, g.co);
+        int rc = check_launch("fc_wgrad_kernel");
+        if (rc || !db) return rc;
+        size_t cs = channel_sum_workspace_bytes(g.n, g.co, 1);
+        if (!ws || ws_bytes < cs) return B2C_ERR_WORKSPACE_TOO_SMALL;
+        return channel_sum(g.dtype, g.layout, g.n, g.co, 1, dy, db, ws, cs, st);
+    }
     IgemmParams p = make_params(g, MODE_WGRAD);
     finish_params(p, g.dtype);
     size_t es = g.dtype == B2C_F32 ? 4 : 8;

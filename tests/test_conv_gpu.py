@@ -163,7 +163,8 @@ def test_fc_against_reference_golden_and_oracle(dtype):
     ref = np.load(os.path.join(GOLD, "fc_ref.npz"))
     cases = [tuple(ref[f"f{i}_{dtype}_{n}"] for n in ("x", "w", "b", "dy", "y", "dw", "db", "dx")) for i in range(3)]
     rng = np.random.Generator(np.random.PCG64(3))
-    for (bsz, fin, fout) in ((64, 2048, 1000), (32, 1000, 4096), (5, 7, 3)):
+    # the last two: tensor-core forward and input gradient; partial tiles and a ragged batch in the dense dw kernel
+    for (bsz, fin, fout) in ((64, 2048, 1000), (32, 1000, 4096), (5, 7, 3), (64, 4096, 2048), (21, 200, 132)):
         x = rng.standard_normal((bsz, fin)).astype(dtype)
         w = (rng.standard_normal((fin, fout)) / np.sqrt(fin)).astype(dtype)
         b = rng.standard_normal((fout,)).astype(dtype)
