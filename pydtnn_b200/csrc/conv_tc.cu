@@ -540,7 +540,7 @@ __global__ void __launch_bounds__(320, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b0,
                const __grid_constant__ CUtensorMap tmap_b1, const __grid_constant__ CUtensorMap tmap_out, TcParams p)
 {
-    pdl_prologue();
+    pdl_launch_dependents();
     // Persistent: each CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ... (column tile fastest, so
     // CTAs running at the same time share activation rows in L2).  The smem pipeline and the two TMEM
     // buffers keep running across tile boundaries: the producer prefetches the next tile while the
@@ -574,8 +574,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         fence_proxy_async();
     }
     if (warp == 1) { tmem_alloc(tmem_slot, L::TMEM_COLS); tmem_relinquish(); }
-    // barriers, tensor memory and the abort flag are on-chip state; global memory is first touched below
-    pdl_prologue();
+    // barriers, tensor memory and the abort flag are on-chip state, set up while the kernel before this one in the
+    // stream may still be draining; global memory is first touched below, after that kernel has completed
+    pdl_wait();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
