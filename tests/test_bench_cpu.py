@@ -32,3 +32,13 @@ def test_workload_table_names_existing_builders():
         assert callable(getattr(nets, wl["build"])), name
         assert wl["layout"] in ("NHWC", "NCHW") and wl["batch"] > 0
     assert bench.WORKLOADS["resnet50"]["metric"] == bench.METRIC
+
+
+def test_sweep_points_cover_the_shape_sweep():
+    import bench
+    pts = bench.sweep_points()
+    assert len(pts) == 640 and len(set(pts)) == 640
+    for n, h, w, ci, co, k, s, p in pts:
+        assert n == 32 and h == w and h in (7, 14, 28, 56, 112) and k in (1, 3, 5, 7) and s in (1, 2)
+        assert ci in (64, 128, 256, 512) and co in (64, 128, 256, 512) and p == (k - 1) // 2
+        assert (h + 2 * p - k) // s + 1 == (h + s - 1) // s          # 'same' padding: ceil(h / stride) outputs
