@@ -53,3 +53,57 @@ def test_sweep_point(hw, ci, cout, k, stride):
                        w_layout="KRSC" if layout == "NHWC" else "KCRS")
         for nm, ref in (("y", y), ("dw", dw), ("db", db), ("dx", dx)):
             assert_parity(out[nm], ref, dtype, f"{g} {layout} {np.dtype(dtype).name} {nm}")
+
+
+def _device_passes(g, layout, tdt, x, w, b, dy):
+    """fprop, wgrad and dgrad of device tensors through the C ABI; returns device tensors."""
+    import ctypes
+    import torch
+    from pydtnn_b200 import _lib
+    from tests.gpu_util import make_desc, stream, workspace
+    L = _lib.lib()
+    desc = make_desc(g, layout, np.float32 if tdt == torch.float32 else np.float64, "KRSC" if layout == "NHWC" else "KCRS")
+    ws = workspace(desc)
+    y = torch.full_like(dy, float("nan"))
+    dw, db, dx = torch.full_like(w, float("nan")), torch.full_like(b, float("nan")), torch.full_like(x, float("nan"))
+    _lib.check(L.b2c_conv_fprop(ctypes.byref(desc), x.data_ptr(), w.data_ptr(), b.data_ptr(), None, 0, y.data_ptr(),
+                                ws.data_ptr(), ws.numel(), stream()))
+    _lib.check(L.b2c_conv_wgrad(ctypes.byref(desc), x.data_ptr(), dy.data_ptr(), dw.data_ptr(), db.data_ptr(),
+                                ws.data_ptr(), ws.numel(), stream()))
+    _lib.check(L.b2c_conv_dgrad(ctypes.byref(desc), dy.data_ptr(), w.data_ptr(), dx.data_ptr(), ws.data_ptr(),
+                                ws.numel(), stream()))
+    return {"y": y, "dw": dw, "db": db, "dx": dx}
+
+
+@pytest.mark.parametrize("layout", ["NHWC", "NCHW"])
+@pytest.mark.parametrize("hw", [7, 14, 28, 56, 112])
+def test_every_sweep_geometry_float32_against_the_float64_engine(hw, layout):
+    """All 128 geometries of one image size (channels x kernel x stride), batch 2, on the device only: the float32
+    result (tensor-core engine wherever it takes the shape) against the float64 FMA engine on the same inputs.
+    The float64 engine is checked against the CPU oracle to 1e-12 on the sampled points above and on the golden
+    vectors, so agreement to the float32 bar here carries the parity to every geometry of the sweep."""
+    import torch
+    from tests.gpu_util import DEV
+    gen = torch.Generator(device=DEV).manual_seed(1000 + hw)
+    worst = {}
+    for ci, cout, k, stride in itertools.product((64, 128, 256, 512), (64, 128, 256, 512), (1, 3, 5, 7), (1, 2)):
+        pad = (k - 1) // 2
+        g = co.Geom(2, hw, hw, ci, cout, k, k, pad, pad, stride, stride)
+        xs, ys = ((g.n, g.h, g.w, g.ci), (g.n, g.ho, g.wo, g.co)) if layout == "NHWC" else ((g.n, g.ci, g.h, g.w), (g.n, g.co, g.ho, g.wo))
+        wsh = (g.co, g.kh, g.kw, g.ci) if layout == "NHWC" else (g.co, g.ci, g.kh, g.kw)
+        x = torch.randn(xs, device=DEV, generator=gen)
+        w = torch.randn(wsh, device=DEV, generator=gen) * float(np.sqrt(2.0 / g.k))
+        b = torch.randn((g.co,), device=DEV, generator=gen)
+        dy = torch.randn(ys, device=DEV, generator=gen)
+        got = _device_passes(g, layout, torch.float32, x, w, b, dy)
+        ref = _device_passes(g, layout, torch.float64, x.double(), w.double(), b.double(), dy.double())
+        torch.cuda.synchronize()
+        for nm in ("y", "dw", "db", "dx"):
+            a, r = got[nm].double(), ref[nm]
+            assert bool(torch.isfinite(a).all()), f"{g} {layout} {nm}: non-finite values"
+            rel = float((a - r).norm() / r.norm().clamp_min(1e-300))
+            mabs = float((a - r).abs().max() / r.abs().max().clamp_min(1e-300))
+            assert rel <= 1e-5, f"{g} {layout} {nm}: rel-L2 {rel:.3e} > 1e-5"
+            assert mabs <= 1e-4, f"{g} {layout} {nm}: max-abs {mabs:.3e} > 1e-4 of the largest value"
+            worst[nm] = max(worst.get(nm, 0.0), rel)
+    print(f"hw {hw} {layout}: worst rel-L2 {worst}")
