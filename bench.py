@@ -545,6 +545,64 @@ def run_sweep(args):
         "summary": summary}), flush=True)
 
 
+def run_single_fc(args):
+    """One fully connected layer (batch, in, out) through the C ABI on device-resident synthetic tensors: forward,
+    weight + bias gradient, input gradient, each timed alone with operands rotating through more than 2x L2."""
+    import ctypes
+    import torch
+    from pydtnn_b200 import _lib
+    b, fin, fout = [int(v) for v in args.fc.split(",")]
+    L = _lib.lib()
+    torch.cuda.set_device(0)
+    f64 = args.conv_dtype == "f64"
+    tdt, esz, dt = (torch.float64, 8, _lib.F64) if f64 else (torch.float32, 4, _lib.F32)
+    eng = {"auto": _lib.ENGINE_AUTO, "fma": _lib.ENGINE_FMA, "tensor": _lib.ENGINE_TENSOR}[args.conv_engine]
+    ws = torch.empty(max(int(L.b2c_fc_workspace_bytes(dt, b, fin, fout, eng)), 256), dtype=torch.uint8, device="cuda")
+    nbuf = max(2, int(256e6 // (fin * fout * esz)) + 1)
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    ws_ = [torch.randn(fin, fout, device="cuda", generator=gen, dtype=tdt) * (1.0 / fin) ** 0.5 for _ in range(nbuf)]
+    dws = [torch.empty_like(w) for w in ws_]
+    x = torch.randn(b, fin, device="cuda", generator=gen, dtype=tdt)
+    dy = torch.randn(b, fout, device="cuda", generator=gen, dtype=tdt)
+    bias = torch.randn(fout, device="cuda", generator=gen, dtype=tdt)
+    y, dx, db = torch.empty_like(dy), torch.empty_like(x), torch.empty_like(bias)
+    st = torch.cuda.current_stream().cuda_stream
+
+    def fwd(i):
+        _lib.check(L.b2c_fc_forward(dt, eng, b, fin, fout, x.data_ptr(), ws_[i % nbuf].data_ptr(), bias.data_ptr(), y.data_ptr(),
+                                    ws.data_ptr(), ws.numel(), st))
+
+    def wgrad(i):
+        _lib.check(L.b2c_fc_backward(dt, eng, b, fin, fout, x.data_ptr(), dy.data_ptr(), ws_[i % nbuf].data_ptr(),
+                                     dws[i % nbuf].data_ptr(), db.data_ptr(), None, ws.data_ptr(), ws.numel(), st))
+
+    def dgrad(i):
+        _lib.check(L.b2c_fc_backward(dt, eng, b, fin, fout, x.data_ptr(), dy.data_ptr(), ws_[i % nbuf].data_ptr(), None, None,
+                                     dx.data_ptr(), ws.data_ptr(), ws.numel(), st))
+
+    res = {}
+    for name, fn in (("forward", fwd), ("wgrad", wgrad), ("dgrad", dgrad)):
+        for i in range(max(args.warmup, 3)):
+            fn(i)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(args.steps):
+            fn(i)
+        e1.record()
+        torch.cuda.synchronize()
+        res[name] = e0.elapsed_time(e1) / args.steps
+    peaks = measured_peaks()
+    flops, wbytes = 2.0 * b * fin * fout, float(esz) * fin * fout
+    print(json.dumps({
+        "metric": "fc_pass_ms", "unit": "ms", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "higher_is_better": False, "dtype": args.conv_dtype, "data": "synthetic",
+        "config": {"workload": "fc layer", "shape": args.fc, "l2": f"{nbuf} rotating weight matrices"},
+        "passes": {k: {"ms": v, "tflops": flops / (v * 1e-3) / 1e12, "weight_gbs": wbytes / (v * 1e-3) / 1e9,
+                       "frac_of_hbm": wbytes / (v * 1e-3) / 1e9 / peaks["hbm_gbs"]} for k, v in res.items()},
+        "roofline_note": "each pass reads or writes the weight matrix once: bound = weight bytes / measured HBM bandwidth"}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -556,6 +614,7 @@ def main():
                     help="whole-network configuration to time (default: the one the headline metric is quoted on)")
     ap.add_argument("--layers", action="store_true", help="add per-layer convolution timings to the JSON line")
     ap.add_argument("--conv", default=None, help="n,h,w,ci,co,k,stride,pad: time one Conv2D pass instead of the model")
+    ap.add_argument("--fc", default=None, help="batch,in,out: time one fully connected layer instead of the model")
     ap.add_argument("--conv-pass", default="fprop", choices=["fprop", "dgrad", "wgrad"])
     ap.add_argument("--conv-dtype", default="f32", choices=["f32", "f64"])
     ap.add_argument("--conv-layout", default="NHWC", choices=["NHWC", "NCHW"])
@@ -569,6 +628,9 @@ def main():
     args = ap.parse_args()
     if args.sweep:
         run_sweep(args)
+        return
+    if args.fc:
+        run_single_fc(args)
         return
     if args.conv:
         run_single_conv(args)
