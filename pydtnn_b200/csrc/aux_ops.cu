@@ -558,25 +558,28 @@ struct PoolP {
     int64_t xsn, xsh, xsw, xsc, ysn, ysh, ysw, ysc;
 };
 
-template <typename T, bool IS_MAX>
+// IDX = int when the element count (plus one grid stride) fits 31 bits: the four divisions per element are the
+// expensive part of this kernel and 64-bit ones cost several times more.
+template <typename T, bool IS_MAX, typename IDX>
 __global__ void pool_fwd_kernel(PoolP p, const T* __restrict__ x, T* __restrict__ y, int32_t* __restrict__ idx_max, int nchw)
 {
     pdl_prologue();
-    int64_t total = (int64_t)p.n * p.ho * p.wo * p.c;
-    int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const IDX total = (IDX)p.n * p.ho * p.wo * p.c;
+    const IDX stride = (IDX)gridDim.x * blockDim.x;
+    for (IDX i = (IDX)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
         int cc, yy, xx, nn;
-        if (nchw) { yy = (int)(i % p.wo); int64_t r = i / p.wo; xx = (int)(r % p.ho); r /= p.ho; cc = (int)(r % p.c); nn = (int)(r / p.c); }
-        else { cc = (int)(i % p.c); int64_t r = i / p.c; yy = (int)(r % p.wo); r /= p.wo; xx = (int)(r % p.ho); nn = (int)(r / p.ho); }
+        if (nchw) { yy = (int)(i % p.wo); IDX r = i / p.wo; xx = (int)(r % p.ho); r /= p.ho; cc = (int)(r % p.c); nn = (int)(r / p.c); }
+        else { cc = (int)(i % p.c); IDX r = i / p.c; yy = (int)(r % p.wo); r /= p.wo; xx = (int)(r % p.ho); nn = (int)(r / p.ho); }
         T best = IS_MAX ? (sizeof(T) == 4 ? (T)(-FLT_MAX) : (T)(-DBL_MAX)) : T(0);
         int bidx = 0, items = 0;
+        const T* xb = x + nn * p.xsn + cc * p.xsc;
         for (int ii = 0; ii < p.kh; ii++) {
             int x_x = p.vstr * xx + p.vdil * ii - p.vpad;
             if (x_x < 0 || x_x >= p.h) continue;
             for (int jj = 0; jj < p.kw; jj++) {
                 int x_y = p.hstr * yy + p.hdil * jj - p.hpad;
                 if (x_y < 0 || x_y >= p.w) continue;
-                T v = x[nn * p.xsn + x_x * p.xsh + x_y * p.xsw + cc * p.xsc];
+                T v = xb[x_x * p.xsh + x_y * p.xsw];
                 if (IS_MAX) { if (v > best) { best = v; bidx = ii * p.kw + jj; } }
                 else { best += v; items++; }
             }
@@ -1060,13 +1063,16 @@ extern "C" int b2c_pool_forward(int dtype, int layout, int is_max, int n, int h,
         else launch_pdl(pool_fwd_v4_kernel<false>, ew_blocks(total / 4), 256, 0, st, p, (const float4*)x, (float4*)y, (int4*)idx_max);
         return check_launch("pool_forward_v4");
     }
-    if (dtype == B2C_F32) {
-        if (is_max) launch_pdl(pool_fwd_kernel<float, true>, ew_blocks(total), 256, 0, st, p, (const float*)x, (float*)y, idx_max, nchw);
-        else launch_pdl(pool_fwd_kernel<float, false>, ew_blocks(total), 256, 0, st, p, (const float*)x, (float*)y, idx_max, nchw);
-    } else {
-        if (is_max) launch_pdl(pool_fwd_kernel<double, true>, ew_blocks(total), 256, 0, st, p, (const double*)x, (double*)y, idx_max, nchw);
-        else launch_pdl(pool_fwd_kernel<double, false>, ew_blocks(total), 256, 0, st, p, (const double*)x, (double*)y, idx_max, nchw);
-    }
+    // 32-bit index arithmetic when the output count, one grid stride and the input offsets all fit
+    const bool small = total + (int64_t)ew_blocks(total) * 256 < 0x7fffffffLL && (int64_t)n * h * w * c < 0x7fffffffLL;
+#define B2C_POOL_FWD(T, MAXF)                                                                                              \
+    do {                                                                                                                   \
+        if (small) launch_pdl(pool_fwd_kernel<T, MAXF, int>, ew_blocks(total), 256, 0, st, p, (const T*)x, (T*)y, idx_max, nchw); \
+        else launch_pdl(pool_fwd_kernel<T, MAXF, int64_t>, ew_blocks(total), 256, 0, st, p, (const T*)x, (T*)y, idx_max, nchw);   \
+    } while (0)
+    if (dtype == B2C_F32) { if (is_max) B2C_POOL_FWD(float, true); else B2C_POOL_FWD(float, false); }
+    else { if (is_max) B2C_POOL_FWD(double, true); else B2C_POOL_FWD(double, false); }
+#undef B2C_POOL_FWD
     return check_launch("pool_forward");
 }
 

@@ -1542,9 +1542,39 @@ __global__ void transpose_inner_kernel(const float* __restrict__ src, float* __r
     }
 }
 
+// The same transpose when one extent is at most 8 (the three channels of a network's input): a 32 x 32 tile would
+// leave nine tenths of its threads idle.  One thread per position of the long axis; ROWS_THIN: src [n][thin][len]
+// -> dst [n][len][thin], else src [n][len][thin] -> dst [n][thin][len].  Loads or stores of a warp cover whole
+// contiguous runs either way.
+template <bool ROWS_THIN>
+__global__ void __launch_bounds__(256) transpose_thin_kernel(const float* __restrict__ src, float* __restrict__ dst, int thin, int len)
+{
+    pdl_prologue();
+    const int l = blockIdx.x * blockDim.x + threadIdx.x;
+    if (l >= len) return;
+    const int64_t plane = (int64_t)thin * len;
+    const float* s = src + blockIdx.y * plane;
+    float* d = dst + blockIdx.y * plane;
+    float v[8];
+#pragma unroll
+    for (int r = 0; r < 8; r++)
+        if (r < thin) v[r] = ROWS_THIN ? s[(int64_t)r * len + l] : s[(int64_t)l * thin + r];
+#pragma unroll
+    for (int r = 0; r < 8; r++)
+        if (r < thin) { if (ROWS_THIN) d[(int64_t)l * thin + r] = v[r]; else d[(int64_t)r * len + l] = v[r]; }
+}
+
 static int transpose_inner(const void* src, void* dst, int n, int rows, int cols, cudaStream_t st)
 {
     if (n > 65535) return B2C_ERR_TOO_LARGE;
+    if (rows <= 8 && cols > 8) {
+        launch_pdl(transpose_thin_kernel<true>, dim3((cols + 255) / 256, n), 256, 0, st, (const float*)src, (float*)dst, rows, cols);
+        return check_launch("transpose_thin_kernel");
+    }
+    if (cols <= 8 && rows > 8) {
+        launch_pdl(transpose_thin_kernel<false>, dim3((rows + 255) / 256, n), 256, 0, st, (const float*)src, (float*)dst, cols, rows);
+        return check_launch("transpose_thin_kernel");
+    }
     launch_pdl(transpose_inner_kernel, dim3((cols + 31) / 32, (rows + 31) / 32, n), dim3(32, 8), 0, st,
                (const float*)src, (float*)dst, rows, cols);
     return check_launch("transpose_inner_kernel");

@@ -274,3 +274,19 @@ def test_a_wait_that_runs_out_is_reported_and_the_context_stays_usable():
     out = run_conv(g, "NHWC", np.float32, x, w, b, dy, w_layout="KRSC")
     assert_parity(out["y"], y, np.float32, "conv after a timed-out wait")
     assert L.b2c_check_device_status(None) == 0
+
+
+@pytest.mark.parametrize("ci,passes", [(4, ("fprop", "wgrad", "dgrad")), (3, ("fprop", "wgrad")), (8, ("fprop", "wgrad", "dgrad"))])
+def test_nchw_few_channels_on_the_tensor_engine(ci, passes):
+    """NCHW tensors with at most 8 channels go through the thin layout copies (one thread per pixel) on their way to
+    and from the channel-last kernels; the engine is forced so that the small shape does not fall to the FMA engine."""
+    g = co.Geom(3, 21, 19, ci, 32, 3, 3, 1, 1, 1, 1)
+    x, w, b, dy = _inputs(g, np.float32, seed=5)
+    xl, wl, dyl = _to_layout(x, w, dy, "NCHW")
+    keep = {}
+    y = co.conv2d_forward(xl, wl, b, g, "NCHW", keep=keep)
+    dw, db, dx = co.conv2d_backward(xl, dyl, wl, g, "NCHW", keep=keep)
+    out = run_conv(g, "NCHW", np.float32, xl, wl, b, dyl, engine=_lib.ENGINE_TENSOR, passes=passes)
+    refs = {"y": y, "dw": dw, "db": db, "dx": dx}
+    for nm in ("y",) + (("dw", "db") if "wgrad" in passes else ()) + (("dx",) if "dgrad" in passes else ()):
+        assert_parity(out[nm], refs[nm], np.float32, f"NCHW ci={ci} {nm}")
