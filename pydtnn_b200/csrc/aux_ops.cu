@@ -589,6 +589,44 @@ __global__ void pool_fwd_kernel(PoolP p, const T* __restrict__ x, T* __restrict_
     }
 }
 
+// NCHW float32 planes that fit shared memory: a block copies a run of whole (image, channel) planes with coalesced
+// loads and pools out of shared memory, so the strided, overlapping window reads never reach L2.  Same tap order,
+// tie rule (first maximum) and in-bounds divisor as the general kernel: results are bit-identical.
+#define B2C_POOL_TILE 8192
+template <bool IS_MAX>
+__global__ void __launch_bounds__(256) pool_fwd_nchw_planes_kernel(PoolP p, const float* __restrict__ x, float* __restrict__ y,
+                                                                   int32_t* __restrict__ idx_max, int planes, int per_block)
+{
+    pdl_prologue();
+    __shared__ float tile[B2C_POOL_TILE];
+    const int hw = p.h * p.w, ohw = p.ho * p.wo;
+    const int plane0 = blockIdx.x * per_block;
+    const int np = planes - plane0 < per_block ? planes - plane0 : per_block;
+    const float* src = x + (int64_t)plane0 * hw;
+    for (int i = threadIdx.x; i < np * hw; i += 256) tile[i] = src[i];
+    __syncthreads();
+    for (int o = threadIdx.x; o < np * ohw; o += 256) {
+        const int pl = o / ohw, r = o - pl * ohw, xx = r / p.wo, yy = r - xx * p.wo;
+        const float* t = tile + pl * hw;
+        float best = IS_MAX ? -FLT_MAX : 0.f;
+        int bidx = 0, items = 0;
+        for (int ii = 0; ii < p.kh; ii++) {
+            const int x_x = p.vstr * xx + p.vdil * ii - p.vpad;
+            if (x_x < 0 || x_x >= p.h) continue;
+            for (int jj = 0; jj < p.kw; jj++) {
+                const int x_y = p.hstr * yy + p.hdil * jj - p.hpad;
+                if (x_y < 0 || x_y >= p.w) continue;
+                const float v = t[x_x * p.w + x_y];
+                if (IS_MAX) { if (v > best) { best = v; bidx = ii * p.kw + jj; } }
+                else { best += v; items++; }
+            }
+        }
+        const int64_t oi = (int64_t)plane0 * ohw + o;
+        if (IS_MAX) { y[oi] = best; if (idx_max) idx_max[oi] = bidx; }
+        else y[oi] = best / (float)items;
+    }
+}
+
 // Backward as a gather over the windows that contain each input element (fixed summation order).
 template <typename T, bool IS_MAX>
 __global__ void pool_bwd_kernel(PoolP p, const T* __restrict__ dy, const int32_t* __restrict__ idx_max, T* __restrict__ dx, int nchw)
@@ -1062,6 +1100,15 @@ extern "C" int b2c_pool_forward(int dtype, int layout, int is_max, int n, int h,
         if (is_max) launch_pdl(pool_fwd_v4_kernel<true>, ew_blocks(total / 4), 256, 0, st, p, (const float4*)x, (float4*)y, (int4*)idx_max);
         else launch_pdl(pool_fwd_v4_kernel<false>, ew_blocks(total / 4), 256, 0, st, p, (const float4*)x, (float4*)y, (int4*)idx_max);
         return check_launch("pool_forward_v4");
+    }
+    if (dtype == B2C_F32 && nchw && (int64_t)h * w <= B2C_POOL_TILE && (int64_t)n * c < 0x7fffffffLL) {
+        const int planes = n * c;
+        int per_block = B2C_POOL_TILE / (h * w);
+        if (per_block > 16) per_block = 16;
+        const int blocks = (planes + per_block - 1) / per_block;
+        if (is_max) launch_pdl(pool_fwd_nchw_planes_kernel<true>, blocks, 256, 0, st, p, (const float*)x, (float*)y, idx_max, planes, per_block);
+        else launch_pdl(pool_fwd_nchw_planes_kernel<false>, blocks, 256, 0, st, p, (const float*)x, (float*)y, idx_max, planes, per_block);
+        return check_launch("pool_forward_nchw_planes");
     }
     // 32-bit index arithmetic when the output count, one grid stride and the input offsets all fit
     const bool small = total + (int64_t)ew_blocks(total) * 256 < 0x7fffffffLL && (int64_t)n * h * w * c < 0x7fffffffLL;

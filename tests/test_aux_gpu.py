@@ -188,3 +188,28 @@ def test_softmax_cce_at_imagenet_width_and_residual_sum():
     ad, od = dev(a4), dev(o4)
     _lib.check(L.b2c_add_inplace(0, ad.numel(), ad.data_ptr(), od.data_ptr(), stream()))
     assert np.array_equal(ad.cpu().numpy(), a4 + o4)
+
+
+@pytest.mark.parametrize("case", [(3, 5, 55, 55, 3, 3, 0, 0, 2, 2), (2, 7, 13, 13, 3, 3, 0, 0, 2, 2), (2, 3, 90, 91, 2, 3, 1, 0, 2, 1),
+                                  (1, 2, 100, 100, 3, 3, 1, 1, 2, 2)])
+def test_nchw_pooling_planes_exact(case):
+    """NCHW float32 pooling at AlexNet's shapes and around the limits of the shared-memory plane kernel (several
+    planes per block with a ragged last block; one plane per block; a plane too large for it): values and argmax
+    indices equal the oracle's exactly (max), averages to float32 rounding."""
+    n, c, h, w, kh, kw, vpad, hpad, vstr, hstr = case
+    rng = np.random.Generator(np.random.PCG64(h * 1000 + w))
+    x = rng.standard_normal((n, c, h, w)).astype(np.float32)
+    L = _lib.lib()
+    xd = dev(x)
+    y_ref, idx_ref = ao.max_pool_forward(x, kh, kw, vpad, hpad, vstr, hstr, layout="NCHW")
+    a_ref = ao.avg_pool_forward(x, kh, kw, vpad, hpad, vstr, hstr, layout="NCHW")
+    a_ref = a_ref[0] if isinstance(a_ref, tuple) else a_ref
+    y = torch.empty(y_ref.shape, dtype=torch.float32, device=DEV)
+    idx = torch.empty(y_ref.shape, dtype=torch.int32, device=DEV)
+    _lib.check(L.b2c_pool_forward(_lib.F32, _lib.LAYOUT_NCHW, 1, n, h, w, c, kh, kw, vpad, hpad, vstr, hstr, 1, 1,
+                                  xd.data_ptr(), y.data_ptr(), idx.data_ptr(), stream()))
+    assert np.array_equal(y.cpu().numpy(), y_ref)
+    assert np.array_equal(idx.cpu().numpy(), idx_ref)
+    _lib.check(L.b2c_pool_forward(_lib.F32, _lib.LAYOUT_NCHW, 0, n, h, w, c, kh, kw, vpad, hpad, vstr, hstr, 1, 1,
+                                  xd.data_ptr(), y.data_ptr(), None, stream()))
+    assert_parity(y.cpu().numpy(), a_ref, np.float32, "average pool NCHW")
