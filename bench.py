@@ -235,7 +235,7 @@ def run_ours(args):
             model.evaluate_batch(None)
 
         def e2e_step():
-            y = model.evaluate_batch(x_host)
+            y = model.evaluate_batch(x_host, next_batch=x_host)    # the next call's input uploads under this call's kernels
             out_host.copy_(y.ary.t.view(batch, 1000), non_blocking=True)       # device -> host read of the class scores
             torch.cuda.current_stream().synchronize()
             return float(out_host[0, 0])

@@ -223,23 +223,42 @@ class Model:
                 with tr.region(layer, tracer.PYDTNN_MDL_UPDATE_DW):
                     layer.update_weights(optimizer)
 
-    def _stage_next(self, x_batch, y_batch):
+    def _stage_next(self, x_batch, y_batch=None):
         """Start the host -> device copy of the batch of the *next* step on a copy stream, into staging
-        buffers, so that it runs under this step's kernels. Pinned torch CPU tensors only."""
+        buffers, so that it runs under this step's kernels. Pinned torch CPU tensors only; ``y_batch`` is
+        None for inference."""
         xin = self.layers[0].y.ary
         if self._stage is None:
-            self._stage = {"x": torch.empty_like(xin.t), "y": torch.empty_like(self.y_batch.t),
+            self._stage = {"x": torch.empty_like(xin.t), "y": None,
                            "stream": torch.cuda.Stream(device=xin.t.device), "ready": torch.cuda.Event(),
                            "free": torch.cuda.Event(), "batch": None}
             self._stage["free"].record()
         st = self._stage
-        lab = self._labels(y_batch)
+        if y_batch is not None and st["y"] is None:
+            st["y"] = torch.empty_like(self.y_batch.t)
+        lab = self._labels(y_batch) if y_batch is not None else None
         with torch.cuda.stream(st["stream"]):
             st["stream"].wait_event(st["free"])           # the step that read the staging buffers has copied them out
             st["x"].copy_(x_batch.view(xin.t.shape), non_blocking=True)
-            st["y"].copy_(lab.to(torch.int32), non_blocking=True)
+            if lab is not None:
+                st["y"].copy_(lab.to(torch.int32), non_blocking=True)
             st["ready"].record()
         st["batch"] = (x_batch, y_batch)
+
+    def _take_staged(self, x_batch, y_batch=None):
+        """If the staged batch is this one, move it from the staging buffers into the input (and label) buffers on
+        the compute stream and return True."""
+        st = self._stage
+        if st is None or st["batch"] is None or st["batch"][0] is not x_batch or st["batch"][1] is not y_batch:
+            return False
+        cur = torch.cuda.current_stream()
+        cur.wait_event(st["ready"])
+        self.layers[0].y.ary.t.copy_(st["x"], non_blocking=True)
+        if y_batch is not None:
+            self.y_batch.t.copy_(st["y"], non_blocking=True)
+        st["free"].record(cur)
+        st["batch"] = None
+        return True
 
     def train_batch(self, x_batch, y_batch, optimizer, global_batch_size=None, next_batch=None):
         """One training step on a host batch; returns the loss object (``.loss()``, ``.accuracy()``
@@ -247,15 +266,7 @@ class Model:
         following step's inputs under this step's kernels; the call that then passes those same tensors
         finds them on the device."""
         self._ensure_loss()
-        st = self._stage
-        if st is not None and st["batch"] is not None and st["batch"][0] is x_batch and st["batch"][1] is y_batch:
-            cur = torch.cuda.current_stream()
-            cur.wait_event(st["ready"])
-            self.layers[0].y.ary.t.copy_(st["x"], non_blocking=True)
-            self.y_batch.t.copy_(st["y"], non_blocking=True)
-            st["free"].record(cur)
-            st["batch"] = None
-        else:
+        if not self._take_staged(x_batch, y_batch):
             self._upload(x_batch, y_batch)
         if next_batch is not None and isinstance(next_batch[0], torch.Tensor):
             self._stage_next(*next_batch)
@@ -263,18 +274,22 @@ class Model:
         self.apply_update(optimizer)
         return loss
 
-    def evaluate_batch(self, x_batch, y_batch=None):
+    def evaluate_batch(self, x_batch, y_batch=None, next_batch=None):
         """Forward only, with the inference fusions that are switched on; returns the output handle
-        (and the loss object when labels are given)."""
+        (and the loss object when labels are given). ``next_batch`` (a pinned torch CPU tensor) starts the upload
+        of the following call's input under this call's kernels, as in ``train_batch``."""
         self.mode = EVALUATE_MODE
         if self._eval_layers is None:
             self._eval_layers = self._fuse_inference(self.layers)
         if x_batch is not None:
             xin = self.layers[0].y.ary
             if isinstance(x_batch, torch.Tensor):
-                xin.t.copy_(x_batch.view(xin.t.shape), non_blocking=True)
+                if not self._take_staged(x_batch, None):
+                    xin.t.copy_(x_batch.view(xin.t.shape), non_blocking=True)
             else:
                 xin.set(x_batch)
+        if isinstance(next_batch, torch.Tensor):
+            self._stage_next(next_batch, None)
         x = self.layers[0].y
         for layer in self._eval_layers[1:]:
             x = layer.forward(x)

@@ -163,6 +163,23 @@ def test_staged_upload_of_the_next_batch_gives_the_same_steps():
             assert np.array_equal(getattr(pa, k).ary.get(), getattr(pb, k).ary.get()), (pa, k)
 
 
+def test_staged_upload_in_evaluation_gives_the_same_outputs():
+    """``evaluate_batch(x, next_batch=...)`` uploads the following call's pinned input on a copy stream; outputs
+    must be bit-identical to plain uploads, for a sequence of different batches."""
+    import torch
+    a = _small_resnet("NHWC", np.float32)
+    b = _small_resnet("NHWC", np.float32)
+    xs = [torch.from_numpy(_batch(a, step)[0]).pin_memory() for step in range(4)]
+    for step in range(4):
+        nxt = xs[step + 1] if step + 1 < 4 else None
+        ya = a.evaluate_batch(xs[step], next_batch=nxt).ary.get()
+        yb = b.evaluate_batch(xs[step]).ary.get()
+        assert np.array_equal(ya, yb), step
+    # a staged batch that is not the one passed next is ignored
+    a.evaluate_batch(xs[0], next_batch=xs[1])
+    assert np.array_equal(a.evaluate_batch(xs[2]).ary.get(), b.evaluate_batch(xs[2]).ary.get())
+
+
 @pytest.mark.parametrize("layout", ["NHWC", "NCHW"])
 def test_inference_fusion_matches_unfused_chain(layout):
     """Conv+BN+ReLU / Conv+BN folded into the convolution epilogue for evaluation: same output as
