@@ -603,6 +603,62 @@ def run_single_fc(args):
         "roofline_note": "each pass reads or writes the weight matrix once: bound = weight bytes / measured HBM bandwidth"}), flush=True)
 
 
+def run_single_bn(args):
+    """Training-mode batch norm (+ fused ReLU) forward and backward on one (n, h, w, c) float32 NHWC tensor through
+    the C ABI, tensors rotating through more than 2x L2: the small, fixed case for profiles of the HBM-bound kernels.
+    Algorithmic bytes: forward reads x twice and writes y (3 passes), backward reads x and dy twice and writes dx
+    (5 passes); the second read of each pair can come from L2 when the tensor fits."""
+    import torch
+    from pydtnn_b200 import _lib
+    n, h, w, c = [int(v) for v in args.bn.split(",")]
+    L = _lib.lib()
+    torch.cuda.set_device(0)
+    numel = n * h * w * c
+    nbuf = max(2, int(256e6 // (numel * 4)) + 1)
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    xs = [torch.randn(n, h, w, c, device="cuda", generator=gen) for _ in range(nbuf)]
+    dys = [torch.randn(n, h, w, c, device="cuda", generator=gen) for _ in range(nbuf)]
+    ys = [torch.empty_like(x) for x in xs]
+    gamma, beta = torch.randn(c, device="cuda", generator=gen), torch.randn(c, device="cuda", generator=gen)
+    rm, rv = torch.zeros(c, device="cuda"), torch.ones(c, device="cuda")
+    mean, inv_std, dg, db = (torch.empty(c, device="cuda") for _ in range(4))
+    scratch = torch.empty(1200 * c, dtype=torch.float64, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+
+    def fwd(i):
+        _lib.check(L.b2c_bn_train_forward(_lib.F32, _lib.LAYOUT_NHWC, n, c, h * w, xs[i % nbuf].data_ptr(), gamma.data_ptr(),
+                                          beta.data_ptr(), rm.data_ptr(), rv.data_ptr(), 0.9, 1e-5, 1, ys[i % nbuf].data_ptr(),
+                                          mean.data_ptr(), inv_std.data_ptr(), scratch.data_ptr(), scratch.numel() * 8, st))
+
+    def bwd(i):
+        _lib.check(L.b2c_bn_train_backward(_lib.F32, _lib.LAYOUT_NHWC, n, c, h * w, xs[i % nbuf].data_ptr(), dys[i % nbuf].data_ptr(),
+                                           None, beta.data_ptr(), gamma.data_ptr(), mean.data_ptr(), inv_std.data_ptr(),
+                                           dg.data_ptr(), db.data_ptr(), ys[i % nbuf].data_ptr(), scratch.data_ptr(),
+                                           scratch.numel() * 8, st))
+
+    res = {}
+    for name, fn, passes in (("forward", fwd, 3), ("backward", bwd, 5)):
+        for i in range(max(args.warmup, 3)):
+            fn(i)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(args.steps):
+            fn(i)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+        res[name] = {"ms": ms, "passes": passes, "gbs": passes * numel * 4 / (ms * 1e-3) / 1e9}
+    peaks = measured_peaks()
+    for v in res.values():
+        v["frac_of_hbm"] = v["gbs"] / peaks["hbm_gbs"]
+    print(json.dumps({"metric": "bn_train_gbs", "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+                      "higher_is_better": True, "dtype": "f32", "data": "synthetic",
+                      "config": {"workload": "batch norm + ReLU, training", "shape": args.bn, "l2": f"{nbuf} rotating tensor sets"},
+                      "passes": res, "roofline": {"bound": "hbm", "peak": peaks["hbm_gbs"], "unit": "GB/s", "source": peaks["source"]}}),
+          flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -615,6 +671,7 @@ def main():
     ap.add_argument("--layers", action="store_true", help="add per-layer convolution timings to the JSON line")
     ap.add_argument("--conv", default=None, help="n,h,w,ci,co,k,stride,pad: time one Conv2D pass instead of the model")
     ap.add_argument("--fc", default=None, help="batch,in,out: time one fully connected layer instead of the model")
+    ap.add_argument("--bn", default=None, help="n,h,w,c: time training-mode batch norm + ReLU forward and backward on one tensor")
     ap.add_argument("--conv-pass", default="fprop", choices=["fprop", "dgrad", "wgrad"])
     ap.add_argument("--conv-dtype", default="f32", choices=["f32", "f64"])
     ap.add_argument("--conv-layout", default="NHWC", choices=["NHWC", "NCHW"])
@@ -631,6 +688,9 @@ def main():
         return
     if args.fc:
         run_single_fc(args)
+        return
+    if args.bn:
+        run_single_bn(args)
         return
     if args.conv:
         run_single_conv(args)
