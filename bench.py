@@ -126,20 +126,39 @@ def _cpu_threads():
     return n
 
 
-def cpu_resnet50_images_per_s(batch, steps, warmup, budget_s=None):
-    """ResNet-50 training steps on the host cores with the oracle's CPU model.
-    Returns (img/s, kind, seconds per step list)."""
-    from oracle import conv_oracle as co
+CPU_GLUE = ("layer classes of oracle/cpu_model.py (this repository's restatement of the reference's CPU layers) "
+            "driving the reference's own compiled Cython kernels (im2row/im2col, pooling, bias add) and NumPy GEMM")
+
+
+def _cpu_net(workload, batch):
     from oracle import cpu_model as cm
+    wl = WORKLOADS[workload]
+    spec = {"resnet50": cm.resnet50_spec, "vgg16bn": lambda: cm.vgg16_spec(batch_norm=True), "alexnet": cm.alexnet_spec}[workload]()
+    hw = wl["hw"]
+    return cm.CpuNet(spec, (hw, hw, 3), batch, np.float32, wl["layout"], seed=0)
+
+
+def cpu_images_per_s(workload, batch, steps, warmup, budget_s=None):
+    """Steps of one of the whole-network workloads on the host cores with the oracle's CPU model (training step, or
+    forward only for the inference workload).  Returns (img/s, kind, seconds per step list)."""
+    from oracle import conv_oracle as co
     kind = "reference" if co.default_backend() == "ref" else "port"
+    wl = WORKLOADS[workload]
     rng = np.random.Generator(np.random.PCG64(0))
-    net = cm.CpuNet(cm.resnet50_spec(), (224, 224, 3), batch, np.float32, "NHWC", seed=0)
-    x = rng.standard_normal((batch, 224, 224, 3)).astype(np.float32)
+    net = _cpu_net(workload, batch)
+    hw = wl["hw"]
+    if wl["layout"] == "NCHW":
+        x = (rng.integers(0, 256, (batch, 3, hw, hw)).astype(np.float32) / 255.0).astype(np.float32)
+    else:
+        x = rng.standard_normal((batch, hw, hw, 3)).astype(np.float32)
     labels = rng.integers(0, 1000, batch)
     times = []
     for i in range(warmup + steps):
         t0 = time.perf_counter()
-        net.train_step(x, labels, lr=0.01, momentum=0.9, global_batch=batch)
+        if wl["train"]:
+            net.train_step(x, labels, lr=0.01, momentum=0.9, global_batch=batch)
+        else:
+            net.forward(x, train=False)
         dt = time.perf_counter() - t0
         if i >= warmup:
             times.append(dt)
@@ -148,28 +167,69 @@ def cpu_resnet50_images_per_s(batch, steps, warmup, budget_s=None):
     return batch * len(times) / sum(times), kind, times
 
 
+def cpu_resnet50_images_per_s(batch, steps, warmup, budget_s=None):
+    return cpu_images_per_s("resnet50", batch, steps, warmup, budget_s)
+
+
+def cpu_conv_pass(n, h, w, ci, co, k, stride, pad, pass_name, layout="NHWC", dtype=np.float32, sample_n=None, reps=3):
+    """One Conv2D pass on the host cores through the reference's lowering + GEMM path
+    (pydtnn/backends/cpu/layers/conv_2d_cpu.py:183-209, 363-397): im2row/im2col by the compiled Cython kernels where
+    oracle/_ref holds them, NumPy ``@`` for the GEMM.  Timed on ``sample_n`` images of the batch (the path is a loop
+    over images, so TFLOP/s does not depend on the batch).  Returns (TFLOP/s, kind, seconds, sample_n)."""
+    from oracle import conv_oracle as cvo
+    kind = "reference" if cvo.default_backend() == "ref" else "port"
+    if sample_n is None:
+        per_image = 2.0 * ((h + 2 * pad - k) // stride + 1) ** 2 * co * ci * k * k
+        sample_n = int(max(1, min(n, 2e10 // per_image)))          # about 20 GFLOP of work per repetition
+    g = cvo.Geom(sample_n, h, w, ci, co, k, k, pad, pad, stride, stride, 1, 1)
+    rng = np.random.Generator(np.random.PCG64(0))
+    nhwc = layout == "NHWC"
+    x = rng.standard_normal((sample_n, h, w, ci) if nhwc else (sample_n, ci, h, w)).astype(dtype)
+    wt = (rng.standard_normal((ci, k, k, co) if nhwc else (co, ci, k, k)) * np.sqrt(2.0 / (ci * k * k))).astype(dtype)
+    dy = rng.standard_normal((sample_n, g.ho, g.wo, co) if nhwc else (sample_n, co, g.ho, g.wo)).astype(dtype)
+    keep = {}
+    cvo.conv2d_forward(x, wt, None, g, layout, keep=keep)
+    best = None
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        if pass_name == "fprop":
+            cvo.conv2d_forward(x, wt, None, g, layout)
+        elif pass_name == "wgrad":
+            cvo.conv2d_backward(x, dy, wt, g, layout, need_dx=False, use_bias=False, keep=dict(keep))
+        else:
+            # the reference computes both gradients in one call; the input gradient alone = whole call - weight gradient
+            cvo.conv2d_backward(x, dy, wt, g, layout, need_dx=True, use_bias=False, keep=dict(keep))
+        dt = time.perf_counter() - t0
+        best = dt if best is None or dt < best else best
+    flops = g.flops * (2 if pass_name == "dgrad" else 1)
+    return flops / best / 1e12, kind, best, sample_n
+
+
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     threads = _cpu_threads()
+    wl = WORKLOADS[args.workload]
     batch = 4
     # size the sample so K+W steps end within a few minutes: probe one step at batch 2
     t0 = time.perf_counter()
-    cpu_resnet50_images_per_s(2, 1, 0)
+    cpu_images_per_s(args.workload, 2, 1, 0)
     probe = time.perf_counter() - t0
     if probe * 2 * (args.steps + args.warmup) > 240:
         batch = 2
     if probe * (args.steps + args.warmup) > 240:
         batch = 1
-    ips, kind, times = cpu_resnet50_images_per_s(batch, args.steps, args.warmup)
+    ips, kind, times = cpu_images_per_s(args.workload, batch, args.steps, args.warmup)
     ms = 1000.0 * sum(times) / len(times)
-    sample = f"ResNet-50 train step, batch {batch} per step (bounded sample of the 64-image step), {len(times)} steps"
+    what = "train step" if wl["train"] else "forward pass"
+    sample = (f"{wl['name']}: {what} at batch {batch} per step (bounded sample of the {wl['batch']}-image step; the path "
+              f"loops over images, so img/s is per image), {len(times)} steps; {CPU_GLUE if kind == 'reference' else 'CPU restatement'}")
     line = {
-        "impl": "reference", "metric": METRIC, "value": ips, "unit": UNIT, "n_gpus": args.gpus, "steps": len(times),
+        "impl": "reference", "metric": wl["metric"], "value": ips, "unit": UNIT, "n_gpus": args.gpus, "steps": len(times),
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "resnet50_imagenet_train", "per_gpu_batch": PER_GPU_BATCH, "tensor_format": "NHWC",
+        "config": {"workload": wl["name"], "per_gpu_batch": wl["batch"], "tensor_format": wl["layout"],
                    "device": "host cores", "sample_batch": batch},
         "cpu_baseline": {"value": ips, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample},
         "e2e": {"value": ips, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -197,6 +257,12 @@ def run_ours(args):
 
     wl = WORKLOADS[args.workload]
     batch, hw, train = wl["batch"], wl["hw"], wl["train"]
+    dp_rec = None
+    if world > 1 and train:
+        # correctness of the data-parallel step before anything is timed: P ranks on shards == 1 rank on the whole
+        # batch, replicas bitwise identical (a small batch-norm-free network, a few steps; see pydtnn_b200/dp_check.py)
+        from pydtnn_b200 import dp_check
+        dp_rec = dp_check.run(world, rank)
     np.random.seed(0)                       # identical replicas
     model = Model(batch_size=batch, tensor_format=wl["layout"], dtype=np.float32, comm=True if world > 1 else None,
                   non_blocking_mpi=True, device=dev, **wl["model_kw"])
@@ -284,7 +350,9 @@ def run_ours(args):
         d = per_pass.setdefault(name, [0.0, 0.0, 0])
         d[0] += ms; d[1] += layer.flops_per_pass; d[2] += 1
         key = (f"{layer.hi}x{layer.wi}x{layer.ci}->{layer.co} k{layer.kh} s{layer.vstride}", name)
-        q = per_layer.setdefault(key, [0.0, 0.0, 0])
+        lbytes = 4.0 * model.batch_size * (layer.hi * layer.wi * layer.ci + layer.ho * layer.wo * layer.co) + \
+            4.0 * layer.kh * layer.kw * layer.ci * layer.co
+        q = per_layer.setdefault(key, [0.0, 0.0, 0, layer.flops_per_pass / lbytes])
         q[0] += ms; q[1] += layer.flops_per_pass; q[2] += 1
     conv_min_bytes = 0.0
     for name, layer, e0, e1 in prof:
@@ -344,24 +412,59 @@ def run_ours(args):
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
                 "h2d_bytes_per_step": int(x_host.numel() * 4 + (y_host.numel() * 4 if train else 0)) * world,
-                "d2h_bytes_per_step": int(batch * 4 if train else batch * 1000 * 4) * world},
+                # training reads the two doubles (mean loss, accuracy) the loss kernel leaves on the device
+                "d2h_bytes_per_step": int(16 if train else batch * 1000 * 4) * world},
         "gpu_launches": int(launches),
         "roofline": roofline,
         "final_loss": final_loss,
     }
-    if world == 1 and not args.no_cpu_baseline and args.workload == "resnet50":
+    if dp_rec is not None:
+        line["dp_check"] = dp_rec
+    if world == 1 and not args.no_cpu_baseline:
         threads = _cpu_threads()
-        ips, kind, times = cpu_resnet50_images_per_s(8, 1, 0)
+        cpu_batch = {"resnet50": 8, "vgg16bn": 4, "alexnet": 16}[args.workload]
+        ips, kind, times = cpu_images_per_s(args.workload, cpu_batch, 1, 0)
+        what = "train step" if train else "forward pass"
         line["cpu_baseline"] = {"value": ips, "unit": UNIT, "cores": threads, "kind": kind,
-                                "sample": f"one ResNet-50 train step at batch 8 ({times[0]:.1f} s), NHWC f32, "
-                                          f"reference Cython im2row + NumPy GEMM" if kind == "reference" else
-                                          f"one ResNet-50 train step at batch 8 ({times[0]:.1f} s), NHWC f32, CPU restatement"}
-    if args.layers:
-        line["per_layer"] = {f"{k[0]} {k[1]}": {"ms": v[0] / v[2], "tflops": v[1] / (v[0] * 1e-3) / 1e12}
-                             for k, v in sorted(per_layer.items())}
+                                "sample": f"one {wl['name']} {what} at batch {cpu_batch} ({times[0]:.1f} s), {wl['layout']} f32; "
+                                          + (CPU_GLUE if kind == "reference" else "CPU restatement (oracle/)")}
+    if not args.no_layers:
+        # per-layer convolution table: time, TFLOP/s, and the fraction of the layer's own bound
+        # min(3xTF32 sustained peak, arithmetic intensity x measured HBM bandwidth)
+        table = {}
+        for k, v in sorted(per_layer.items()):
+            tf = v[1] / (v[0] * 1e-3) / 1e12
+            bound = min(peak_3xtf32, v[3] * peaks["hbm_gbs"] / 1e3)
+            table[f"{k[0]} {k[1]}"] = {"ms": round(v[0] / v[2], 5), "tflops": round(tf, 1), "bound_tflops": round(bound, 1),
+                                       "frac": round(tf / bound, 3), "bound": "tensor" if bound >= peak_3xtf32 else "hbm"}
+        line["per_layer"] = table
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def measure_fma_peak(L, f64):
+    """FMA rate the device sustains on register-resident chains (b2c_probe_fma, CUDA events, best of 3), in
+    TFLOP/s: the roofline denominator of the FMA engine."""
+    import ctypes
+    import torch
+    from pydtnn_b200 import _lib
+    blocks, iters = 148 * 8, 20000
+    sink = torch.empty(blocks * 256, dtype=torch.float64 if f64 else torch.float32, device="cuda")
+    flops = ctypes.c_double(0.0)
+    st = torch.cuda.current_stream().cuda_stream
+    dt = _lib.F64 if f64 else _lib.F32
+    _lib.check(L.b2c_probe_fma(dt, blocks, iters, sink.data_ptr(), ctypes.byref(flops), st))
+    best = None
+    for _ in range(3):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        _lib.check(L.b2c_probe_fma(dt, blocks, iters, sink.data_ptr(), ctypes.byref(flops), st))
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        best = ms if best is None or ms < best else best
+    return flops.value / (best * 1e-3) / 1e12
 
 
 def run_single_conv(args):
@@ -393,9 +496,19 @@ def run_single_conv(args):
     dw = torch.empty_like(wt)
     st = torch.cuda.current_stream().cuda_stream
 
+    stats = None
+    if args.conv_bn_stats:
+        sb = L.b2c_conv_stats_bytes(ctypes.byref(desc))
+        if pidx != 0 or not sb:
+            raise SystemExit("--conv-bn-stats needs a forward pass on the float32 NHWC tensor-core path")
+        stats = torch.empty(sb, dtype=torch.uint8, device="cuda")
+
     def call(i):
         x, y = xs[i % nbuf], ys[i % nbuf]
-        if pidx == 0:
+        if pidx == 0 and stats is not None:
+            rc = L.b2c_conv_fprop_stats(ctypes.byref(desc), x.data_ptr(), wt.data_ptr(), None, y.data_ptr(), stats.data_ptr(),
+                                        stats.numel(), ws.data_ptr(), ws.numel(), st)
+        elif pidx == 0:
             rc = L.b2c_conv_fprop(ctypes.byref(desc), x.data_ptr(), wt.data_ptr(), None, None, 0, y.data_ptr(),
                                   ws.data_ptr(), ws.numel(), st)
         elif pidx == 1:
@@ -420,20 +533,29 @@ def run_single_conv(args):
     min_bytes = float(esz) * (n * h * w * ci + k * k * ci * co + n * ho * wo * co)
     peaks = measured_peaks()
     on_tc = engine == _lib.ENGINE_TENSOR
-    # tensor-core engine: measured bf16 / 2 / 3.  FMA engine: nominal FMA peaks of the part (148 SMs x 128 lanes x 2
-    # flops x 1.965 GHz = 74.4 TFLOP/s float32, half of that float64); no measured figure for these exists here.
-    peak = peaks["bf16"] / 6.0 if on_tc else (37.2 if f64 else 74.4)
+    # tensor-core engine: measured bf16 / 2 / 3.  FMA engine: the FMA rate measured in this run by the register-resident
+    # probe kernel (nominal: 148 SMs x 128 lanes x 2 flops x 1.965 GHz = 74.4 TFLOP/s float32, half of that float64).
+    fma_peak = None if on_tc else measure_fma_peak(L, f64)
+    peak = peaks["bf16"] / 6.0 if on_tc else fma_peak
     tflops = flops / (ms * 1e-3) / 1e12
+    cpu = None
+    if not args.no_cpu_baseline:
+        ctf, kind, secs, sn = cpu_conv_pass(n, h, w, ci, co, k, stride, pad, args.conv_pass, args.conv_layout,
+                                            np.float64 if f64 else np.float32)
+        cpu = {"value": ctf, "unit": "TFLOP/s", "cores": _cpu_threads(), "kind": kind,
+               "sample": f"the same pass on {sn} of the {n} images ({secs:.2f} s, best of 3): reference lowering "
+                         f"(Cython im2row/im2col) + NumPy GEMM" + ("" if kind == "reference" else " restated in oracle/")}
     print(json.dumps({
         "metric": "conv_pass_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "dtype": args.conv_dtype, "data": "synthetic",
-        "config": {"workload": f"conv2d_{args.conv_pass}", "shape": args.conv, "tensor_format": args.conv_layout,
+        "config": {"workload": f"conv2d_{args.conv_pass}" + ("+bn_stats" if stats is not None else ""), "shape": args.conv, "tensor_format": args.conv_layout,
                    "engine": "tensor" if on_tc else "fma", "l2": f"{nbuf} rotating buffer sets"},
         "roofline": {"bound": "tensor" if on_tc else "fma", "achieved": tflops, "peak": peak, "unit": "TFLOP/s", "frac": tflops / peak,
                      "peak_basis": (f"{peaks['source']} bf16 burst {peaks['bf16']:.1f} / 2 / 3 (kernel timed alone)" if on_tc
-                                    else "nominal FMA peak: 148 SMs x 128 lanes x 2 x 1.965 GHz" + (" / 2 (float64)" if f64 else "")),
+                                    else "FMA rate measured in this run by the register-resident probe kernel"),
                      "min_bytes": min_bytes, "hbm_gbs_at_min_bytes": min_bytes / (ms * 1e-3) / 1e9,
-                     "arithmetic_intensity": flops / min_bytes}}), flush=True)
+                     "arithmetic_intensity": flops / min_bytes},
+        "cpu_baseline": cpu}), flush=True)
 
 
 SWEEP_AXES = ((7, 14, 28, 56, 112), (64, 128, 256, 512), (64, 128, 256, 512), (1, 3, 5, 7), (1, 2))
@@ -466,6 +588,7 @@ def run_sweep(args):
     combos = [(d, l) for d in args.sweep_dtypes.split(",") for l in args.sweep_layouts.split(",")]
     gen = torch.Generator(device="cuda").manual_seed(0)
     rows, launches0 = [], L.b2c_launch_count()
+    fma64_peak = None
     for dname, layout in combos:
         f64, nchw = dname == "f64", layout == "NCHW"
         tdt, esz = (torch.float64, 8) if f64 else (torch.float32, 4)
@@ -475,7 +598,9 @@ def run_sweep(args):
         xin = torch.randn(pool_el, device="cuda", generator=gen, dtype=tdt)
         yin = torch.randn(pool_el, device="cuda", generator=gen, dtype=tdt)
         out = torch.empty(pool_el, device="cuda", dtype=tdt)
-        peak = 37.2 if f64 else peaks["bf16"] / 6.0
+        if f64 and fma64_peak is None:
+            fma64_peak = measure_fma_peak(L, True)
+        peak = fma64_peak if f64 else peaks["bf16"] / 6.0
         for n, h, w, ci, co, k, s, p in pts:
             ho = wo = (h + 2 * p - k) // s + 1
             desc = _lib.ConvDesc(_lib.LAYOUT_NCHW if nchw else _lib.LAYOUT_NHWC, _lib.F64 if f64 else _lib.F32,
@@ -536,11 +661,29 @@ def run_sweep(args):
                 "max_tflops": max(r[10] for r in sel), "median_frac": statistics.median(fr),
                 "p10_frac": fr[len(fr) // 10], "min_frac": fr[0], "share_at_or_above_0.6": sum(v >= 0.6 for v in fr) / len(fr),
                 "on_tensor_engine": sum(r[8] == "tensor" for r in sel)}
+    cpu = None
+    if not args.no_cpu_baseline:
+        # the reference's CPU path on a stated subset: 16 evenly spaced geometries, float32 NHWC, three passes each,
+        # about 2 GFLOP of work per pass (a few images of the batch)
+        sub = sweep_points()[20::40][:16]
+        crow, t0 = [], time.perf_counter()
+        for n, h, w, ci, co, k, sstr, p in sub:
+            per_image = 2.0 * ((h + 2 * p - k) // sstr + 1) ** 2 * co * ci * k * k
+            sn = int(max(1, min(n, 2e9 // per_image)))
+            for pname in ("fprop", "dgrad", "wgrad"):
+                ctf, kind, _, _ = cpu_conv_pass(n, h, w, ci, co, k, sstr, p, pname, "NHWC", np.float32, sample_n=sn, reps=1)
+                gpu = [r for r in rows if r[0] == "f32" and r[1] == "NHWC" and r[2] == pname and r[3:8] == (h, ci, co, k, sstr)]
+                crow.append((pname, h, ci, co, k, sstr, ctf, gpu[0][10] if gpu else None))
+        cpu = {"value": statistics.median(r[6] for r in crow), "unit": "TFLOP/s (median over the subset)", "cores": _cpu_threads(),
+               "kind": kind, "sample": f"{len(sub)} geometries x 3 passes, float32 NHWC, a few images each ({time.perf_counter() - t0:.0f} s)",
+               "points": [{"pass": r[0], "hw": r[1], "ci": r[2], "co": r[3], "k": r[4], "stride": r[5], "cpu_tflops": round(r[6], 4),
+                           "gpu_tflops": None if r[7] is None else round(r[7], 1)} for r in crow]}
     print(json.dumps({
+        "cpu_baseline": cpu,
         "metric": "conv_sweep_roofline_frac", "unit": "fraction of min(compute peak, intensity x HBM)", "n_gpus": 1,
         "data": "synthetic", "higher_is_better": True, "points": len(rows), "iters_per_point": args.sweep_iters,
         "gpu_launches": L.b2c_launch_count() - launches0,
-        "peaks": {"f32_tflops": peaks["bf16"] / 6.0, "f64_tflops": 37.2, "hbm_gbs": peaks["hbm_gbs"], "source": peaks["source"]},
+        "peaks": {"f32_tflops": peaks["bf16"] / 6.0, "f64_tflops": fma64_peak, "f64_basis": "measured FMA probe", "hbm_gbs": peaks["hbm_gbs"], "source": peaks["source"]},
         "config": {"workload": "conv2d shape sweep, batch 32", "l2": "operands rotate through > 2x L2"},
         "summary": summary}), flush=True)
 
@@ -668,7 +811,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="resnet50",
                     help="whole-network configuration to time (default: the one the headline metric is quoted on)")
-    ap.add_argument("--layers", action="store_true", help="add per-layer convolution timings to the JSON line")
+    ap.add_argument("--layers", action="store_true", help="(default now) per-layer convolution timings are in the JSON line")
+    ap.add_argument("--no-layers", action="store_true", help="leave the per-layer convolution table out of the JSON line")
     ap.add_argument("--conv", default=None, help="n,h,w,ci,co,k,stride,pad: time one Conv2D pass instead of the model")
     ap.add_argument("--fc", default=None, help="batch,in,out: time one fully connected layer instead of the model")
     ap.add_argument("--bn", default=None, help="n,h,w,c: time training-mode batch norm + ReLU forward and backward on one tensor")
@@ -676,6 +820,8 @@ def main():
     ap.add_argument("--conv-dtype", default="f32", choices=["f32", "f64"])
     ap.add_argument("--conv-layout", default="NHWC", choices=["NHWC", "NCHW"])
     ap.add_argument("--conv-engine", default="auto", choices=["auto", "fma", "tensor"])
+    ap.add_argument("--conv-bn-stats", action="store_true",
+                    help="with --conv (forward pass): also take the per-channel batch sums of the output (b2c_conv_fprop_stats)")
     ap.add_argument("--sweep", action="store_true", help="time the whole Conv2D shape sweep instead of the model")
     ap.add_argument("--sweep-dtypes", default="f32,f64")
     ap.add_argument("--sweep-layouts", default="NHWC,NCHW")

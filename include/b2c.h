@@ -98,6 +98,18 @@ int b2c_conv_fprop(const b2c_conv_desc *desc, const void *x, const void *w, cons
                    const b2c_bn_params *bn, int relu, void *y,
                    void *workspace, size_t workspace_bytes, void *stream);
 
+/* The forward pass for a convolution that feeds a training-mode batch norm (the Conv2D -> BatchNormalization pairs the
+ * reference's fusion flags name, pydtnn/parser.py:74-77; the statistics are those of
+ * pydtnn/backends/cpu/layers/batch_normalization_cpu.py:65-70): y = conv(x, w) + bias as b2c_conv_fprop writes it, and
+ * in `stats` the per-channel sum and sum of squares of y, taken from the tiles on their way to memory, so that the batch
+ * norm does not read y a second time for them.  `stats` is an opaque DEVICE buffer of b2c_conv_stats_bytes(desc) bytes
+ * (16-byte aligned) that b2c_bn_train_forward_prestats consumes; it is rewritten by every call.
+ * b2c_conv_stats_bytes returns 0, and b2c_conv_fprop_stats B2C_ERR_UNSUPPORTED, for shapes outside the float32 NHWC
+ * tensor-core path (callers then use b2c_conv_fprop and b2c_bn_train_forward). */
+size_t b2c_conv_stats_bytes(const b2c_conv_desc *desc);
+int b2c_conv_fprop_stats(const b2c_conv_desc *desc, const void *x, const void *w, const void *bias, void *y,
+                         void *stats, size_t stats_bytes, void *workspace, size_t workspace_bytes, void *stream);
+
 /* dx = conv_transpose(dy, w) (the scatter-add of row2im / col2im written as a gather).
  * Replaces cudnnConvolutionBackwardData, conv_2d_gpu.py:224-229, and sconvGemm*_back,
  * pydtnn/backends/cpu/libs/conv_gemm.py:311-330. */
@@ -149,6 +161,15 @@ int b2c_bn_train_forward_residual(int dtype, int layout, int n, int c, int hw, c
                                   const void *beta, void *running_mean, void *running_var, double momentum,
                                   double eps, const void *addend, int relu, void *y, void *save_mean,
                                   void *save_inv_std, void *scratch, size_t scratch_bytes, void *stream);
+
+/* b2c_bn_train_forward (float32, NHWC) with the batch sums already taken by b2c_conv_fprop_stats on the convolution
+ * that wrote x: mean, inverse standard deviation and the running averages come from `stats` (summed in double, in a
+ * fixed order), then y = relu?(bn(x) [+ addend]) in one pass over x.  addend may be NULL (see
+ * b2c_bn_train_forward_residual).  scratch: as for b2c_bn_train_forward.  Backward is b2c_bn_train_backward, unchanged. */
+int b2c_bn_train_forward_prestats(int n, int c, int hw, const void *x, const void *stats, size_t stats_bytes,
+                                  const void *gamma, const void *beta, void *running_mean, void *running_var,
+                                  double momentum, double eps, int fuse_relu, const void *addend, void *y,
+                                  void *save_mean, void *save_inv_std, void *scratch, size_t scratch_bytes, void *stream);
 
 /* b2c_bn_train_forward for callers that must not allocate and have no scratch buffer to lend: hosts
  * that give all device memory to their own pool at start-up and then forbid allocation (a late
@@ -213,6 +234,23 @@ int b2c_softmax_backward(int dtype, int rows, int cols, const void *dy, const vo
  *  pydtnn/backends/gpu/metrics/categorical_accuracy_gpu.py:33-51). */
 int b2c_cce_forward_backward(int dtype, int rows, int cols, const void *probs, const int32_t *labels,
                              int global_batch, double eps, void *row_loss, int32_t *hit, void *dx, void *stream);
+
+/* Totals of b2c_cce_forward_backward's per-row outputs, written to DEVICE memory as two doubles:
+ * out2[0] = -sum(row_loss) / rows (the batch's mean loss), out2[1] = 100 * sum(hit) / rows (accuracy in per cent;
+ * hit may be NULL -> 0).  These are the values the reference divides by the process count and sums over ranks,
+ * pydtnn/model.py:426-438; a data-parallel caller all-reduces the two doubles in place. */
+int b2c_cce_totals(int dtype, int rows, const void *row_loss, const int32_t *hit, double *out2, void *stream);
+
+/* inv_std[i] = 1 / sqrt(running_var[i] + eps), evaluated in double and rounded once: the per-channel factor of the
+ * inference-mode batch norm, pydtnn/layers/batch_normalization.py:61 and
+ * pydtnn/backends/cpu/layers/batch_normalization_cpu.py:92-94 (computed there on the host). */
+int b2c_bn_inv_std(int dtype, int c, const void *running_var, double eps, void *inv_std, void *stream);
+
+/* Diagnostic: launches `blocks` CTAs of 256 threads that each run `iters` rounds of 8 independent register-resident
+ * fused multiply-adds, and reports the floating-point operations of the launch in *flops (may be NULL).  Timed by the
+ * caller, it gives the FMA rate the device sustains: the roofline denominator of the FMA engine.  sink: blocks*256
+ * elements, never written.  No counterpart in the reference. */
+int b2c_probe_fma(int dtype, int blocks, int iters, void *sink, double *flops, void *stream);
 
 /* SGD with momentum over one flat tensor: v = m*v + dw; w -= lr*(decay*w + v)
  * (Nesterov: w -= lr*(decay*w + dw + m*v)); pydtnn/backends/gpu/optimizers/sgd_gpu.py:40-47. */

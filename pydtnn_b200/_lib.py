@@ -44,6 +44,12 @@ PROTOTYPES = {
     "b2c_conv_engine_for": (c_int, [POINTER(ConvDesc), c_int]),
     "b2c_conv_fprop": (c_int, [POINTER(ConvDesc), c_void_p, c_void_p, c_void_p, POINTER(BnParams), c_int, c_void_p,
                                c_void_p, c_size_t, c_void_p]),
+    "b2c_conv_stats_bytes": (c_size_t, [POINTER(ConvDesc)]),
+    "b2c_conv_fprop_stats": (c_int, [POINTER(ConvDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t,
+                                     c_void_p, c_size_t, c_void_p]),
+    "b2c_bn_train_forward_prestats": (c_int, [c_int, c_int, c_int, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p,
+                                              c_void_p, c_void_p, c_double, c_double, c_int, c_void_p, c_void_p,
+                                              c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
     "b2c_conv_dgrad": (c_int, [POINTER(ConvDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
     "b2c_conv_wgrad": (c_int, [POINTER(ConvDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t,
                                c_void_p]),
@@ -77,6 +83,9 @@ PROTOTYPES = {
     "b2c_softmax_backward": (c_int, [c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "b2c_cce_forward_backward": (c_int, [c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_double, c_void_p, c_void_p,
                                          c_void_p, c_void_p]),
+    "b2c_cce_totals": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "b2c_bn_inv_std": (c_int, [c_int, c_int, c_void_p, c_double, c_void_p, c_void_p]),
+    "b2c_probe_fma": (c_int, [c_int, c_int, c_int, c_void_p, POINTER(c_double), c_void_p]),
     "b2c_sgd_update": (c_int, [c_int, c_int64, c_void_p, c_void_p, c_void_p, c_double, c_double, c_double, c_int,
                                c_void_p]),
 }

@@ -53,6 +53,7 @@ class BatchNormalizationGPU(LayerGPU, BatchNormalization):
         if self.need_dx:
             self.dx = TensorGPU(empty(x.ary.shape, m.dtype), m.tensor_format)
         self.fuse_relu = False           # set by the model's fusion pass (BN followed by ReLU)
+        self.prestats = None             # (buffer, bytes) left by the preceding convolution's forward pass of this step
         self.residual = None             # (other branch, output) while an addition block folds its sum + ReLU in here
         self._dt = _lib.dtype_code(m.dtype)
         self._hw = self.hi * self.wi if self.spatial else 1
@@ -62,6 +63,18 @@ class BatchNormalizationGPU(LayerGPU, BatchNormalization):
         m = self.model
         L = _lib.lib()
         self.x = x
+        if m.mode == TRAIN_MODE and self.prestats is not None:
+            # the convolution that wrote x already summed it per channel: statistics from those sums, one pass over x
+            st, nbytes = self.prestats
+            self.prestats = None
+            addend, out, relu = (self.residual[0], self.residual[1], 1) if self.residual is not None else (None, self.y, int(self.fuse_relu))
+            _lib.check(L.b2c_bn_train_forward_prestats(
+                m.batch_size, self.ci, self._hw, x.ptr, st.data_ptr(), nbytes, self.gamma.ptr, self.beta.ptr,
+                self.running_mean.ptr, self.running_var.ptr, float(self.momentum), float(self.epsilon), relu,
+                addend.ptr if addend is not None else None, out.ptr, self.save_mean.ptr, self.save_inv_var.ptr,
+                wsp.reduction_scratch().data_ptr(), wsp.reduction_scratch().numel() * 8, m.stream_handle))
+            self.updated_running_var = True
+            return out
         if m.mode == TRAIN_MODE and self.residual is not None:
             # last batch norm of a residual branch: out = relu(bn(x) + other branch), written to the block's ReLU
             addend, out = self.residual
@@ -81,16 +94,22 @@ class BatchNormalizationGPU(LayerGPU, BatchNormalization):
                                               wsp.reduction_scratch().numel() * 8, m.stream_handle))
             self.updated_running_var = True
         elif m.mode == EVALUATE_MODE:
-            if self.updated_running_var:
-                var = self.running_var.ary.get().astype(np.float64)
-                self._inv_std.set((1.0 / np.sqrt(var + self.epsilon)).astype(m.dtype))
-                self.updated_running_var = False
             _lib.check(L.b2c_bn_inference(self._dt, _layout(m), m.batch_size, self.ci, self._hw, x.ptr,
-                                          self.running_mean.ptr, self._inv_std.gpudata, self.gamma.ptr,
+                                          self.running_mean.ptr, self.inference_inv_std().gpudata, self.gamma.ptr,
                                           self.beta.ptr, int(self.fuse_relu), self.y.ptr, m.stream_handle))
         else:
             raise ValueError("Unexpected model mode")
         return self.y
+
+    def inference_inv_std(self):
+        """1 / sqrt(running_var + eps) on the device, recomputed (one small kernel, no host round trip) only after
+        the running variance changed: a training step or a checkpoint load
+        (pydtnn/backends/cpu/layers/batch_normalization_cpu.py:92-94 refreshes it under the same flag)."""
+        if self.updated_running_var:
+            _lib.check(_lib.lib().b2c_bn_inv_std(self._dt, self.ci, self.running_var.ptr, float(self.epsilon),
+                                                 self._inv_std.gpudata, self.model.stream_handle))
+            self.updated_running_var = False
+        return self._inv_std
 
     def backward(self, dy):
         m = self.model

@@ -5,10 +5,10 @@ import ctypes
 
 import numpy as np
 
-from .... import _lib
+from .... import _lib, tracer
 from ....layers import Conv2D, Conv2DBatchNormalization, Conv2DBatchNormalizationRelu, Conv2DRelu
-from ....tensor_gpu import TensorGPU, empty, to_gpu
-from ....utils import PYDTNN_TENSOR_FORMAT_NCHW, PYDTNN_TENSOR_FORMAT_NHWC
+from ....tensor_gpu import TensorGPU, empty
+from ....utils import PYDTNN_TENSOR_FORMAT_NCHW, PYDTNN_TENSOR_FORMAT_NHWC, TRAIN_MODE
 from .. import memory_allocation as wsp
 from .layer_gpu import LayerGPU
 
@@ -19,6 +19,8 @@ class Conv2DGPU(LayerGPU, Conv2D):
         super().__init__(*args, **kwargs)
         self.desc = None
         self.engine = _lib.ENGINE_AUTO
+        self.stats_for_bn = None         # set by the model's fusion pass: the BatchNormalization this layer feeds
+        self.stats_bytes = 0
 
     def _make_desc(self):
         m = self.model
@@ -54,18 +56,25 @@ class Conv2DGPU(LayerGPU, Conv2D):
         need = max(L.b2c_conv_workspace_bytes(ctypes.byref(self.desc), p) for p in
                    (_lib.PASS_FPROP, _lib.PASS_DGRAD, _lib.PASS_WGRAD))
         wsp.require(need)
+        # can this layer's forward pass leave the batch sums of its output for a following batch norm?
+        self.stats_bytes = int(L.b2c_conv_stats_bytes(ctypes.byref(self.desc)))
 
     @property
     def flops_per_pass(self):
         """2*M*K*Co, padding taps counted (the reference's model, pydtnn/performance_models.py:68-70)."""
         return 2 * self.model.batch_size * self.ho * self.wo * self.co * self.ci * self.kh * self.kw
 
+    _OPS = {"fprop": tracer.PYDTNN_OPS_FORWARD_CUDNN, "wgrad": tracer.PYDTNN_OPS_BACKWARD_CUDNN_DW,
+            "dgrad": tracer.PYDTNN_OPS_BACKWARD_CUDNN_DX}
+
     def _timed(self, name, call):
-        """Run one pass; when the model carries a ``conv_profile`` list, bracket it with CUDA events
-        on the launching stream (read back by the benchmark after the timed region)."""
+        """Run one pass inside its per-operation tracer event (off by default); when the model carries a
+        ``conv_profile`` list, bracket it with CUDA events on the launching stream (read back by the benchmark
+        after the timed region)."""
         prof = getattr(self.model, "conv_profile", None)
         if prof is None:
-            _lib.check(call())
+            with self.model.tracer.op_region(self, self._OPS[name]):
+                _lib.check(call())
             return
         import torch
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -77,6 +86,15 @@ class Conv2DGPU(LayerGPU, Conv2D):
     def forward(self, x):
         L = _lib.lib()
         self.x = x          # backward reads the tensor this call saw (a fused predecessor may hand over its own buffer)
+        bn = self.stats_for_bn
+        if bn is not None and self.model.mode == TRAIN_MODE:
+            # training step, a batch norm follows: the same pass also sums y and y^2 per channel while the tiles leave
+            st = wsp.conv_stats()
+            self._timed("fprop", lambda: L.b2c_conv_fprop_stats(
+                ctypes.byref(self.desc), x.ptr, self.weights.ptr, self.biases.ptr if self.use_bias else None,
+                self.y.ptr, st.data_ptr(), self.stats_bytes, wsp.ptr(), wsp.size(), self.model.stream_handle))
+            bn.prestats = (st, self.stats_bytes)
+            return self.y
         self._timed("fprop", lambda: L.b2c_conv_fprop(
             ctypes.byref(self.desc), x.ptr, self.weights.ptr, self.biases.ptr if self.use_bias else None, None, 0,
             self.y.ptr, wsp.ptr(), wsp.size(), self.model.stream_handle))
@@ -110,12 +128,17 @@ class _FusedConvInference(Conv2DGPU):
             self.bn_layer = from_parent_2
 
     def _refresh_bn(self):
+        """Point the epilogue at the batch-norm layer's vectors; its inv_std lives on the device and is recomputed
+        there only after the running variance changed (no host copy, no allocation per call)."""
         bn = self.bn_layer
-        var = bn.running_var.ary.get().astype(np.float64)
-        inv_std = (1.0 / np.sqrt(var + bn.epsilon)).astype(self.model.dtype)
-        self._inv_std = to_gpu(inv_std.reshape(-1))
-        self._bn = _lib.BnParams(bn.running_mean.ary.gpudata, self._inv_std.gpudata, bn.gamma.ary.gpudata,
-                                 bn.beta.ary.gpudata)
+        inv_std = bn.inference_inv_std()
+        if getattr(self, "_bn", None) is None:
+            self._bn = _lib.BnParams(bn.running_mean.ary.gpudata, inv_std.gpudata, bn.gamma.ary.gpudata,
+                                     bn.beta.ary.gpudata)
+
+    def _relu_flag(self):
+        # a batch norm that absorbed its ReLU for training (BN+ReLU fusion) keeps it when folded into the convolution
+        return self._with_relu or (self._with_bn and getattr(self.bn_layer, "fuse_relu", False))
 
     def forward(self, x):
         from ....utils import TRAIN_MODE
@@ -126,7 +149,7 @@ class _FusedConvInference(Conv2DGPU):
         L = _lib.lib()
         self._timed("fprop", lambda: L.b2c_conv_fprop(
             ctypes.byref(self.desc), x.ptr, self.weights.ptr, self.biases.ptr if self.use_bias else None,
-            ctypes.byref(self._bn) if self._with_bn else None, int(self._with_relu),
+            ctypes.byref(self._bn) if self._with_bn else None, int(self._relu_flag()),
             self.y.ptr, wsp.ptr(), wsp.size(), self.model.stream_handle))
         return self.y
 

@@ -2,7 +2,7 @@
 Weights are (in, out) row-major as in the reference; biases (1, out)."""
 import numpy as np
 
-from .... import _lib
+from .... import _lib, tracer
 from ....layers import FC
 from ....tensor_gpu import TensorGPU, empty
 from .. import memory_allocation as wsp
@@ -35,17 +35,30 @@ class FCGPU(LayerGPU, FC):
     def forward(self, x):
         m = self.model
         self.x = x
-        _lib.check(_lib.lib().b2c_fc_forward(self._dt, self._engine, m.batch_size, self._in, self._out, x.ptr,
-                                             self.weights.ptr, self.biases.ptr if self.use_bias else None,
-                                             self.y.ptr, wsp.ptr(), wsp.size(), m.stream_handle))
+        with m.tracer.op_region(self, tracer.PYDTNN_OPS_FORWARD_CUBLAS_MATMUL):       # the bias is added in the same call
+            _lib.check(_lib.lib().b2c_fc_forward(self._dt, self._engine, m.batch_size, self._in, self._out, x.ptr,
+                                                 self.weights.ptr, self.biases.ptr if self.use_bias else None,
+                                                 self.y.ptr, wsp.ptr(), wsp.size(), m.stream_handle))
         return self.y
 
     def backward(self, dy):
         m = self.model
-        _lib.check(_lib.lib().b2c_fc_backward(self._dt, self._engine, m.batch_size, self._in, self._out, self.x.ptr,
-                                              dy.ptr, self.weights.ptr, self.dw.ptr,
-                                              self.db.ptr if self.use_bias else None,
-                                              self.dx.ptr if self.need_dx else None,
-                                              wsp.ptr(), wsp.size(), m.stream_handle))
+        L = _lib.lib()
+        if not (m.tracer.enabled and m.tracer.ops):
+            _lib.check(L.b2c_fc_backward(self._dt, self._engine, m.batch_size, self._in, self._out, self.x.ptr,
+                                         dy.ptr, self.weights.ptr, self.dw.ptr, self.db.ptr if self.use_bias else None,
+                                         self.dx.ptr if self.need_dx else None, wsp.ptr(), wsp.size(), m.stream_handle))
+        else:
+            # per-operation tracing: the weight (+ bias) gradient and the input gradient as separate calls, each in
+            # its own event (the reference brackets its three cuBLAS calls the same way)
+            with m.tracer.op_region(self, tracer.PYDTNN_OPS_BACKWARD_CUBLAS_MATMUL_DW):
+                _lib.check(L.b2c_fc_backward(self._dt, self._engine, m.batch_size, self._in, self._out, self.x.ptr,
+                                             dy.ptr, self.weights.ptr, self.dw.ptr, self.db.ptr if self.use_bias else None,
+                                             None, wsp.ptr(), wsp.size(), m.stream_handle))
+            if self.need_dx:
+                with m.tracer.op_region(self, tracer.PYDTNN_OPS_BACKWARD_CUBLAS_MATMUL_DX):
+                    _lib.check(L.b2c_fc_backward(self._dt, self._engine, m.batch_size, self._in, self._out, self.x.ptr,
+                                                 dy.ptr, self.weights.ptr, None, None, self.dx.ptr, wsp.ptr(), wsp.size(),
+                                                 m.stream_handle))
         if self.need_dx:
             return self.dx

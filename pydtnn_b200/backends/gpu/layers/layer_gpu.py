@@ -7,6 +7,7 @@ the bucketer launches one NCCL all-reduce per contiguous bucket, ordered after t
 kernels by a stream event, so no host synchronisation happens inside a step."""
 from abc import ABC
 
+from .... import tracer
 from ....layers.base import Layer
 
 
@@ -33,7 +34,8 @@ class LayerGPU(Layer, ABC):
     def reduce_weights_async(self):
         if self.model.comm is None or not self.grad_vars:
             return
-        self.model.bucketer.mark_ready(self)
+        with self.model.tracer.op_region(self, tracer.PYDTNN_OPS_ALLREDUCE_DW):
+            self.model.bucketer.mark_ready(self)
 
     def wait_allreduce_async(self):
         if self.model.comm is None or not self.grad_vars:

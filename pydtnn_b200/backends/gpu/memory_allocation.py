@@ -43,3 +43,21 @@ def require_reduction_scratch(channels, device=None):
 
 def reduction_scratch():
     return _red
+
+
+_stats = None
+
+
+def require_conv_stats(nbytes, device=None):
+    """Shared buffer for the batch statistics a convolution leaves for the batch norm that follows it (consumed
+    before the next convolution runs, so one buffer serves every Conv2D -> BatchNormalization pair)."""
+    global _stats
+    nbytes = int(nbytes)
+    if _stats is None or _stats.numel() < nbytes:
+        device = device or (_stats.device if _stats is not None else torch.device("cuda", torch.cuda.current_device()))
+        _stats = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    return _stats
+
+
+def conv_stats():
+    return _stats

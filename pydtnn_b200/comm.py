@@ -18,10 +18,17 @@ import torch
 import torch.distributed as dist
 
 
+class CommError(RuntimeError):
+    """The exchange between ranks failed: a rank never joined, left, or disagrees about the gradient layout.
+    Raised on the host; no kernel is left waiting (the reference's NCCL wrapper raises ``NcclError`` on a non-zero
+    status, pydtnn/backends/gpu/libs/libnccl.py:54-77)."""
+
+
 def init_process_group_from_env(backend=None, timeout_s=120):
     """Join the job described by RANK / WORLD_SIZE / MASTER_ADDR / MASTER_PORT (as set by
     ``torch.distributed.run``). Returns (rank, world_size); (0, 1) when not launched as a job.
-    Replaces the MPI bootstrap + ncclCommInitRank of pydtnn/model.py:141-171."""
+    Replaces the MPI bootstrap + ncclCommInitRank of pydtnn/model.py:141-171.  A job whose ranks do not all
+    arrive within ``timeout_s`` seconds ends with ``CommError`` on the ranks that did."""
     import datetime
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if world <= 1:
@@ -33,7 +40,13 @@ def init_process_group_from_env(backend=None, timeout_s=120):
         kwargs = {}
         if backend == "nccl":
             kwargs["device_id"] = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
-        dist.init_process_group(backend=backend, timeout=datetime.timedelta(seconds=timeout_s), **kwargs)
+        try:
+            dist.init_process_group(backend=backend, timeout=datetime.timedelta(seconds=timeout_s), **kwargs)
+        except Exception as e:
+            if dist.is_initialized():
+                dist.destroy_process_group()
+            raise CommError(f"rank {os.environ.get('RANK', '?')} of {world}: the process group did not form within "
+                            f"{timeout_s} s (a rank never joined?): {type(e).__name__}: {e}") from e
     return dist.get_rank(), dist.get_world_size()
 
 
@@ -70,8 +83,30 @@ class GradientBucketer:
         for b, bk in enumerate(self.buckets):
             for idx in bk["members"]:
                 self.bucket_of[idx] = b
+        self._check_same_layout()
         self._built = True
         self.reset()
+
+    def _check_same_layout(self):
+        """Every rank must cut the same buckets, or an all-reduce would pair ranges of different lengths (NCCL then
+        hangs or corrupts memory).  The ranks compare a short signature of their bucket lists once, before the first
+        all-reduce, and all of them raise if any differs."""
+        if self.group is None:
+            return
+        sig = [len(self.arena.entries), len(self.buckets), sum(n for _, _, n in self.arena.entries)]
+        h = 1469598103934665603
+        for bk in self.buckets:
+            for v in (bk["chunk"], bk["start"], bk["end"]):
+                h = ((h ^ v) * 1099511628211) % (1 << 62)
+        sig.append(h)
+        mine = torch.tensor(sig, dtype=torch.int64, device=self.arena.device)
+        world = dist.get_world_size(self.group)
+        theirs = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(theirs, mine, group=self.group)
+        rows = [t.cpu().tolist() for t in theirs]
+        if any(r != rows[0] for r in rows):
+            raise CommError("gradient arenas differ between ranks (entries, buckets, elements, layout hash per rank): "
+                            f"{rows}")
 
     def reset(self):
         if not self._built:
@@ -95,8 +130,12 @@ class GradientBucketer:
             if idx in pend:
                 pend.discard(idx)
                 if not pend and self._works[b] is None:
-                    self._works[b] = dist.all_reduce(self._view(b), op=dist.ReduceOp.SUM, group=self.group,
-                                                     async_op=True)
+                    try:
+                        self._works[b] = dist.all_reduce(self._view(b), op=dist.ReduceOp.SUM, group=self.group,
+                                                         async_op=True)
+                    except Exception as e:
+                        raise CommError(f"all-reduce of gradient bucket {b} could not be issued: "
+                                        f"{type(e).__name__}: {e}") from e
                     self.launch_order.append(b)
 
     def mark_ready(self, layer):
@@ -104,7 +143,10 @@ class GradientBucketer:
 
     def wait_bucket(self, b):
         if self._works[b] is not None and not self._done[b]:
-            self._works[b].wait()
+            try:
+                self._works[b].wait()
+            except Exception as e:          # a rank that left or a collective that timed out surfaces here, on the host
+                raise CommError(f"all-reduce of gradient bucket {b} failed: {type(e).__name__}: {e}") from e
             self._done[b] = True
 
     def wait_for(self, layer):

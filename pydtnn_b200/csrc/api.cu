@@ -98,6 +98,23 @@ extern "C" int b2c_conv_fprop(const b2c_conv_desc* desc, const void* x, const vo
     return fma_fprop(g, x, w, bias, bn, relu, y, ws, ws_bytes, (cudaStream_t)stream);
 }
 
+extern "C" size_t b2c_conv_stats_bytes(const b2c_conv_desc* desc) {
+    Geo g; if (make_geo(desc, g)) return 0;
+    if (g.dtype != B2C_F32) return 0;
+    int e; if (pick_engine(g, B2C_PASS_FPROP, e) || e != B2C_ENGINE_TENSOR) return 0;
+    return tc_stats_bytes(g);
+}
+
+extern "C" int b2c_conv_fprop_stats(const b2c_conv_desc* desc, const void* x, const void* w, const void* bias, void* y,
+                                    void* stats, size_t stats_bytes, void* ws, size_t ws_bytes, void* stream) {
+    Geo g; int rc = make_geo(desc, g); if (rc) return rc;
+    if (!x || !w || !y || !stats) return B2C_ERR_NULL_POINTER;
+    if (g.dtype != B2C_F32) return B2C_ERR_UNSUPPORTED;
+    int e; rc = pick_engine(g, B2C_PASS_FPROP, e); if (rc) return rc;
+    if (e != B2C_ENGINE_TENSOR) return B2C_ERR_UNSUPPORTED;
+    return tc_fprop_stats(g, x, w, bias, y, stats, stats_bytes, ws, ws_bytes, (cudaStream_t)stream);
+}
+
 extern "C" int b2c_conv_dgrad(const b2c_conv_desc* desc, const void* dy, const void* w, void* dx,
                               void* ws, size_t ws_bytes, void* stream) {
     Geo g; int rc = make_geo(desc, g); if (rc) return rc;

@@ -386,6 +386,45 @@ __global__ void __launch_bounds__(256) bn_bwd_dx_v4_kernel(const float4* __restr
     }
 }
 
+// First stage of the batch statistics from the partial sums a convolution left while it stored its output
+// (conv_tc.cu): `sums` = [rows][2][c] floats, one row per 32 output rows.  Block (32 channels, 8 row lanes), grid
+// (c / 32, chunks): a thread adds the rows of its chunk, 8 apart, in index order in double; the 8 row lanes are added
+// in lane order; result partial[chunk][2][c] in double, the input format of reduce2_final_warp_kernel.
+__global__ void __launch_bounds__(256) bn_conv_sums_kernel(const float* __restrict__ sums, int rows, int c, double* __restrict__ partial)
+{
+    pdl_prologue();
+    __shared__ double s0[8][33], s1[8][33];
+    const int ch = blockIdx.x * 32 + threadIdx.x;
+    const int per = (rows + gridDim.y - 1) / gridDim.y;
+    const int r0 = blockIdx.y * per, r1 = r0 + per < rows ? r0 + per : rows;
+    double a0 = 0.0, a1 = 0.0;
+    if (ch < c) {
+        int i = r0 + threadIdx.y;
+        for (; i + 24 < r1; i += 32) {          // four independent row pairs in flight, added in index order
+            float u0[4], u1[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                u0[u] = __ldcg(sums + ((size_t)(i + 8 * u) * 2) * c + ch);
+                u1[u] = __ldcg(sums + ((size_t)(i + 8 * u) * 2 + 1) * c + ch);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++) { a0 += (double)u0[u]; a1 += (double)u1[u]; }
+        }
+        for (; i < r1; i += 8) {
+            a0 += (double)__ldcg(sums + ((size_t)i * 2) * c + ch);
+            a1 += (double)__ldcg(sums + ((size_t)i * 2 + 1) * c + ch);
+        }
+    }
+    s0[threadIdx.y][threadIdx.x] = a0; s1[threadIdx.y][threadIdx.x] = a1;
+    __syncthreads();
+    if (threadIdx.y == 0 && ch < c) {
+        double t0 = 0.0, t1 = 0.0;
+        for (int i = 0; i < 8; i++) { t0 += s0[i][threadIdx.x]; t1 += s1[i][threadIdx.x]; }
+        partial[((size_t)blockIdx.y * 2 + 0) * c + ch] = t0;
+        partial[((size_t)blockIdx.y * 2 + 1) * c + ch] = t1;
+    }
+}
+
 static V4Geo v4_apply_geo(int64_t rows, int c)
 {
     V4Geo g = v4_geo(rows, c, 1 << 20);
@@ -858,6 +897,54 @@ __global__ void cce_kernel(const T* __restrict__ probs, const int32_t* __restric
     }
 }
 
+// Totals of the loss kernel's per-row outputs: out[0] = -sum(row_loss) / rows (the mean loss), out[1] = 100 * hits /
+// rows (accuracy in per cent).  One block; every thread adds its rows in index order in double, then a fixed tree.
+template <typename T>
+__global__ void cce_totals_kernel(const T* __restrict__ row_loss, const int32_t* __restrict__ hit, int rows, double* __restrict__ out)
+{
+    pdl_prologue();
+    __shared__ double s0[256], s1[256];
+    double a0 = 0.0, a1 = 0.0;
+    for (int i = threadIdx.x; i < rows; i += 256) { a0 += (double)row_loss[i]; a1 += hit ? (double)hit[i] : 0.0; }
+    s0[threadIdx.x] = a0; s1[threadIdx.x] = a1;
+    __syncthreads();
+    for (int s = 128; s > 0; s >>= 1) {
+        if (threadIdx.x < s) { s0[threadIdx.x] += s0[threadIdx.x + s]; s1[threadIdx.x] += s1[threadIdx.x + s]; }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) { out[0] = -s0[0] / (double)rows; out[1] = 100.0 * s1[0] / (double)rows; }
+}
+
+// inv_std[c] = 1 / sqrt(var[c] + eps), evaluated in double and rounded once (what NumPy gives for a float64
+// intermediate): the per-channel factor of the inference-mode batch norm.
+template <typename T>
+__global__ void bn_inv_std_kernel(const T* __restrict__ var, int c, double eps, T* __restrict__ inv_std)
+{
+    pdl_prologue();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < c) inv_std[i] = (T)(1.0 / sqrt((double)var[i] + eps));
+}
+
+// Register-resident chains of dependent fused multiply-adds: 8 independent chains per thread, `iters` rounds.
+// Measures the FMA issue rate of the device for the roofline denominator of the FMA engine (no memory traffic).
+template <typename T>
+__global__ void __launch_bounds__(256) fma_probe_kernel(int iters, T seed, T* __restrict__ sink)
+{
+    pdl_prologue();
+    T a[8];
+#pragma unroll
+    for (int k = 0; k < 8; k++) a[k] = seed + (T)(threadIdx.x + k);
+    const T m = (T)0.999, b = (T)1e-3;
+    for (int i = 0; i < iters; i++) {
+#pragma unroll
+        for (int k = 0; k < 8; k++) a[k] = a[k] * m + b;
+    }
+    T s = a[0];
+#pragma unroll
+    for (int k = 1; k < 8; k++) s += a[k];
+    if (s == (T)-1) sink[blockIdx.x * blockDim.x + threadIdx.x] = s;     // never true: keeps the chains alive
+}
+
 }  // namespace b2c
 
 // ================================= C ABI ==========================================================
@@ -958,6 +1045,37 @@ extern "C" int b2c_bn_train_forward_static(int dtype, int layout, int n, int c, 
     return bn_train_forward_t<double>(layout, n, c, hw, (const double*)x, (const double*)gamma, (const double*)beta, (double*)running_mean,
                                       (double*)running_var, momentum, eps, fuse_relu, (double*)y, (double*)save_mean, (double*)save_inv_std,
                                       scratch, scratch_bytes, st);
+}
+
+extern "C" int b2c_bn_train_forward_prestats(int n, int c, int hw, const void* x, const void* stats, size_t stats_bytes,
+                                             const void* gamma, const void* beta, void* running_mean, void* running_var,
+                                             double momentum, double eps, int fuse_relu, const void* addend, void* y,
+                                             void* save_mean, void* save_inv_std, void* scratch, size_t scratch_bytes, void* stream)
+{
+    if (!x || !stats || !gamma || !beta || !running_mean || !running_var || !y || !save_mean || !save_inv_std || !scratch) return B2C_ERR_NULL_POINTER;
+    if (n <= 0 || c <= 0 || hw <= 0) return B2C_ERR_BAD_GEOMETRY;
+    if (!v4_ok(B2C_F32, B2C_LAYOUT_NHWC, c, x, y, addend ? addend : x)) return B2C_ERR_UNSUPPORTED;
+    const int64_t rows64 = ((int64_t)n * hw + 31) / 32;
+    if (stats_bytes < (size_t)rows64 * 2 * c * sizeof(float)) return B2C_ERR_WORKSPACE_TOO_SMALL;
+    if (scratch_bytes < reduce2_bytes(c)) return B2C_ERR_WORKSPACE_TOO_SMALL;
+    const int rows = (int)rows64;
+    cudaStream_t st = (cudaStream_t)stream;
+    // chunks: at least 32 rows of sums each, about two blocks per SM, no more than the scratch holds
+    const int gx = (c + 31) / 32;
+    int chunks = (296 + gx - 1) / gx;
+    if (chunks > rows / 32) chunks = rows / 32;
+    const int max_chunks = (int)(scratch_bytes / ((size_t)2 * c * sizeof(double)));
+    if (chunks > max_chunks) chunks = max_chunks;
+    if (chunks < 1) chunks = 1;
+    launch_pdl(bn_conv_sums_kernel, dim3(gx, chunks), dim3(32, 8), 0, st, (const float*)stats, rows, c, (double*)scratch);
+    int rc = check_launch("bn_conv_sums"); if (rc) return rc;
+    rc = final_warp((const double*)scratch, chunks, c, 0, (double)n * hw, momentum, eps, (float*)save_mean, (float*)save_inv_std,
+                    (float*)running_mean, (float*)running_var, st);
+    if (rc) return rc;
+    V4Geo ga = v4_apply_geo((int64_t)n * hw, c);
+    launch_pdl(bn_apply_v4_kernel, dim3(ga.gx, ga.chunks), 256, 0, st, (const float4*)x, (float4*)y, (const float*)save_mean, (const float*)save_inv_std,
+                                                              (const float*)gamma, (const float*)beta, ga, fuse_relu, (const float4*)addend);
+    return check_launch("bn_apply_v4");
 }
 
 extern "C" int b2c_bn_train_backward(int dtype, int layout, int n, int c, int hw, const void* x, const void* dy,
@@ -1182,6 +1300,40 @@ extern "C" int b2c_cce_forward_backward(int dtype, int rows, int cols, const voi
     if (dtype == B2C_F32) launch_pdl(cce_kernel<float>, rows, 256, 0, st, (const float*)probs, labels, cols, global_batch, (float)eps, (float*)row_loss, hit, (float*)dx);
     else launch_pdl(cce_kernel<double>, rows, 256, 0, st, (const double*)probs, labels, cols, global_batch, eps, (double*)row_loss, hit, (double*)dx);
     return check_launch("cce");
+}
+
+extern "C" int b2c_cce_totals(int dtype, int rows, const void* row_loss, const int32_t* hit, double* out2, void* stream)
+{
+    CHECK_DTYPE(dtype);
+    if (!row_loss || !out2) return B2C_ERR_NULL_POINTER;
+    if (rows <= 0) return B2C_ERR_BAD_GEOMETRY;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == B2C_F32) launch_pdl(cce_totals_kernel<float>, 1, 256, 0, st, (const float*)row_loss, hit, rows, out2);
+    else launch_pdl(cce_totals_kernel<double>, 1, 256, 0, st, (const double*)row_loss, hit, rows, out2);
+    return check_launch("cce_totals");
+}
+
+extern "C" int b2c_bn_inv_std(int dtype, int c, const void* running_var, double eps, void* inv_std, void* stream)
+{
+    CHECK_DTYPE(dtype);
+    if (!running_var || !inv_std) return B2C_ERR_NULL_POINTER;
+    if (c <= 0) return B2C_ERR_BAD_GEOMETRY;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == B2C_F32) launch_pdl(bn_inv_std_kernel<float>, (c + 127) / 128, 128, 0, st, (const float*)running_var, c, eps, (float*)inv_std);
+    else launch_pdl(bn_inv_std_kernel<double>, (c + 127) / 128, 128, 0, st, (const double*)running_var, c, eps, (double*)inv_std);
+    return check_launch("bn_inv_std");
+}
+
+extern "C" int b2c_probe_fma(int dtype, int blocks, int iters, void* sink, double* flops, void* stream)
+{
+    CHECK_DTYPE(dtype);
+    if (!sink) return B2C_ERR_NULL_POINTER;
+    if (blocks <= 0 || iters <= 0) return B2C_ERR_BAD_GEOMETRY;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == B2C_F32) launch_pdl(fma_probe_kernel<float>, blocks, 256, 0, st, iters, 1.0f, (float*)sink);
+    else launch_pdl(fma_probe_kernel<double>, blocks, 256, 0, st, iters, 1.0, (double*)sink);
+    if (flops) *flops = 2.0 * 8.0 * 256.0 * (double)blocks * (double)iters;
+    return check_launch("fma_probe");
 }
 
 extern "C" int b2c_sgd_update(int dtype, int64_t count, void* w, const void* dw, void* velocity,

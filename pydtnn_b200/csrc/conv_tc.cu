@@ -34,6 +34,7 @@
 #include "b2c_common.cuh"
 #include <cuda.h>
 #include <stdlib.h>
+#include <mutex>
 
 namespace b2c {
 
@@ -222,6 +223,15 @@ __host__ __device__ constexpr uint32_t make_idesc_tf32(int M, int N, int a_mn_ma
 
 // Device status word shared by all tensor-core kernels (0 = fine).
 __device__ int g_tc_status = 0;
+
+// Hand-over flags of the balanced mode (4 per CTA).  They live in the library image, start as zeros and are returned
+// to zero by the warp that consumes them, so no launch has to clear them first.  A bank belongs to one stream
+// (kernels of one stream never overlap); a stream beyond the bank count gets its flags in the caller's workspace,
+// cleared before the launch.
+#define TC_SYNC_BANKS 8
+#define TC_SYNC_WORDS 4096
+#define TC_SYNC_FLAGS 4096
+static __device__ __align__(256) unsigned int g_tc_sync[TC_SYNC_BANKS * TC_SYNC_WORDS];
 
 enum { TC_ERR_FULL = 1, TC_ERR_XFORM = 2, TC_ERR_EMPTY = 3, TC_ERR_TFULL = 4, TC_ERR_TEMPTY = 5, TC_ERR_PARTIAL = 6, TC_ERR_SELFTEST = 7 };
 
@@ -421,6 +431,10 @@ struct TcParams {
     int* sk_flags;
     float* db_partial;         // WGRAD: per-(split, transform warp) channel sums of dy, [splits][4][N], or null
     int tma_store;             // output rows are dense [M][N] (or [split][M][N]): store tiles through the output tensor map
+    int sk_selfclean;          // balanced mode: the owner returns a consumed flag to zero (flags in the library's bank)
+    // FWD with batch statistics: for every block of 32 output rows, row (m / 32) of `stats` ([ceil(M/32)][2][N] floats)
+    // receives the per-channel sum and sum of squares of the stored values (rows past M left out).  Null: off.
+    float* stats;
 };
 
 // Per-channel epilogue steps of the forward pass, decided once on the host so the drain warps branch on
@@ -546,6 +560,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     // buffers keep running across tile boundaries: the producer prefetches the next tile while the
     // drain warps still store the previous one.
     using L = TcSmem<BN, STAGES, SLABS>;
+    // the four-slab variant serves tiles of at most TC_CHUNK k-blocks with dense outputs (see dispatch_fwd)
+    constexpr bool STREAM = MODE == TCM_FWD && !SK && SLABS == 4;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* full_bar = (uint64_t*)(smem + L::BAR_OFFSET);
@@ -855,6 +871,89 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             const int tile = w.tile;
             const int ni = tile % nt, rest = tile / nt, mi = rest % mt, z = rest / mt;
             const int m0 = mi * 128, n0 = ni * BN;
+            // One 32-row x 32-column slab of the tile on its way out (dense outputs): epilogue steps, staging in a
+            // 128B-swizzled slab (conflict-free float4 writes), TMA store (whole rows, asynchronous, rows >= M and
+            // columns >= N clipped; SLABS slabs per warp rotate so the warp never waits on HBM), and the slab's batch
+            // statistics when asked for.
+            uint8_t* ebuf = smem + L::EPI_OFFSET + (warp - 6) * (SLABS * 4096);
+            float st0[BN / 32], st1[BN / 32];                           // batch statistics of the tile's slabs
+            auto emit_slab = [&](float* a, int cc) {
+                uint8_t* buf = ebuf + (ecount % SLABS) * 4096;
+                if (MODE == TCM_FWD && p.epi) tc_epilogue_math(p, n0 + cc * 32, a);
+                if (lane == 0) tma_store_wait_read<SLABS - 1>();     // the store that last read this slab is done
+                __syncwarp();
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                    *reinterpret_cast<float4*>(buf + lane * 128 + ((((j >> 2) ^ (lane & 7))) << 4)) = make_float4(a[j], a[j + 1], a[j + 2], a[j + 3]);
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) {
+                    if (MODE == TCM_FWD) tma_store_2d(&tmap_out, buf, n0 + cc * 32, m0 + quad * 32);
+                    else tma_store_3d(&tmap_out, buf, n0 + cc * 32, m0 + quad * 32, z);
+                    tma_store_commit();
+                }
+                if (MODE == TCM_FWD && p.stats) {
+                    // lane j sums column j of the slab (one shared-memory row per step, no bank conflicts) over the rows
+                    // that exist.  The sums wait in registers until the tile's last slab is on its way.
+                    // All 32 slab rows are read (they exist in shared memory whatever M is) in batches of eight
+                    // independent loads; rows past M count as zeros.
+                    const int valid = p.M - (m0 + quad * 32);
+                    float s0 = 0.f, s1 = 0.f;
+                    const uint32_t col = smem_u32(buf) + (lane & 3) * 4;
+#pragma unroll
+                    for (int r8 = 0; r8 < 32; r8 += 8) {
+                        float v[8];
+#pragma unroll
+                        for (int r = 0; r < 8; r++)
+                            asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v[r]) : "r"(col + (r8 + r) * 128 + ((((lane >> 2) ^ r)) << 4)));
+#pragma unroll
+                        for (int r = 0; r < 8; r++) {
+                            const float u = r8 + r < valid ? v[r] : 0.f;
+                            s0 += u; s1 = fmaf(u, u, s1);
+                        }
+                    }
+                    st0[cc] = s0; st1[cc] = s1;
+                }
+                ecount++;
+            };
+            auto store_stats = [&]() {
+                if (MODE == TCM_FWD && p.stats && m0 + quad * 32 < p.M) {
+                    // row (m / 32) of the statistics: the block's two rows of sums, 128 contiguous bytes per slab
+                    float* srow = p.stats + ((size_t)((m0 >> 5) + quad) * 2) * p.N + n0 + lane;
+#pragma unroll
+                    for (int cc = 0; cc < BN / 32; cc++)
+                        if (n0 + cc * 32 + lane < p.N) { __stcg(srow + cc * 32, st0[cc]); __stcg(srow + cc * 32 + p.N, st1[cc]); }
+                }
+            };
+            if constexpr (STREAM) {
+                // Short K loops: the tile is one chunk in tensor memory and the epilogue, not the tensor pipe, sets the
+                // pace.  The drain warp takes 32 columns at a time straight from tensor memory (the next 32 already in
+                // flight) and sends them out, so it never holds a whole row of the tile in registers.
+                const int b = gc & 1;
+                TC_PROF_T0();
+                ok = mbar_wait(&tfull_bar[b], (gc >> 1) & 1, abort_flag, &g_tc_status, TC_ERR_TFULL);
+                if (threadIdx.x == 192) TC_PROF_ADD(7);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t tsrc = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(b * BN);
+                float a[2][32];
+                tmem_ld_32x32_f(tsrc, a[0]);
+#pragma unroll
+                for (int cc = 0; cc < BN / 32; cc++) {
+                    tmem_ld_wait();
+                    if (cc + 1 < BN / 32) tmem_ld_32x32_f(tsrc + (uint32_t)((cc + 1) * 32), a[(cc + 1) & 1]);
+                    else {
+                        // every column of the buffer is in registers: the tensor core may have it back
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&tempty_bar[b]);
+                    }
+                    if (n0 + cc * 32 < p.N && m0 + quad * 32 < p.M) emit_slab(a[cc & 1], cc);
+                }
+                gc++;
+                store_stats();
+                continue;
+            }
             const int nchunks = (w.kb_e - w.kb_b + TC_CHUNK - 1) / TC_CHUNK;
             float acc[BN];
             for (int c = 0; c < nchunks && ok; c++, gc++) {
@@ -920,6 +1019,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         got = __shfl_sync(0xffffffffu, got, 0);
                         if (!got) { ok = false; break; }
                         __threadfence();
+                        // this warp is the flag's only reader: once seen, it goes back to zero for the next launch
+                        if (p.sk_selfclean && lane == 0) p.sk_flags[c2 * 4 + quad] = 0;
                         const float4* slot = reinterpret_cast<const float4*>(p.sk_partial + (size_t)c2 * (128 * BN)) + row;
 #pragma unroll
                         for (int j = 0; j < BN; j += 4) {
@@ -946,31 +1047,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 }
             }
             if (ok && p.tma_store) {
-                // Dense output: each warp stages its 32 rows x 32 columns in a 128B-swizzled slab (conflict-free
-                // float4 writes) and hands it to the TMA store engine, which writes whole rows asynchronously and
-                // clips rows >= M and columns >= N; two slabs per warp alternate so the warp never waits on HBM.
-                uint8_t* ebuf = smem + L::EPI_OFFSET + (warp - 6) * (SLABS * 4096);
 #pragma unroll
-                for (int cc = 0; cc < BN / 32; cc++) {
-                    if (n0 + cc * 32 < p.N && m0 + quad * 32 < p.M) {       // slabs wholly outside the output are skipped
-                        uint8_t* buf = ebuf + (ecount % SLABS) * 4096;
-                        if (MODE == TCM_FWD && p.epi) tc_epilogue_math(p, n0 + cc * 32, &acc[cc * 32]);
-                        if (lane == 0) tma_store_wait_read<SLABS - 1>();     // the store that last read this slab is done
-                        __syncwarp();
-#pragma unroll
-                        for (int j = 0; j < 32; j += 4)
-                            *reinterpret_cast<float4*>(buf + lane * 128 + ((((j >> 2) ^ (lane & 7))) << 4)) =
-                                make_float4(acc[cc * 32 + j], acc[cc * 32 + j + 1], acc[cc * 32 + j + 2], acc[cc * 32 + j + 3]);
-                        fence_proxy_async();
-                        __syncwarp();
-                        if (lane == 0) {
-                            if (MODE == TCM_FWD) tma_store_2d(&tmap_out, buf, n0 + cc * 32, m0 + quad * 32);
-                            else tma_store_3d(&tmap_out, buf, n0 + cc * 32, m0 + quad * 32, z);
-                            tma_store_commit();
-                        }
-                        ecount++;
-                    }
-                }
+                for (int cc = 0; cc < BN / 32; cc++)
+                    if (n0 + cc * 32 < p.N && m0 + quad * 32 < p.M) emit_slab(&acc[cc * 32], cc);     // slabs wholly outside the output are skipped
+                store_stats();
             } else if (ok) {
                 float* stage = (float*)(smem + L::EPI_OFFSET) + (warp - 6) * (SLABS * 4096 / 4);
 #pragma unroll
@@ -1131,16 +1211,64 @@ static bool tc_supported_nhwc(const Geo& g, int pass)
     return (g.ci % 32 == 0 || lowered_ok(g)) && g.co % 32 == 0;
 }
 
+// Function attributes and the SM count belong to a device, not to the process: both are kept per device ordinal
+// (the device current at the call), so a process that drives several GPUs sets each one up.
+#define B2C_MAX_DEVICES 64
+static int current_device()
+{
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= B2C_MAX_DEVICES) dev = 0;
+    return dev;
+}
+struct PerDeviceOnce {
+    std::mutex m;
+    bool done[B2C_MAX_DEVICES] = {};
+    // Runs fn() the first time it is called with a given device current; returns fn's error (and retries next time).
+    template <typename Fn> cudaError_t run(Fn fn) {
+        const int dev = current_device();
+        std::lock_guard<std::mutex> lock(m);
+        if (done[dev]) return cudaSuccess;
+        cudaError_t e = fn();
+        if (e == cudaSuccess) done[dev] = true;
+        return e;
+    }
+};
+
 static int tc_sm_count()
 {
-    static int sm_count = 0;
-    if (!sm_count) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
+    static int sm_count[B2C_MAX_DEVICES] = {};
+    static std::mutex m;
+    const int dev = current_device();
+    std::lock_guard<std::mutex> lock(m);
+    if (!sm_count[dev]) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        sm_count[dev] = n;
     }
-    return sm_count;
+    return sm_count[dev];
 }
+// The bank of synchronisation words of `st` on the current device, or null when all banks belong to other streams.
+// In host code g_tc_sync is only a handle for the runtime: the device address is looked up once per device.
+static unsigned int* tc_sync_bank(cudaStream_t st)
+{
+    static std::mutex m;
+    static unsigned int* base[B2C_MAX_DEVICES] = {};
+    static cudaStream_t owner[B2C_MAX_DEVICES][TC_SYNC_BANKS];
+    static int owners[B2C_MAX_DEVICES] = {};
+    const int dev = current_device();
+    std::lock_guard<std::mutex> lock(m);
+    if (!base[dev]) {
+        void* ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_tc_sync) != cudaSuccess || !ptr) { cudaGetLastError(); return nullptr; }
+        base[dev] = (unsigned int*)ptr;
+    }
+    for (int i = 0; i < owners[dev]; i++)
+        if (owner[dev][i] == st) return base[dev] + (size_t)i * TC_SYNC_WORDS;
+    if (owners[dev] == TC_SYNC_BANKS) return nullptr;
+    owner[dev][owners[dev]] = st;
+    return base[dev] + (size_t)(owners[dev]++) * TC_SYNC_WORDS;
+}
+
 // Balanced mode scratch: 4 flags per CTA (padded to 4 KB) and one 128 x 128 float partial tile per CTA.
 static size_t sk_flag_bytes() { return align_up((size_t)tc_sm_count() * 4 * sizeof(int), 4096); }
 static size_t sk_bytes() { return sk_flag_bytes() + (size_t)tc_sm_count() * 128 * 128 * sizeof(float); }
@@ -1166,12 +1294,13 @@ static WgradPlan wgrad_plan(const Geo& g)
     const int64_t blocks = (g.M + 31) / 32;
     const double reduce_per_split = (double)Krows * g.co * 4.0 / 5e12 / 0.6e-6;   // k-block units (0.6 us each)
     double best = 0.0;
+    const int64_t G = tc_sm_count();
     pl.splits = 1; pl.kblocks = (int)blocks;
     for (int64_t s = 1; s <= 512 && s <= blocks; s++) {
         const int64_t kb = (blocks + s - 1) / s;
         if ((blocks + kb - 1) / kb != s) continue;       // same k-blocks per split as a smaller count
         if (kb < 4 && s > 1) break;
-        const int64_t rounds = (tiles * s + 147) / 148;
+        const int64_t rounds = (tiles * s + G - 1) / G;
         const double cost = (double)rounds * (double)(kb + 6) + (double)s * reduce_per_split;
         if (s == 1 || cost < best) { best = cost; pl.splits = (int)s; pl.kblocks = (int)kb; }
     }
@@ -1194,11 +1323,10 @@ template <int MODE, int BN, int STAGES, bool SK, int SLABS, int BSRC>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb0, const CUtensorMap& mb1, const CUtensorMap& mo, const TcParams& p, int splits, cudaStream_t st)
 {
     using L = TcSmem<BN, STAGES, SLABS>;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(conv_tc_kernel<MODE, BN, STAGES, SK, SLABS, BSRC>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    static PerDeviceOnce attr;
+    {
+        cudaError_t e = attr.run([] { return cudaFuncSetAttribute(conv_tc_kernel<MODE, BN, STAGES, SK, SLABS, BSRC>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL); });
         if (e != cudaSuccess) { set_cuda_error(e, "cudaFuncSetAttribute(conv_tc_kernel)"); return B2C_ERR_CUDA; }
-        attr_set = true;
     }
     const int sm_count = tc_sm_count();
     int64_t tiles = (int64_t)((p.M + 127) / 128) * ((p.N + BN - 1) / BN) * splits;
@@ -1275,6 +1403,9 @@ static bool make_map_out(CUtensorMap* map, const void* base, uint64_t planes, ui
 // fprop-shaped launch: `act` (n, ah, aw, C) gathered through a window whose first position is
 // (low_h, low_w), with cnt_h x cnt_w positions per image and traversal stride (str_h, str_w); virtual
 // filter kh x kw (dilation dil); output rows (n, i, j) over P x Q written at out + n*o_sn + i*o_sh + j*o_sw.
+// Where a forward pass leaves the batch statistics of its output (see TcParams::stats), or null.
+struct StatsOut { float* sums; };
+
 struct FwdLaunch {
     int n, ah, aw, C, P, Q, N, kh, kw, low_h, low_w, cnt_h, cnt_w, str_h, str_w, dil_h, dil_w;
     int64_t o_sn, o_sh, o_sw;
@@ -1282,7 +1413,7 @@ struct FwdLaunch {
 
 static int run_fwd(const FwdLaunch& f, const void* act, const void* w, const PrepParams& pp, const void* bias,
                    const b2c_bn_params* bn, int relu, float* out, void* ws, size_t ws_bytes, cudaStream_t st,
-                   bool filters_ready = false)
+                   bool filters_ready = false, const StatsOut* stats = nullptr)
 {
     if (!load_driver_entry_points()) return B2C_ERR_UNSUPPORTED;
     const int64_t K = (int64_t)f.kh * f.kw * f.C;
@@ -1296,6 +1427,10 @@ static int run_fwd(const FwdLaunch& f, const void* act, const void* w, const Pre
     // Balanced mode when whole tiles would leave a large part of the last round of the CTA grid idle.
     int sk = 0;
     int* sk_flags = (int*)(base + 2 * fbytes);
+    float* sk_partial = (float*)((uintptr_t)sk_flags + sk_flag_bytes());
+    // hand-over flags: in the library's self-cleaning bank when this stream has one, else cleared in the workspace
+    unsigned int* sk_bank = tc_sm_count() * 4 <= TC_SYNC_FLAGS ? tc_sync_bank(st) : nullptr;
+    if (sk_bank) sk_flags = (int*)sk_bank;
     {
         const int G = tc_sm_count();
         const int64_t tiles = (((int64_t)f.n * f.P * f.Q + 127) / 128) * ((f.N + BN - 1) / BN);
@@ -1326,11 +1461,11 @@ static int run_fwd(const FwdLaunch& f, const void* act, const void* w, const Pre
     }
     if (!filters_ready && bsrc == TCB_SPLIT) {
         int64_t total = (int64_t)f.N * K;
-        int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
-        launch_pdl(tc_prep_filter_kernel, blocks, 256, 0, st, pp, (const float*)w, w_hi, w_lo, sk_flags, sk ? tc_sm_count() * 4 : 0);
+        int blocks = (int)((total + 255) / 256 < tc_sm_count() * 8 ? (total + 255) / 256 : tc_sm_count() * 8);
+        launch_pdl(tc_prep_filter_kernel, blocks, 256, 0, st, pp, (const float*)w, w_hi, w_lo, sk_flags, sk && !sk_bank ? tc_sm_count() * 4 : 0);
         int rc = check_launch("tc_prep_filter_kernel");
         if (rc) return rc;
-    } else if (sk) {
+    } else if (sk && !sk_bank) {
         cudaError_t e = cudaMemsetAsync(sk_flags, 0, (size_t)tc_sm_count() * 4 * sizeof(int), st);
         if (e != cudaSuccess) { set_cuda_error(e, "cudaMemsetAsync(balanced-mode flags)"); return B2C_ERR_CUDA; }
     }
@@ -1348,12 +1483,17 @@ static int run_fwd(const FwdLaunch& f, const void* act, const void* w, const Pre
         p.epi |= TC_EPI_VEC;
     p.out = out; p.o_sn = f.o_sn; p.o_sh = f.o_sh; p.o_sw = f.o_sw;
     p.tap_r0 = pp.r0; p.tap_rstep = pp.rstep; p.tap_s0 = pp.s0; p.tap_sstep = pp.sstep; p.tap_sreal = pp.Sreal;
-    p.sk = sk; p.sk_flags = sk_flags; p.sk_partial = (float*)((uintptr_t)sk_flags + sk_flag_bytes());
+    p.sk = sk; p.sk_flags = sk_flags; p.sk_partial = sk_partial; p.sk_selfclean = sk_bank ? 1 : 0;
     // dense rows (plain fprop / stride-1 dgrad): rows are N floats apart in (n, i, j) order
     const bool dense = f.o_sw == f.N && f.o_sh == (int64_t)f.Q * f.N && f.o_sn == (int64_t)f.P * f.Q * f.N;
     CUtensorMap mo = mbh;
     p.tma_store = 0;
     if (dense && make_map_out(&mo, out, 0, (uint64_t)p.M, (uint64_t)f.N)) p.tma_store = 1;
+    if (stats) {
+        // the statistics are taken from the staging slabs of the TMA-store epilogue
+        if (!p.tma_store) return B2C_ERR_UNSUPPORTED;
+        p.stats = stats->sums;
+    }
     if (bsrc == TCB_RAW_K) return dispatch_fwd<TCB_RAW_K>(BN, ma, mbh, mbl, mo, p, st);
     if (bsrc == TCB_RAW_MN) return dispatch_fwd<TCB_RAW_MN>(BN, ma, mbh, mbl, mo, p, st);
     return dispatch_fwd<TCB_SPLIT>(BN, ma, mbh, mbl, mo, p, st);
@@ -1371,11 +1511,9 @@ static int launch_lower(const Geo& g, const void* x, float* rows, cudaStream_t s
     const int wp = (g.wo - 1) * g.hstr + (g.kw - 1) * g.hdil + 1;
     const size_t patch_bytes = (size_t)g.kh * wp * g.ci * sizeof(float);
     if (kq <= 256 && patch_bytes <= 200 * 1024 && (int64_t)g.n * g.ho < 0x7fffffffLL) {
-        static bool attr_set = false;
-        if (!attr_set) {
-            cudaFuncSetAttribute(tc_lower_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-            attr_set = true;
-        }
+        static PerDeviceOnce attr;
+        cudaError_t e = attr.run([] { return cudaFuncSetAttribute(tc_lower_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); });
+        if (e != cudaSuccess) { set_cuda_error(e, "cudaFuncSetAttribute(tc_lower_rows_kernel)"); return B2C_ERR_CUDA; }
         const int threads = 256 / kq * kq < 64 ? kq : 256 / kq * kq;       // a whole number of column-group sets
         launch_pdl(tc_lower_rows_kernel, (unsigned)(g.n * g.ho), threads, patch_bytes, st, lp, (const float*)x, (float4*)rows, wp);
         return check_launch("tc_lower_rows_kernel");
@@ -1385,14 +1523,14 @@ static int launch_lower(const Geo& g, const void* x, float* rows, cudaStream_t s
     int a = kq, b = 256;
     while (b) { int t = a % b; a = b; b = t; }
     const int unit = kq / a;
-    int64_t blocks = (total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16;
+    int64_t blocks = (total + 255) / 256 < tc_sm_count() * 16 ? (total + 255) / 256 : tc_sm_count() * 16;
     blocks = (blocks + unit - 1) / unit * unit;
     launch_pdl(tc_lower_kernel, (unsigned)blocks, 256, 0, st, lp, (const float*)x, (float4*)rows);
     return check_launch("tc_lower_kernel");
 }
 
 static int tc_fprop_nhwc(const Geo& g, const void* x, const void* w, const void* bias, const b2c_bn_params* bn, int relu,
-             void* y, void* ws, size_t ws_bytes, cudaStream_t st)
+             void* y, void* ws, size_t ws_bytes, cudaStream_t st, const StatsOut* stats = nullptr)
 {
     WStride wsd = w_stride(g.w_layout, g.ci, g.co, g.kh, g.kw);
     if (g.ci % 32 != 0) {
@@ -1415,13 +1553,13 @@ static int tc_fprop_nhwc(const Geo& g, const void* x, const void* w, const void*
         PrepParams none{};
         FwdLaunch f{g.n, g.ho, g.wo, Kp, g.ho, g.wo, g.co, 1, 1, 0, 0, g.ho, g.wo, 1, 1, 1, 1,
                     (int64_t)g.ho * g.wo * g.co, (int64_t)g.wo * g.co, (int64_t)g.co};
-        return run_fwd(f, rows, nullptr, none, bias, bn, relu, (float*)y, (void*)w_hi, 2 * fbytes + 1024, st, true);
+        return run_fwd(f, rows, nullptr, none, bias, bn, relu, (float*)y, (void*)w_hi, 2 * fbytes + 1024, st, true, stats);
     }
     PrepParams pp{g.co, g.ci, g.kh, g.kw, wsd.sk, wsd.sc, wsd.sr, wsd.ss, 0, 1, 0, 1, g.kh, g.kw};
     FwdLaunch f{g.n, g.h, g.w, g.ci, g.ho, g.wo, g.co, g.kh, g.kw, -g.vpad, -g.hpad,
                 g.h + 2 * g.vpad - (g.kh - 1) * g.vdil, g.w + 2 * g.hpad - (g.kw - 1) * g.hdil,
                 g.vstr, g.hstr, g.vdil, g.hdil, (int64_t)g.ho * g.wo * g.co, (int64_t)g.wo * g.co, (int64_t)g.co};
-    return run_fwd(f, x, w, pp, bias, bn, relu, (float*)y, ws, ws_bytes, st);
+    return run_fwd(f, x, w, pp, bias, bn, relu, (float*)y, ws, ws_bytes, st, false, stats);
 }
 
 static int tc_dgrad_nhwc(const Geo& g, const void* dy, const void* w, void* dx, void* ws, size_t ws_bytes, cudaStream_t st)
@@ -1501,12 +1639,12 @@ static int tc_wgrad_nhwc(const Geo& g, const void* x, const void* dy, void* dw, 
     p.db_partial = db ? (float*)(base + lbytes + pbytes) : nullptr;
     CUtensorMap mo = mb;
     p.tma_store = make_map_out(&mo, partial, (uint64_t)pl.splits, (uint64_t)Krows, (uint64_t)g.co) ? 1 : 0;
+    WStride wsd = w_stride(g.w_layout, g.ci, g.co, g.kh, g.kw);
     int rc = dispatch_wgrad(pl.bn, ma, mb, mo, p, pl.splits, st);
     if (rc) return rc;
-    WStride wsd = w_stride(g.w_layout, g.ci, g.co, g.kh, g.kw);
     WgradReduceParams rp{Krows, g.co, g.ci, g.kw, pl.splits, wsd.sk, wsd.sc, wsd.sr, wsd.ss, (int)g.K};
     int64_t total = (int64_t)Krows * g.co;
-    int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+    int blocks = (int)((total + 255) / 256 < tc_sm_count() * 8 ? (total + 255) / 256 : tc_sm_count() * 8);
     launch_pdl(tc_wgrad_reduce_kernel, blocks, 256, 0, st, rp, partial, (float*)dw, p.db_partial, (float*)db);
     return check_launch("tc_wgrad_reduce_kernel");
 }
@@ -1617,6 +1755,25 @@ static bool nchw_ws(const Geo& g, void* ws, size_t ws_bytes, NchwWs& o)
     return true;
 }
 
+// Forward pass that also leaves the per-channel sums of its output for a training-mode batch norm (NHWC float32 on this
+// engine only).  Buffer: [ceil(M / 32)][2][co] floats.
+size_t tc_stats_bytes(const Geo& g)
+{
+    if (g.layout != B2C_LAYOUT_NHWC || !tc_supported_nhwc(g, B2C_PASS_FPROP) || g.co % 4) return 0;
+    return (size_t)((g.M + 31) / 32) * 2 * g.co * sizeof(float);
+}
+
+int tc_fprop_stats(const Geo& g, const void* x, const void* w, const void* bias, void* y, void* stats, size_t stats_bytes,
+                   void* ws, size_t ws_bytes, cudaStream_t st)
+{
+    const size_t need = tc_stats_bytes(g);
+    if (!need) return B2C_ERR_UNSUPPORTED;
+    if (stats_bytes < need) return B2C_ERR_WORKSPACE_TOO_SMALL;
+    if ((uintptr_t)stats & 15) return B2C_ERR_MISALIGNED;
+    StatsOut so{(float*)stats};
+    return tc_fprop_nhwc(g, x, w, bias, nullptr, 0, y, ws, ws_bytes, st, &so);
+}
+
 int tc_fprop(const Geo& g, const void* x, const void* w, const void* bias, const b2c_bn_params* bn, int relu,
              void* y, void* ws, size_t ws_bytes, cudaStream_t st)
 {
@@ -1689,7 +1846,13 @@ int tc_read_status(int* out)
     int v = 0;
     cudaError_t e = cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int));
     if (e != cudaSuccess) { set_cuda_error(e, "cudaMemcpyFromSymbol(g_tc_status)"); return B2C_ERR_CUDA; }
-    if (v != 0) { int zero = 0; cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(int)); }
+    if (v != 0) {
+        // a kernel that gave up may have left hand-over flags behind: return every bank to zeros
+        int zero = 0;
+        cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(int));
+        void* sync = nullptr;
+        if (cudaGetSymbolAddress(&sync, g_tc_sync) == cudaSuccess && sync) cudaMemset(sync, 0, sizeof(unsigned int) * TC_SYNC_BANKS * TC_SYNC_WORDS);
+    }
     *out = v;
     return B2C_OK;
 }

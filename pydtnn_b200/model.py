@@ -15,6 +15,7 @@ import torch
 
 from . import _lib, tracer
 from .arena import ParamArena
+from .backends.gpu import memory_allocation as wsp
 from .comm import GradientBucketer
 from .layers import (BatchNormalization, Conv2D, Conv2DBatchNormalization, Conv2DBatchNormalizationRelu, Conv2DRelu,
                      Relu)
@@ -22,6 +23,15 @@ from .losses import CategoricalCrossEntropy
 from .tensor_gpu import empty
 from .utils import (EVALUATE_MODE, PYDTNN_TENSOR_FORMAT_NCHW, PYDTNN_TENSOR_FORMAT_NHWC, TRAIN_MODE,
                     UNSPECIFIED_MODE, np_dtype)
+
+
+def _bn_fast_path(c):
+    """Channel counts the float4 batch-norm kernels take (the ones that accept sums from the convolution)."""
+    if c % 4 or c > 2048:
+        return False
+    c4 = c // 4
+    cx = min(c4, 64)
+    return 256 % cx == 0 and c4 % cx == 0
 
 
 class Model:
@@ -70,6 +80,7 @@ class Model:
         self._eval_layers = None
         self.fast_update = True
         self.fuse_add_relu = True
+        self.fuse_conv_bn_stats = True      # training: a Conv2D that feeds a BatchNormalization also sums its output per channel
         if model_name:
             from . import nets
             getattr(nets, f"create_{model_name}")(self)
@@ -109,6 +120,13 @@ class Model:
             for a, b in zip(seq, seq[1:]):
                 if self.enable_fused_bn_relu and isinstance(a, BatchNormalization) and isinstance(b, Relu):
                     a.fuse_relu, b.absorbed = True, True
+                # Conv2D followed by BatchNormalization (training): the convolution's epilogue takes the batch sums, the
+                # batch norm skips its own statistics pass over the tensor
+                if self.fuse_conv_bn_stats and type(a).__name__ == "Conv2DGPU" and type(b).__name__ == "BatchNormalizationGPU" \
+                        and getattr(a, "stats_bytes", 0) and b.spatial and self.dtype == np.float32 \
+                        and self.tensor_format == PYDTNN_TENSOR_FORMAT_NHWC and _bn_fast_path(b.ci):
+                    a.stats_for_bn = b
+                    wsp.require_conv_stats(a.stats_bytes)
                 # an addition block followed by a ReLU: the last residual sum writes max(sum, 0)
                 # straight into the ReLU's output (same arithmetic, one pass over memory fewer)
                 if self.fuse_add_relu and a.is_block_layer and len(a.paths) > 1 and isinstance(b, Relu) \
@@ -124,6 +142,8 @@ class Model:
                     walk(p)
         walk(self.layers)
         self._train_fused = True
+        # an evaluation list built before these flags were set holds block copies without them
+        self._eval_layers = None
 
     def _fuse_inference(self, seq):
         """Conv2D [+ BatchNormalization] [+ Relu] -> one convolution with a fused epilogue
@@ -280,6 +300,7 @@ class Model:
         of the following call's input under this call's kernels, as in ``train_batch``."""
         self.mode = EVALUATE_MODE
         if self._eval_layers is None:
+            self._fuse_training()          # the flags it sets (absorbed ReLUs, folded sums) are read in evaluation too
             self._eval_layers = self._fuse_inference(self.layers)
         if x_batch is not None:
             xin = self.layers[0].y.ary
@@ -315,4 +336,7 @@ class Model:
         return missing
 
     def synchronize(self):
+        """Wait for the device and raise ``B2CError`` (device timeout) if a bounded in-kernel wait ran out since the
+        last check: the kernel then returned with partial results, which must not be trained on silently."""
         torch.cuda.synchronize(self.device)
+        _lib.check(_lib.lib().b2c_check_device_status(None))

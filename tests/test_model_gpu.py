@@ -234,6 +234,64 @@ def test_alexnet_style_inference_with_fused_conv_relu(layout):
     assert _rel_l2(y.ary.get(), ref) <= 1e-5
 
 
+def test_evaluate_train_evaluate_matches_a_fresh_model():
+    """Evaluation before the first training step builds the fused evaluation list early; the training fusion pass
+    then changes flags on blocks and ReLUs that list shares.  Evaluating again must give what a model that only
+    trained and then evaluated gives, bit for bit."""
+    from pydtnn_b200.optimizers import SGD
+    kw = dict(enable_fused_bn_relu=True, enable_fused_conv_bn=True, enable_fused_conv_bn_relu=True)
+    a = _small_resnet("NHWC", np.float32, **kw)
+    b = _small_resnet("NHWC", np.float32, **kw)
+    oa, ob = SGD(0.0, 0.0), SGD(0.0, 0.0)       # lr 0: only the running statistics change
+    net = cpu_twin(b)
+    x, labels = _batch(a, 0)
+    x2, _ = _batch(a, 1)
+    a.evaluate_batch(x2)                        # builds a's evaluation list before any training
+    a.train_batch(x, labels, oa)
+    b.train_batch(x, labels, ob)
+    net.forward(x, True)
+    ya = a.evaluate_batch(x2).ary.get()
+    yb = b.evaluate_batch(x2).ary.get()
+    a.synchronize()
+    assert np.array_equal(ya, yb)
+    # and against the un-fused CPU chain
+    _NOISE["f32"] = True
+    assert rel_l2(yb, net.forward(x2, False)) <= 2e-4
+
+
+@pytest.mark.parametrize("flags", [dict(enable_fused_bn_relu=True, enable_fused_conv_bn=True),
+                                   dict(enable_fused_bn_relu=True, enable_fused_conv_bn=True, enable_fused_conv_relu=True),
+                                   dict(enable_fused_bn_relu=True)])
+def test_inference_after_training_fusion_keeps_every_relu(flags):
+    """Training-mode BN+ReLU fusion marks the ReLU as absorbed by its batch norm; an inference pass that folds
+    Conv+BN (without the +ReLU variant switched on) must still apply that ReLU."""
+    from pydtnn_b200.optimizers import SGD
+    model = _small_resnet("NHWC", np.float32, **flags)
+    opt = SGD(learning_rate=0.0, momentum=0.0)
+    x, labels = _batch(model, 3)
+    model.train_batch(x, labels, opt)          # lr 0: only the running statistics change
+    net = cpu_twin(model)
+    net.forward(x, True)                       # moves the twin's running statistics the same way
+    y = model.evaluate_batch(x)
+    model.synchronize()
+    _NOISE["f32"] = True
+    assert rel_l2(y.ary.get(), net.forward(x, False)) <= 2e-4
+
+
+def test_loss_and_accuracy_totals_match_the_row_values():
+    """``loss()`` / ``accuracy()`` read two doubles summed on the device; they must equal the host-side sums of
+    the per-row values the same kernel wrote."""
+    from pydtnn_b200.optimizers import SGD
+    m = _small_resnet("NHWC", np.float32)
+    x, labels = _batch(m, 0)
+    lo = m.train_batch(x, labels, SGD(0.05, 0.9))
+    rows = lo.row_loss.get().astype(np.float64)
+    hits = lo.hit.get()
+    assert abs(lo.loss() - (-rows.sum() / m.batch_size)) <= 1e-12
+    assert abs(lo.accuracy() - hits.sum() * 100.0 / m.batch_size) <= 1e-12
+    assert lo.local_loss() == -rows.sum() / m.batch_size
+
+
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     from pydtnn_b200 import _lib
     monkeypatch.setattr(_lib, "_lib", None)

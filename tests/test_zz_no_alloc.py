@@ -45,7 +45,9 @@ def _run(fn_static, x, gamma, beta, layout, relu, dtype):
 
 
 @pytest.mark.parametrize("layout,dtype,shape", [("NHWC", "float32", (8, 28, 28, 128)), ("NHWC", "float32", (4, 7, 7, 2048)),
-                                                ("NCHW", "float32", (4, 24, 9, 9)), ("NHWC", "float64", (4, 6, 6, 20))])
+                                                ("NCHW", "float32", (4, 24, 9, 9)), ("NHWC", "float64", (4, 6, 6, 20)),
+                                                # 2048 channels on the generic reduction: 64 chunks x 2 x 2048 doubles, the whole array
+                                                ("NCHW", "float32", (2, 2048, 8, 8)), ("NHWC", "float64", (2, 8, 8, 2048))])
 def test_static_scratch_entry_point_matches_regular_one_twice(layout, dtype, shape):
     rng = np.random.Generator(np.random.PCG64(21))
     c = shape[3] if layout == "NHWC" else shape[1]
@@ -56,6 +58,48 @@ def test_static_scratch_entry_point_matches_regular_one_twice(layout, dtype, sha
         got = _run(True, x, gamma, beta, layout, relu=bool(call), dtype=dtype)
         for name, g, w in zip(("y", "save_mean", "save_inv_std", "running_mean", "running_var"), got, want):
             assert_parity(g, w, dtype, f"call {call} {name}")
+
+
+def test_static_scratch_entry_point_against_the_cpu_oracle():
+    """One direct comparison with the CPU restatement of the reference's batch norm (not only with the regular
+    entry point): y, the running averages and the saved mean."""
+    from oracle import aux_oracle as ao
+    rng = np.random.Generator(np.random.PCG64(5))
+    shape, c = (8, 14, 14, 64), 64
+    x = rng.standard_normal(shape).astype(np.float32) * 2.0 + 0.3
+    gamma, beta = rng.standard_normal(c).astype(np.float32), rng.standard_normal(c).astype(np.float32)
+    y, sm, si, rm, rv = _run(True, x, gamma, beta, "NHWC", relu=False, dtype="float32")
+    y_ref, (std, _), rm_ref, rv_ref = ao.bn_train_forward(x.astype(np.float64), gamma.astype(np.float64), beta.astype(np.float64),
+                                                          np.full(c, 0.25), np.full(c, 0.75), 0.9, 1e-5, "NHWC")
+    assert_parity(y, y_ref, np.float32, "y")
+    assert_parity(rm, rm_ref, np.float32, "running_mean")
+    assert_parity(rv, rv_ref, np.float32, "running_var")
+    assert_parity(si, 1.0 / std, np.float32, "save_inv_std")
+    assert_parity(sm, x.astype(np.float64).reshape(-1, c).mean(axis=0), np.float32, "save_mean")
+
+
+def test_static_scratch_entry_point_allocates_nothing():
+    """The property the entry point exists for: with every tensor in place and the first call done, further calls
+    leave the device's free memory exactly where it was (cudaMemGetInfo before and after)."""
+    L = _lib.lib()
+    n, h, w, c = 8, 28, 28, 256
+    x = torch.randn((n, h, w, c), device=DEV)
+    y = torch.empty_like(x)
+    gamma, beta = torch.ones(c, device=DEV), torch.zeros(c, device=DEV)
+    rm, rv, sm, si = (torch.zeros(c, device=DEV) for _ in range(4))
+
+    def call():
+        _lib.check(L.b2c_bn_train_forward_static(_lib.F32, _lib.LAYOUT_NHWC, n, c, h * w, x.data_ptr(), gamma.data_ptr(),
+                                                 beta.data_ptr(), rm.data_ptr(), rv.data_ptr(), 0.9, 1e-5, 1, y.data_ptr(),
+                                                 sm.data_ptr(), si.data_ptr(), stream()))
+    call()                                      # first call on the device: looks up the array's address
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    for _ in range(5):
+        call()
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0, (free0, free1)
 
 
 def test_static_scratch_entry_point_rejects_sizes_beyond_its_array():
