@@ -432,6 +432,14 @@ struct TcParams {
     float* db_partial;         // WGRAD: per-(split, transform warp) channel sums of dy, [splits][4][N], or null
     int tma_store;             // output rows are dense [M][N] (or [split][M][N]): store tiles through the output tensor map
     int sk_selfclean;          // balanced mode: the owner returns a consumed flag to zero (flags in the library's bank)
+    // FWD over several pixel classes in one launch (the parity classes of a strided data gradient): the tile list is
+    // the concatenation of the classes' tile lists, class c owning tiles [cls_tile0[c], cls_tile0[c + 1]).  A class has
+    // its own pixel grid, window corner, tap set, k-block count, output offset and activation tensor map; channel
+    // counts, filter and output strides are the launch's.  Used by the MULTI variants only.
+    int ncls;
+    int cls_tile0[5];
+    int cls_M[4], cls_P[4], cls_Q[4], cls_kblocks[4], cls_S[4], cls_low_h[4], cls_low_w[4], cls_r0[4], cls_s0[4];
+    int64_t cls_out[4];
     // FWD with batch statistics: for every block of 32 output rows, row (m / 32) of `stats` ([ceil(M/32)][2][N] floats)
     // receives the per-channel sum and sum of squares of the stored values (rows past M left out).  Null: off.
     float* stats;
@@ -549,19 +557,45 @@ __device__ __forceinline__ void st_release_gpu(int* p, int v) {
 
 // Registers are handed out per group of four warps, so the 10 warps are budgeted as 12: 168 registers per thread
 // is the most a launch of this shape gets (200 compiles but is refused at launch).
-template <int MODE, int BN, int STAGES, bool SK, int SLABS, int BSRC>
+// Geometry of the tile a role is working on: the launch's own, or that of the tile's pixel class (MULTI).
+struct TileGeo {
+    int M, P, Q, kblocks, S, low_h, low_w, r0, s0, ltile;
+    int64_t out_off;
+    const CUtensorMap* ma;
+};
+
+template <int MODE, int BN, int STAGES, bool SK, int SLABS, int BSRC, bool STREAM, bool MULTI>
 __global__ void __launch_bounds__(320, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b0,
-               const __grid_constant__ CUtensorMap tmap_b1, const __grid_constant__ CUtensorMap tmap_out, TcParams p)
+               const __grid_constant__ CUtensorMap tmap_b1, const __grid_constant__ CUtensorMap tmap_out,
+               const __grid_constant__ CUtensorMap tmap_a3, TcParams p)
 {
+    static_assert(!MULTI || (MODE == TCM_FWD && !SK && !STREAM && BSRC != TCB_SPLIT), "pixel classes: whole-tile forward variant on the caller's filter");
+    // MULTI: the activation maps of classes 0..3 travel in the parameter slots tmap_a, tmap_b1, tmap_out, tmap_a3
+    // (the split-filter map and the output map have no use there: filters are read in place, rows are scattered).
+    auto tile_geo = [&](int tile) {
+        TileGeo t;
+        if (MULTI) {
+            int c = 0;
+            while (c + 1 < p.ncls && tile >= p.cls_tile0[c + 1]) c++;
+            t.M = p.cls_M[c]; t.P = p.cls_P[c]; t.Q = p.cls_Q[c]; t.kblocks = p.cls_kblocks[c]; t.S = p.cls_S[c];
+            t.low_h = p.cls_low_h[c]; t.low_w = p.cls_low_w[c]; t.r0 = p.cls_r0[c]; t.s0 = p.cls_s0[c];
+            t.ltile = tile - p.cls_tile0[c]; t.out_off = p.cls_out[c];
+            t.ma = c == 0 ? &tmap_a : c == 1 ? &tmap_b1 : c == 2 ? &tmap_out : &tmap_a3;
+        } else {
+            t.M = p.M; t.P = p.P; t.Q = p.Q; t.kblocks = p.kblocks; t.S = p.S; t.low_h = p.low_h; t.low_w = p.low_w;
+            t.r0 = p.tap_r0; t.s0 = p.tap_s0; t.ltile = tile; t.out_off = 0; t.ma = &tmap_a;
+        }
+        return t;
+    };
     pdl_launch_dependents();
     // Persistent: each CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ... (column tile fastest, so
     // CTAs running at the same time share activation rows in L2).  The smem pipeline and the two TMEM
     // buffers keep running across tile boundaries: the producer prefetches the next tile while the
     // drain warps still store the previous one.
     using L = TcSmem<BN, STAGES, SLABS>;
-    // the four-slab variant serves tiles of at most TC_CHUNK k-blocks with dense outputs (see dispatch_fwd)
-    constexpr bool STREAM = MODE == TCM_FWD && !SK && SLABS == 4;
+    // STREAM variants serve tiles of at most TC_CHUNK k-blocks with dense outputs (see dispatch_fwd)
+    static_assert(!STREAM || (MODE == TCM_FWD && !SK), "the streaming epilogue is a whole-tile forward variant");
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* full_bar = (uint64_t*)(smem + L::BAR_OFFSET);
@@ -575,12 +609,13 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     TC_PROF_DECL();
     const int mt = (p.M + 127) / 128, nt = (p.N + BN - 1) / BN;
-    const int total_tiles = mt * nt * p.splits;
+    const int total_tiles = MULTI ? p.cls_tile0[p.ncls] : mt * nt * p.splits;
 
     if (threadIdx.x == 32) {      // the tensor maps are kernel parameters: their fetch can start before anything else
         tma_prefetch_map(&tmap_a); tma_prefetch_map(&tmap_b0);
         if (BSRC == TCB_SPLIT && MODE == TCM_FWD) tma_prefetch_map(&tmap_b1);
         if (p.tma_store) tma_prefetch_map(&tmap_out);
+        if (MULTI) { if (p.ncls > 1) tma_prefetch_map(&tmap_b1); if (p.ncls > 2) tma_prefetch_map(&tmap_out); if (p.ncls > 3) tma_prefetch_map(&tmap_a3); }
     }
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&xform_bar[s], 4); mbar_init(&empty_bar[s], 1); }
@@ -607,15 +642,17 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         TileWalk w;
         w.init(total_tiles, p.kblocks);
         while (ok && w.template next<SK>()) {
-            const int tile = w.tile;
-            const int ni = tile % nt, rest = tile / nt, mi = rest % mt, z = rest / mt;
+            const TileGeo tg = tile_geo(w.tile);
+            if (MULTI) w.kb_e = tg.kblocks;
+            const int tile = tg.ltile;
+            const int ni = tile % nt, rest = tile / nt, mi = MULTI ? rest : rest % mt, z = MULTI ? 0 : rest / mt;
             const int m0 = mi * 128, n0 = ni * BN;
             int img = 0, base_w = 0, base_h = 0;
             if (MODE == TCM_FWD) {
-                img = m0 / (p.P * p.Q);
-                const int rem = m0 - img * (p.P * p.Q);
-                const int p0 = rem / p.Q, q0 = rem - p0 * p.Q;
-                base_w = q0 * p.str_w + p.low_w; base_h = p0 * p.str_h + p.low_h;
+                img = m0 / (tg.P * tg.Q);
+                const int rem = m0 - img * (tg.P * tg.Q);
+                const int p0 = rem / tg.Q, q0 = rem - p0 * tg.Q;
+                base_w = q0 * p.str_w + tg.low_w; base_h = p0 * p.str_h + tg.low_h;
             }
             // WGRAD: the tile's boxes are fixed: up to four x boxes (32 rows of (tap, ci) each) and BN/32 dy
             // boxes (32 output channels each)
@@ -648,7 +685,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 uint8_t* st = smem + s * L::STAGE_BYTES;
                 if (MODE == TCM_FWD) {
                     const int tap = kb / p.cblocks, cb = kb - tap * p.cblocks;
-                    const int r = tap / p.S, sx = tap - r * p.S;
+                    const int r = tap / tg.S, sx = tap - r * tg.S;
                     if (elect_one_sync()) {
 #ifdef B2C_TC_DEV
                         if (p.dbg & 64) mbar_arrive(&full_bar[s]);
@@ -656,13 +693,13 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #endif
                         {
                             mbar_expect_tx(&full_bar[s], (uint32_t)(BSRC == TCB_SPLIT ? L::STAGE_BYTES : L::A_BYTES + L::B_BYTES));
-                            tma_load_im2col_4d(st, &tmap_a, &full_bar[s], cb * 32, base_w, base_h, img,
+                            tma_load_im2col_4d(st, tg.ma, &full_bar[s], cb * 32, base_w, base_h, img,
                                                (uint16_t)(sx * p.dil_w), (uint16_t)(r * p.dil_h));
                             if (BSRC == TCB_SPLIT) {
                                 tma_load_2d(st + L::A_BYTES, &tmap_b0, &full_bar[s], kb * 32, n0);
                                 tma_load_2d(st + L::A_BYTES + L::B_BYTES, &tmap_b1, &full_bar[s], kb * 32, n0);
                             } else {
-                                const int tap_real = (p.tap_r0 + p.tap_rstep * r) * p.tap_sreal + p.tap_s0 + p.tap_sstep * sx;
+                                const int tap_real = (tg.r0 + p.tap_rstep * r) * p.tap_sreal + tg.s0 + p.tap_sstep * sx;
                                 if (BSRC == TCB_RAW_K) {
                                     tma_load_3d(st + L::A_BYTES, &tmap_b0, &full_bar[s], cb * 32, tap_real, n0);
                                 } else {
@@ -680,6 +717,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     const int p0 = rem / p.Q, q0 = rem - p0 * p.Q;
                     const int cw = q0 * p.str_w + p.low_w, chh = p0 * p.str_h + p.low_h;
                     if (elect_one_sync()) {
+#ifdef B2C_TC_DEV
+                        if (p.dbg & 64) mbar_arrive(&full_bar[s]);
+                        else
+#endif
+                        {
                         mbar_expect_tx(&full_bar[s], (uint32_t)(boxes * 4096));
 #pragma unroll
                         for (int j = 0; j < 4; j++)
@@ -690,6 +732,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         for (int j = 0; j < BN / 32; j++)
                             if (n0 + 32 * j < p.N)
                                 tma_load_2d(st + L::A_BYTES + j * 4096, &tmap_b0, &full_bar[s], n0 + 32 * j, pix0);
+                        }
                     }
                 }
                 __syncwarp();
@@ -714,6 +757,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             TileWalk w;
             w.init(total_tiles, p.kblocks);
             while (ok && w.template next<SK>()) {
+                if (MULTI) w.kb_e = tile_geo(w.tile).kblocks;
                 for (int kb = w.kb_b; kb < w.kb_e && ok; kb++, it++) {
                     const int s = it % STAGES, use = it / STAGES;
                     const int b = gc & 1;
@@ -776,6 +820,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         TileWalk w;
         w.init(total_tiles, p.kblocks);
         while (ok && w.template next<SK>()) {
+            if (MULTI) w.kb_e = tile_geo(w.tile).kblocks;
             // WGRAD: the tiles of the first row block also sum their dy tile over the pixels (the bias gradient);
             // a thread meets the same four channels of each 32-channel box in every k-block (see below)
             float4 dbacc[B_VEC / 2 + 1];
@@ -868,8 +913,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         TileWalk w;
         w.init(total_tiles, p.kblocks);
         while (ok && w.template next<SK>()) {
-            const int tile = w.tile;
-            const int ni = tile % nt, rest = tile / nt, mi = rest % mt, z = rest / mt;
+            const TileGeo tg = tile_geo(w.tile);
+            if (MULTI) w.kb_e = tg.kblocks;
+            const int tile = tg.ltile;
+            const int ni = tile % nt, rest = tile / nt, mi = MULTI ? rest : rest % mt, z = MULTI ? 0 : rest / mt;
             const int m0 = mi * 128, n0 = ni * BN;
             // One 32-row x 32-column slab of the tile on its way out (dense outputs): epilogue steps, staging in a
             // 128B-swizzled slab (conflict-free float4 writes), TMA store (whole rows, asynchronous, rows >= M and
@@ -1036,12 +1083,12 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             // that every store instruction writes whole 128-byte row segments (8 lanes per row, 4 rows).
             const int m = m0 + quad * 32 + lane;
             int64_t my_off = -1;
-            if (m < p.M) {
+            if (m < tg.M) {
                 if (MODE == TCM_FWD) {
-                    const int img = m / (p.P * p.Q);
-                    const int rem = m - img * (p.P * p.Q);
-                    const int pi = rem / p.Q, qi = rem - pi * p.Q;
-                    my_off = img * p.o_sn + pi * p.o_sh + qi * p.o_sw;
+                    const int img = m / (tg.P * tg.Q);
+                    const int rem = m - img * (tg.P * tg.Q);
+                    const int pi = rem / tg.Q, qi = rem - pi * tg.Q;
+                    my_off = tg.out_off + img * p.o_sn + pi * p.o_sh + qi * p.o_sw;
                 } else {
                     my_off = ((int64_t)z * p.M + m) * p.N;
                 }
@@ -1319,17 +1366,18 @@ static size_t tc_workspace_bytes_nhwc(const Geo& g, int pass)
            align_up((size_t)pl.splits * 4 * g.co * sizeof(float), 1024);
 }
 
-template <int MODE, int BN, int STAGES, bool SK, int SLABS, int BSRC>
-static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb0, const CUtensorMap& mb1, const CUtensorMap& mo, const TcParams& p, int splits, cudaStream_t st)
+template <int MODE, int BN, int STAGES, bool SK, int SLABS, int BSRC, bool STREAM = false, bool MULTI = false>
+static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb0, const CUtensorMap& mb1, const CUtensorMap& mo, const TcParams& p, int splits, cudaStream_t st,
+                     const CUtensorMap* ma3 = nullptr)
 {
     using L = TcSmem<BN, STAGES, SLABS>;
     static PerDeviceOnce attr;
     {
-        cudaError_t e = attr.run([] { return cudaFuncSetAttribute(conv_tc_kernel<MODE, BN, STAGES, SK, SLABS, BSRC>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL); });
+        cudaError_t e = attr.run([] { return cudaFuncSetAttribute(conv_tc_kernel<MODE, BN, STAGES, SK, SLABS, BSRC, STREAM, MULTI>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL); });
         if (e != cudaSuccess) { set_cuda_error(e, "cudaFuncSetAttribute(conv_tc_kernel)"); return B2C_ERR_CUDA; }
     }
     const int sm_count = tc_sm_count();
-    int64_t tiles = (int64_t)((p.M + 127) / 128) * ((p.N + BN - 1) / BN) * splits;
+    int64_t tiles = MULTI ? p.cls_tile0[p.ncls] : (int64_t)((p.M + 127) / 128) * ((p.N + BN - 1) / BN) * splits;
     if (tiles > 0x7fffffffLL) return B2C_ERR_TOO_LARGE;
     TcParams q = p;
     q.splits = splits;
@@ -1337,7 +1385,7 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb0, const CUtens
     { const char* e = getenv("B2C_TC_DBG"); q.dbg = e ? atoi(e) : 0; }
 #endif
     const int grid = q.sk ? sm_count : (int)(tiles < sm_count ? tiles : sm_count);     // one persistent CTA per SM
-    launch_pdl(conv_tc_kernel<MODE, BN, STAGES, SK, SLABS, BSRC>, grid, 320, L::TOTAL, st, ma, mb0, mb1, mo, q);
+    launch_pdl(conv_tc_kernel<MODE, BN, STAGES, SK, SLABS, BSRC, STREAM, MULTI>, grid, 320, L::TOTAL, st, ma, mb0, mb1, mo, ma3 ? *ma3 : ma, q);
     return check_launch("conv_tc_kernel");
 }
 
@@ -1348,11 +1396,16 @@ static int dispatch_fwd(int bn, const CUtensorMap& ma, const CUtensorMap& mb0, c
         if (bn == 64) return launch_tc<TCM_FWD, 64, 6, true, 2, BSRC>(ma, mb0, mb1, mo, p, 1, st);
         return launch_tc<TCM_FWD, 128, 4, true, 2, BSRC>(ma, mb0, mb1, mo, p, 1, st);
     }
-    // Short K loops (up to four k-blocks per tile) are bound by the epilogue: a shallower operand pipeline
-    // leaves room for four output slabs per drain warp, so a whole tile's stores are in flight at once.
+    // Short K loops are bound by the epilogue.  Tiles of one tensor-memory chunk (at most TC_CHUNK k-blocks) take the
+    // streaming epilogue (32 columns at a time straight from tensor memory); up to four k-blocks per tile a shallower
+    // operand pipeline also leaves room for four output slabs per drain warp, so a whole tile's stores are in flight.
     if (p.kblocks <= 4 && p.tma_store) {
-        if (bn == 64) return launch_tc<TCM_FWD, 64, 4, false, 4, BSRC>(ma, mb0, mb1, mo, p, 1, st);
-        return launch_tc<TCM_FWD, 128, 3, false, 4, BSRC>(ma, mb0, mb1, mo, p, 1, st);
+        if (bn == 64) return launch_tc<TCM_FWD, 64, 4, false, 4, BSRC, true>(ma, mb0, mb1, mo, p, 1, st);
+        return launch_tc<TCM_FWD, 128, 3, false, 4, BSRC, true>(ma, mb0, mb1, mo, p, 1, st);
+    }
+    if (p.kblocks <= TC_CHUNK && p.tma_store) {
+        if (bn == 64) return launch_tc<TCM_FWD, 64, 6, false, 2, BSRC, true>(ma, mb0, mb1, mo, p, 1, st);
+        return launch_tc<TCM_FWD, 128, 4, false, 2, BSRC, true>(ma, mb0, mb1, mo, p, 1, st);
     }
     if (bn == 64) return launch_tc<TCM_FWD, 64, 6, false, 2, BSRC>(ma, mb0, mb1, mo, p, 1, st);
     return launch_tc<TCM_FWD, 128, 4, false, 2, BSRC>(ma, mb0, mb1, mo, p, 1, st);
@@ -1562,6 +1615,73 @@ static int tc_fprop_nhwc(const Geo& g, const void* x, const void* w, const void*
     return run_fwd(f, x, w, pp, bias, bn, relu, (float*)y, ws, ws_bytes, st, false, stats);
 }
 
+// Strided data gradient, all parity classes in one launch (MULTI kernel variants): up to four classes, every class
+// with at least one tap, filters read in place.  The tiles of the classes with the most taps come first in the tile
+// list, so the persistent CTAs end with the short ones.  Returns 1 when the shape does not qualify.
+static int tc_dgrad_classes_one_launch(const Geo& g, const WStride& wsd, const void* dy, const void* w, void* dx, cudaStream_t st)
+{
+    if (g.vstr * g.hstr > 4 || !load_driver_entry_points()) return 1;
+    struct Cls { AxisClass a, b; int ia, ib; };
+    Cls cls[4];
+    int ncls = 0;
+    for (int a = 0; a < g.vstr; a++)
+        for (int b = 0; b < g.hstr; b++) {
+            AxisClass ca = axis_class(a, g.vstr, g.vpad, g.kh, g.h), cb = axis_class(b, g.hstr, g.hpad, g.kw, g.w);
+            if (ca.out_cnt == 0 || cb.out_cnt == 0) continue;
+            if (ca.cnt == 0 || cb.cnt == 0) return 1;           // a class without taps: the zero-fill path handles it
+            cls[ncls++] = Cls{ca, cb, a, b};
+        }
+    if (ncls < 2) return 1;
+    for (int i = 0; i < ncls; i++)                              // most taps first
+        for (int j = i + 1; j < ncls; j++)
+            if (cls[j].a.cnt * cls[j].b.cnt > cls[i].a.cnt * cls[i].b.cnt) { Cls t = cls[i]; cls[i] = cls[j]; cls[j] = t; }
+    if (((uintptr_t)dy & 15) || ((uintptr_t)dx & 15) || ((uintptr_t)w & 15)) return 1;
+    // the filter as the B operand, in place (see run_fwd): rows = ci (GEMM N), contraction channel = co
+    const int64_t s_row = wsd.sc, s_c = wsd.sk, s_r = wsd.sr, s_s = wsd.ss;
+    if (s_r != (int64_t)g.kw * s_s || (s_s * 4) % 16) return 1;
+    const int BN = g.ci <= 64 ? 64 : 128;
+    const uint64_t taps = (uint64_t)g.kh * g.kw;
+    CUtensorMap mb;
+    int bsrc;
+    if (s_c == 1 && (s_row * 4) % 16 == 0 &&
+        make_map_filter(&mb, w, (uint64_t)g.co, taps, (uint64_t)g.ci, (uint64_t)s_s * 4, (uint64_t)s_row * 4, BN, CU_TENSOR_MAP_SWIZZLE_128B))
+        bsrc = TCB_RAW_K;
+    else if (s_row == 1 && (s_c * 4) % 16 == 0 &&
+             make_map_filter(&mb, w, (uint64_t)g.ci, taps, (uint64_t)g.co, (uint64_t)s_s * 4, (uint64_t)s_c * 4, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B))
+        bsrc = TCB_RAW_MN;
+    else return 1;
+    TcParams p{};
+    CUtensorMap ma[4];
+    const int nt = (g.ci + BN - 1) / BN;
+    p.N = g.ci; p.C = g.co; p.cblocks = g.co / 32;
+    p.str_h = 1; p.str_w = 1; p.dil_h = 1; p.dil_w = 1;
+    p.out = (float*)dx; p.o_sn = (int64_t)g.h * g.w * g.ci; p.o_sh = (int64_t)g.vstr * g.w * g.ci; p.o_sw = (int64_t)g.hstr * g.ci;
+    p.tap_rstep = -g.vstr; p.tap_sstep = -g.hstr; p.tap_sreal = g.kw;
+    p.splits = 1; p.ncls = ncls;
+    int64_t tiles = 0;
+    for (int i = 0; i < ncls; i++) {
+        const AxisClass &ca = cls[i].a, &cb = cls[i].b;
+        if (!make_map_im2col(&ma[i], dy, g.n, g.ho, g.wo, g.co, ca.dmin, cb.dmin, ca.out_cnt, cb.out_cnt, 1, 1, 128)) return 1;
+        p.cls_tile0[i] = (int)tiles;
+        p.cls_M[i] = g.n * ca.out_cnt * cb.out_cnt; p.cls_P[i] = ca.out_cnt; p.cls_Q[i] = cb.out_cnt;
+        p.cls_kblocks[i] = ca.cnt * cb.cnt * p.cblocks; p.cls_S[i] = cb.cnt;
+        p.cls_low_h[i] = ca.dmin; p.cls_low_w[i] = cb.dmin; p.cls_r0[i] = ca.r0; p.cls_s0[i] = cb.r0;
+        p.cls_out[i] = ((int64_t)cls[i].ia * g.w + cls[i].ib) * g.ci;
+        tiles += (int64_t)((p.cls_M[i] + 127) / 128) * nt;
+        if (tiles > 0x7fffffffLL) return 1;
+    }
+    for (int i = ncls; i < 4; i++) ma[i] = ma[0];
+    p.cls_tile0[ncls] = (int)tiles;
+    // launch-wide fields the kernel still reads
+    p.M = p.cls_M[0]; p.P = p.cls_P[0]; p.Q = p.cls_Q[0]; p.kblocks = p.cls_kblocks[0]; p.S = p.cls_S[0];
+    if (bsrc == TCB_RAW_K) {
+        if (BN == 64) return launch_tc<TCM_FWD, 64, 6, false, 2, TCB_RAW_K, false, true>(ma[0], mb, ma[1], ma[2], p, 1, st, &ma[3]);
+        return launch_tc<TCM_FWD, 128, 4, false, 2, TCB_RAW_K, false, true>(ma[0], mb, ma[1], ma[2], p, 1, st, &ma[3]);
+    }
+    if (BN == 64) return launch_tc<TCM_FWD, 64, 6, false, 2, TCB_RAW_MN, false, true>(ma[0], mb, ma[1], ma[2], p, 1, st, &ma[3]);
+    return launch_tc<TCM_FWD, 128, 4, false, 2, TCB_RAW_MN, false, true>(ma[0], mb, ma[1], ma[2], p, 1, st, &ma[3]);
+}
+
 static int tc_dgrad_nhwc(const Geo& g, const void* dy, const void* w, void* dx, void* ws, size_t ws_bytes, cudaStream_t st)
 {
     WStride wsd = w_stride(g.w_layout, g.ci, g.co, g.kh, g.kw);
@@ -1576,6 +1696,10 @@ static int tc_dgrad_nhwc(const Geo& g, const void* dy, const void* w, void* dx, 
     // Strided: the input positions split into str_h*str_w parity classes; each class is a dense
     // stride-1 convolution of dy with the sub-filter of the taps that reach it, written to its
     // strided positions of dx. Classes no tap reaches stay zero.
+    {
+        int rc = tc_dgrad_classes_one_launch(g, wsd, dy, w, dx, st);
+        if (rc != 1) return rc;            // 1: not applicable, one launch per class below
+    }
     bool any_empty = false;
     for (int a = 0; a < g.vstr; a++)
         for (int b = 0; b < g.hstr; b++) {
