@@ -371,15 +371,43 @@ def run_ours(args):
             for p, pname in enumerate(("fprop", "dgrad", "wgrad")):
                 e = L.b2c_conv_engine_for(ctypes.byref(layer.desc), p)
                 engines[pname + ("_tensor" if e == _lib.ENGINE_TENSOR else "_fma")] = engines.get(pname + ("_tensor" if e == _lib.ENGINE_TENSOR else "_fma"), 0) + 1
+    # DRAM traffic of the convolution launches: every pass is put in a kernel class, and the class's measured /
+    # algorithmic ratio (small ncu captures of one layer per class, profiles/traffic.json) is applied to the pass's
+    # own algorithmic bytes; the sum over the passes, per launch, is the line's `traffic`.
     traffic, traffic_note = None, None
     tpath = os.path.join(ROOT, "profiles", "traffic.json")
     if os.path.exists(tpath) and conv_launches:
         with open(tpath) as f:
-            tj = json.load(f)
-        # DRAM bytes per launch: the measured/algorithmic ratio of the ncu capture (a smaller case of the
-        # same kernel) applied to the average algorithmic bytes of the launches timed here
-        traffic = tj["measured_over_algorithmic"] * conv_min_bytes / conv_launches
-        traffic_note = tj["case"]
+            tj = json.load(f)["classes"]
+
+        def klass(layer, name):
+            if layer.ci % 32:
+                return "stem_wgrad" if name == "wgrad" else "stem_fprop"
+            small = layer.hi <= 14
+            if name == "wgrad":
+                return "wgrad_small" if small else ("wgrad_1x1_large" if layer.kh == 1 else "wgrad_large")
+            if name == "dgrad" and layer.vstride > 1 and layer.kh > 1:
+                return "strided_dgrad"
+            if small:
+                return "l2_resident_fprop_dgrad"
+            k = layer.ci if name == "fprop" else layer.co
+            if layer.kh == 1 and k <= 256 and layer.hi >= 56:
+                return "short_k_fprop_with_bn_sums" if name == "fprop" and getattr(layer, "stats_for_bn", None) is not None \
+                    else "short_k_fprop_dgrad"
+            return "long_fprop_dgrad"
+        total, shares = 0.0, {}
+        for name, layer, e0, e1 in prof:
+            lb = 4.0 * model.batch_size * (layer.hi * layer.wi * layer.ci + layer.ho * layer.wo * layer.co) + \
+                4.0 * layer.kh * layer.kw * layer.ci * layer.co
+            c = klass(layer, name)
+            total += lb * tj[c]["measured_over_algorithmic"]
+            shares[c] = shares.get(c, 0.0) + lb
+        traffic = total / conv_launches
+        traffic_note = {"basis": "per-class measured/algorithmic DRAM ratios of profiles/traffic.json weighted by each class's "
+                                 "algorithmic bytes in this step",
+                        "share_of_algorithmic_bytes": {c: round(v / conv_min_bytes, 3) for c, v in sorted(shares.items())},
+                        "ratios": {c: tj[c]["measured_over_algorithmic"] for c in sorted(shares)},
+                        "classes_over_1.2x": [c for c in sorted(shares) if tj[c]["measured_over_algorithmic"] > 1.2]}
     roofline = {
         "bound": "tensor", "achieved": achieved, "peak": peak_3xtf32, "unit": "TFLOP/s",
         "frac": achieved / peak_3xtf32, "traffic": traffic, "traffic_basis": traffic_note,

@@ -52,10 +52,14 @@ class PinnedFeeder:
             model.train_batch(x, labels, optimizer, global_bs, next_batch=nxt)
     """
 
-    def __init__(self, model, generator, pin=True):
+    def __init__(self, model, generator, pin=True, wait_upload=None):
+        """``wait_upload``: called before a pair is overwritten; must return once the asynchronous upload that read the
+        pair two steps earlier has finished (the model passes a wait on its copy stream's event).  Callers that read
+        a result back every step, as the reference's loop does for its metrics, are past that point anyway."""
         import torch
         self.model = model
         self.gen = iter(generator)
+        self.wait_upload = wait_upload
         in_shape = tuple(model.layers[0].y.ary.shape)
         tdt = torch.float64 if np.dtype(model.dtype) == np.float64 else torch.float32
         mk = (lambda *a, **k: torch.empty(*a, **k).pin_memory()) if pin else torch.empty
@@ -70,6 +74,8 @@ class PinnedFeeder:
                 self.skipped += 1
                 continue
             xs, ys = self.slots[slot]
+            if self.wait_upload is not None:
+                self.wait_upload()
             xs.copy_(torch.from_numpy(np.ascontiguousarray(x, dtype=self.model.dtype)).view(xs.shape))
             lab = y if y.ndim == 1 else np.argmax(y, axis=1)
             ys.copy_(torch.from_numpy(np.ascontiguousarray(lab, dtype=np.int32)))

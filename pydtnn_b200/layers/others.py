@@ -7,7 +7,7 @@ import numpy as np
 
 from .. import initializers
 from ..utils import decode_tensor, encode_tensor
-from .base import Layer
+from .base import Layer, pair, window_output_extent
 from .conv_2d import Conv2D
 
 
@@ -91,9 +91,8 @@ class _Pool2D(Layer, ABC):
         super().__init__()
         self.pool_shape = tuple(pool_shape)
         self.padding, self.stride, self.dilation = padding, stride, dilation
-        self.vpadding, self.hpadding = (padding, padding) if isinstance(padding, int) else padding
-        self.vstride, self.hstride = (stride, stride) if isinstance(stride, int) else stride
-        self.vdilation, self.hdilation = (dilation, dilation) if isinstance(dilation, int) else dilation
+        (self.vpadding, self.hpadding), (self.vstride, self.hstride) = pair(padding), pair(stride)
+        self.vdilation, self.hdilation = pair(dilation)
 
     def initialize(self, prev_shape, need_dx=True):
         super().initialize(prev_shape, need_dx)
@@ -104,8 +103,8 @@ class _Pool2D(Layer, ABC):
             self.pool_shape = (self.pool_shape[0], self.wi)
         self.kh, self.kw = self.pool_shape
         self.co = self.ci
-        self.ho = (self.hi + 2 * self.vpadding - self.vdilation * (self.kh - 1) - 1) // self.vstride + 1
-        self.wo = (self.wi + 2 * self.hpadding - self.hdilation * (self.kw - 1) - 1) // self.hstride + 1
+        self.ho = window_output_extent(self.hi, self.kh, self.vpadding, self.vstride, self.vdilation)
+        self.wo = window_output_extent(self.wi, self.kw, self.hpadding, self.hstride, self.hdilation)
         assert self.ho > 0 and self.wo > 0, "Output dimensions must be greater than 0"
         self.shape = encode_tensor((self.ho, self.wo, self.co), self.model.tensor_format)
 

@@ -20,6 +20,7 @@ from .comm import GradientBucketer
 from .layers import (BatchNormalization, Conv2D, Conv2DBatchNormalization, Conv2DBatchNormalizationRelu, Conv2DRelu,
                      Relu)
 from .losses import CategoricalCrossEntropy
+from .performance_counter import PerformanceCounter
 from .tensor_gpu import empty
 from .utils import (EVALUATE_MODE, PYDTNN_TENSOR_FORMAT_NCHW, PYDTNN_TENSOR_FORMAT_NHWC, TRAIN_MODE,
                     UNSPECIFIED_MODE, np_dtype)
@@ -77,6 +78,7 @@ class Model:
         self._train_fused = False
         self._stage = None
         self.tracer = tracer.StepTracer()        # off until enable_tracing()
+        self.perf_counter = PerformanceCounter()
         self._eval_layers = None
         self.fast_update = True
         self.fuse_add_relu = True
@@ -293,6 +295,24 @@ class Model:
         loss = self.forward_backward(global_batch_size)
         self.apply_update(optimizer)
         return loss
+
+    def train_epoch(self, x_data, y_data, optimizer, epoch=0, shuffle=True, rng=None):
+        """One pass over host arrays (first axis = samples), the way the reference's training loop walks a data set
+        (pydtnn/model.py:560-590): this rank's slices of every global batch (``datasets.batch_generator``), short last
+        batches skipped, loss and accuracy read back after every step, times booked in ``perf_counter``.  The batch
+        of step i + 1 is copied into pinned memory and uploaded while step i runs.  Returns the last step's
+        (loss, accuracy), or None when the data hold no full batch."""
+        import time
+        from .datasets import PinnedFeeder, batch_generator
+        gen = batch_generator(x_data, y_data, self.batch_size, self.rank, self.nprocs, shuffle, rng)
+        feeder = PinnedFeeder(self, gen, wait_upload=lambda: self._stage is not None and self._stage["ready"].synchronize())
+        last = None
+        for x, y, global_bs, nxt in feeder:
+            tic = time.perf_counter()
+            loss = self.train_batch(x, y, optimizer, global_bs, next_batch=nxt)
+            last = (loss.loss(), loss.accuracy())
+            self.perf_counter.add_training_time_and_batch_size(epoch, time.perf_counter() - tic, global_bs)
+        return last
 
     def evaluate_batch(self, x_batch, y_batch=None, next_batch=None):
         """Forward only, with the inference fusions that are switched on; returns the output handle

@@ -298,3 +298,54 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "absent.so"))
     with pytest.raises(_lib.B2CError):
         _lib.lib()
+
+
+def test_train_epoch_feeds_rank_slices_through_pinned_buffers():
+    """``train_epoch`` (rank-sliced batches, pinned double buffering, upload of the next batch under the running step)
+    against a plain loop over the same slices: same weights bit for bit, the short last batch skipped, every step
+    booked in the performance counter."""
+    from pydtnn_b200.datasets import batch_generator
+    from pydtnn_b200.optimizers import SGD
+    a = _small_resnet("NHWC", np.float32)
+    b = _small_resnet("NHWC", np.float32)
+    rng = np.random.Generator(np.random.PCG64(11))
+    n = 4 * 5 + 3                                        # five full batches and a short one
+    x = rng.standard_normal((n, *a.layers[0].shape)).astype(np.float32)
+    y = rng.integers(0, 10, n)
+    oa, ob = SGD(0.05, 0.9), SGD(0.05, 0.9)
+    last = a.train_epoch(x, y, oa, epoch=0, shuffle=True, rng=np.random.Generator(np.random.PCG64(5)))
+    steps = 0
+    for xb, yb, gbs in batch_generator(x, y, 4, 0, 1, True, np.random.Generator(np.random.PCG64(5))):
+        if xb.shape[0] != 4:
+            continue
+        lb = b.train_batch(xb, yb, ob, gbs)
+        steps += 1
+    assert steps == 5 and last is not None and last[0] == lb.loss()
+    assert a.perf_counter.num_epochs == 1 and a.perf_counter.training_throughput > 0
+    for pa, pb in zip(a.get_all_layers(), b.get_all_layers()):
+        for k in pa.grad_vars:
+            assert np.array_equal(getattr(pa, k).ary.get(), getattr(pb, k).ary.get()), (pa, k)
+
+
+def test_per_operation_events_of_conv_and_fc_layers():
+    from pydtnn_b200 import tracer as tr
+    from pydtnn_b200.optimizers import SGD
+    m = _small_resnet("NHWC", np.float32)
+    opt = SGD(0.05, 0.9)
+    x, labels = _batch(m, 0)
+    m.train_batch(x, labels, opt)
+    m.tracer.enable_tracing(ops=True)
+    m.train_batch(x, labels, opt)
+    m.tracer.disable_tracing()
+    m.synchronize()
+    ops = m.tracer.ops_summary()
+    convs = [l for l in m.get_all_layers() if type(l).__name__ == "Conv2DGPU"]
+    fcs = [l for l in m.get_all_layers() if type(l).__name__ == "FCGPU"]
+    assert convs and fcs
+    for l in convs:
+        assert ops[tr.ops_event_value(l.id, tr.PYDTNN_OPS_FORWARD_CUDNN)][1] == 1
+        assert ops[tr.ops_event_value(l.id, tr.PYDTNN_OPS_BACKWARD_CUDNN_DW)][1] == 1
+        assert (tr.ops_event_value(l.id, tr.PYDTNN_OPS_BACKWARD_CUDNN_DX) in ops) == bool(l.need_dx)
+    for l in fcs:
+        assert ops[tr.ops_event_value(l.id, tr.PYDTNN_OPS_FORWARD_CUBLAS_MATMUL)][1] == 1
+        assert ops[tr.ops_event_value(l.id, tr.PYDTNN_OPS_BACKWARD_CUBLAS_MATMUL_DW)][1] == 1
