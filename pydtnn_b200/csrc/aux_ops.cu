@@ -293,31 +293,40 @@ struct BnBwdV4 {
     }
 };
 
-// One warp per channel sums the per-chunk partials (fixed order per lane, then a shuffle tree).
+// Four warps per channel sum the per-chunk partials: every thread adds its chunks (128 apart) in index order, a shuffle
+// tree adds the lanes of a warp, and the four warp sums are added in warp order -- a fixed order whatever the launch.
+// With a few hundred chunks a thread has a handful of independent loads, so the kernel costs one memory round trip.
 // mode 0: batch statistics -> save_mean, save_inv_std, running averages. mode 1: (dgamma, dbeta).
 // mode 2: single sum -> out0.
-__global__ void reduce2_final_warp_kernel(const double* __restrict__ partial, int chunks, int c, int mode, double count,
-                                          double momentum, double eps, float* out0, float* out1, float* run0, float* run1)
+__global__ void __launch_bounds__(256) reduce2_final_warp_kernel(const double* __restrict__ partial, int chunks, int c, int mode, double count,
+                                                                 double momentum, double eps, float* out0, float* out1, float* run0, float* run1)
 {
     pdl_prologue();
-    const int ch = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-    if (ch >= c) return;
+    __shared__ double w0[2][4], w1[2][4];
+    const int sub = threadIdx.x >> 7;                       // which of the block's two channels
+    const int ch = blockIdx.x * 2 + sub;
+    const int t = threadIdx.x & 127, lane = threadIdx.x & 31, wrp = t >> 5;
     double s0 = 0.0, s1 = 0.0;
-    int i = lane;
-    // four independent loads per value in flight; the order of the additions stays fixed
-    for (; i + 96 < chunks; i += 128) {
-        double a0[4], a1[4];
+    if (ch < c) {
+        int i = t;
+        for (; i + 384 < chunks; i += 512) {
+            double a0[4], a1[4];
 #pragma unroll
-        for (int u = 0; u < 4; u++) {
-            a0[u] = partial[((int64_t)(i + 32 * u) * 2) * c + ch];
-            a1[u] = partial[((int64_t)(i + 32 * u) * 2 + 1) * c + ch];
+            for (int u = 0; u < 4; u++) {
+                a0[u] = partial[((int64_t)(i + 128 * u) * 2) * c + ch];
+                a1[u] = partial[((int64_t)(i + 128 * u) * 2 + 1) * c + ch];
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++) { s0 += a0[u]; s1 += a1[u]; }
         }
-#pragma unroll
-        for (int u = 0; u < 4; u++) { s0 += a0[u]; s1 += a1[u]; }
+        for (; i < chunks; i += 128) { s0 += partial[((int64_t)i * 2) * c + ch]; s1 += partial[((int64_t)i * 2 + 1) * c + ch]; }
     }
-    for (; i < chunks; i += 32) { s0 += partial[((int64_t)i * 2) * c + ch]; s1 += partial[((int64_t)i * 2 + 1) * c + ch]; }
     for (int o = 16; o > 0; o >>= 1) { s0 += __shfl_down_sync(0xffffffffu, s0, o); s1 += __shfl_down_sync(0xffffffffu, s1, o); }
-    if (lane) return;
+    if (lane == 0) { w0[sub][wrp] = s0; w1[sub][wrp] = s1; }
+    __syncthreads();
+    if (t != 0 || ch >= c) return;
+    s0 = ((w0[sub][0] + w0[sub][1]) + w0[sub][2]) + w0[sub][3];
+    s1 = ((w1[sub][0] + w1[sub][1]) + w1[sub][2]) + w1[sub][3];
     if (mode == 0) {
         double mean = s0 / count, var = s1 / count - mean * mean;
         if (var < 0.0) var = 0.0;
@@ -438,7 +447,7 @@ static V4Geo v4_apply_geo(int64_t rows, int c)
 static int final_warp(const double* partial, int chunks, int c, int mode, double count, double momentum, double eps,
                       float* o0, float* o1, float* r0, float* r1, cudaStream_t st)
 {
-    launch_pdl(reduce2_final_warp_kernel, (c * 32 + 255) / 256, 256, 0, st, partial, chunks, c, mode, count, momentum, eps, o0, o1, r0, r1);
+    launch_pdl(reduce2_final_warp_kernel, (c + 1) / 2, 256, 0, st, partial, chunks, c, mode, count, momentum, eps, o0, o1, r0, r1);
     return check_launch("reduce2_final_warp");
 }
 
@@ -739,7 +748,7 @@ __global__ void __launch_bounds__(256) pool_fwd_v4_kernel(PoolP p, const float4*
 }
 
 // IDX = int when the element count fits 31 bits: the index decomposition is then done with 32-bit divisions.
-template <bool IS_MAX, typename IDX>
+template <bool IS_MAX, typename IDX, bool UNIT_DIL>
 __global__ void __launch_bounds__(256) pool_bwd_v4_kernel(PoolP p, const float4* __restrict__ dy, const int4* __restrict__ idx_max, float4* __restrict__ dx)
 {
     pdl_prologue();
@@ -750,15 +759,21 @@ __global__ void __launch_bounds__(256) pool_bwd_v4_kernel(PoolP p, const float4*
         const int iw = (int)(r % p.w); r /= p.w;
         const int ih = (int)(r % p.h); const int nn = (int)(r / p.h);
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int ii = 0; ii < p.kh; ii++) {
-            const int t = ih + p.vpad - p.vdil * ii;
-            if (t < 0 || t % p.vstr) continue;
-            const int xx = t / p.vstr;
+        // Windows that contain this element, in ascending tap order.  With dilation 1 (UNIT_DIL) the taps that can reach
+        // it are ii0, ii0 + vstr, ... with ii0 = (ih + vpad) mod vstr, and the window row falls by one per step: one
+        // division per axis instead of a modulo and a division per tap.
+        const int th = ih + p.vpad, tw = iw + p.hpad;
+        const int ii0 = UNIT_DIL ? th % p.vstr : 0, ii_step = UNIT_DIL ? p.vstr : 1, xx0 = UNIT_DIL ? th / p.vstr : 0;
+        const int jj0 = UNIT_DIL ? tw % p.hstr : 0, jj_step = UNIT_DIL ? p.hstr : 1, yy0 = UNIT_DIL ? tw / p.hstr : 0;
+        for (int ii = ii0, ka = 0; ii < p.kh; ii += ii_step, ka++) {
+            int xx;
+            if (UNIT_DIL) { xx = xx0 - ka; if (xx < 0) break; }
+            else { const int t = th - p.vdil * ii; if (t < 0 || t % p.vstr) continue; xx = t / p.vstr; }
             if (xx >= p.ho) continue;
-            for (int jj = 0; jj < p.kw; jj++) {
-                const int u = iw + p.hpad - p.hdil * jj;
-                if (u < 0 || u % p.hstr) continue;
-                const int yy = u / p.hstr;
+            for (int jj = jj0, kb = 0; jj < p.kw; jj += jj_step, kb++) {
+                int yy;
+                if (UNIT_DIL) { yy = yy0 - kb; if (yy < 0) break; }
+                else { const int u = tw - p.hdil * jj; if (u < 0 || u % p.hstr) continue; yy = u / p.hstr; }
                 if (yy >= p.wo) continue;
                 const int64_t o = (((int64_t)nn * p.ho + xx) * p.wo + yy) * c4 + cg;
                 const float4 g = dy[o];
@@ -1252,10 +1267,17 @@ extern "C" int b2c_pool_backward(int dtype, int layout, int is_max, int n, int h
     int64_t total = (int64_t)n * h * w * c; int nchw = layout == B2C_LAYOUT_NCHW;
     if (dtype == B2C_F32 && !nchw && c % 4 == 0 && (((uintptr_t)dy | (uintptr_t)dx | (uintptr_t)idx_max) & 15) == 0) {
         const bool small = total / 4 + (int64_t)ew_blocks(total / 4) * 256 < 0x7fffffffLL;
-        if (is_max && small) launch_pdl(pool_bwd_v4_kernel<true, int>, ew_blocks(total / 4), 256, 0, st, p, (const float4*)dy, (const int4*)idx_max, (float4*)dx);
-        else if (is_max) launch_pdl(pool_bwd_v4_kernel<true, int64_t>, ew_blocks(total / 4), 256, 0, st, p, (const float4*)dy, (const int4*)idx_max, (float4*)dx);
-        else if (small) launch_pdl(pool_bwd_v4_kernel<false, int>, ew_blocks(total / 4), 256, 0, st, p, (const float4*)dy, (const int4*)idx_max, (float4*)dx);
-        else launch_pdl(pool_bwd_v4_kernel<false, int64_t>, ew_blocks(total / 4), 256, 0, st, p, (const float4*)dy, (const int4*)idx_max, (float4*)dx);
+        const bool unit = vdil == 1 && hdil == 1;
+#define B2C_POOL_BWD_V4(MAXF, IDXT)                                                                                                         \
+        do {                                                                                                                                \
+            if (unit) launch_pdl(pool_bwd_v4_kernel<MAXF, IDXT, true>, ew_blocks(total / 4), 256, 0, st, p, (const float4*)dy, (const int4*)idx_max, (float4*)dx);  \
+            else launch_pdl(pool_bwd_v4_kernel<MAXF, IDXT, false>, ew_blocks(total / 4), 256, 0, st, p, (const float4*)dy, (const int4*)idx_max, (float4*)dx);     \
+        } while (0)
+        if (is_max && small) B2C_POOL_BWD_V4(true, int);
+        else if (is_max) B2C_POOL_BWD_V4(true, int64_t);
+        else if (small) B2C_POOL_BWD_V4(false, int);
+        else B2C_POOL_BWD_V4(false, int64_t);
+#undef B2C_POOL_BWD_V4
         return check_launch("pool_backward_v4");
     }
     if (dtype == B2C_F32) {

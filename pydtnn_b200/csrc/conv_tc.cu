@@ -1135,26 +1135,72 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 // caller's filter layout.
 struct WgradReduceParams { int M, N, C, S, splits; int64_t sk, sc, sr, ss; int Mreal; };
 
-__global__ void tc_wgrad_reduce_kernel(WgradReduceParams p, const float* __restrict__ partial, float* __restrict__ dw,
-                                       const float* __restrict__ db_partial, float* __restrict__ db)
+__global__ void __launch_bounds__(256) tc_wgrad_reduce_kernel(WgradReduceParams p, const float* __restrict__ partial, float* __restrict__ dw,
+                                                              const float* __restrict__ db_partial, float* __restrict__ db)
 {
     pdl_prologue();
-    // bias gradient: the [splits][4] per-channel sums, added in a fixed order
-    if (db) {
-        for (int n = blockIdx.x * blockDim.x + threadIdx.x; n < p.N; n += gridDim.x * blockDim.x) {
+    // bias gradient: the [splits][4] per-channel sums, added in a fixed order (first block row only)
+    if (db && blockIdx.y == 0) {
+        const int n = blockIdx.x * 32 + threadIdx.x;
+        if (threadIdx.y == 0 && n < p.N) {
             float v = 0.f;
-            for (int i = 0; i < p.splits * 4; i++) v += db_partial[(size_t)i * p.N + n];
+            for (int i = 0; i < p.splits * 4; i++) v += __ldcg(db_partial + (size_t)i * p.N + n);
             db[n] = v;
         }
     }
-    int64_t total = (int64_t)p.M * p.N;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-        int m = (int)(i / p.N), n = (int)(i - (int64_t)m * p.N);
-        if (m >= p.Mreal) continue;            // zero-padding rows of a lowered few-channel layer
-        float v = 0.f;
-        for (int z = 0; z < p.splits; z++) v += partial[(int64_t)z * total + i];
-        int tap = m / p.C, c = m - tap * p.C, r = tap / p.S, s = tap - r * p.S;
-        dw[n * p.sk + c * p.sc + r * p.sr + s * p.ss] = v;
+    // A block owns 32 rows (tap, ci) x 32 output channels.  Thread (x, y) adds, in split order, the partials of column
+    // n0 + x for rows y, y + 8, y + 16, y + 24 (loads of a warp cover 128 contiguous bytes; the four rows and four
+    // splits at a time are independent loads).  The sums then leave along whichever axis is contiguous in the caller's
+    // filter layout: output channels as they are, (tap, ci) rows through a transposing shared-memory tile.
+    __shared__ float tile[32][33];
+    const int m0 = blockIdx.y * 32, n0 = blockIdx.x * 32;
+    const int64_t plane = (int64_t)p.M * p.N;
+    const int n = n0 + threadIdx.x;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (n < p.N) {
+        const float* src = partial + (int64_t)(m0 + threadIdx.y) * p.N + n;
+        bool in[4];
+#pragma unroll
+        for (int r = 0; r < 4; r++) in[r] = m0 + threadIdx.y + 8 * r < p.M;
+        int z = 0;
+        for (; z + 4 <= p.splits; z += 4) {
+            float q[4][4];
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+#pragma unroll
+                for (int r = 0; r < 4; r++) q[u][r] = in[r] ? __ldcg(src + (int64_t)(z + u) * plane + (int64_t)(8 * r) * p.N) : 0.f;
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+#pragma unroll
+                for (int r = 0; r < 4; r++) v[r] += q[u][r];
+        }
+        for (; z < p.splits; z++)
+#pragma unroll
+            for (int r = 0; r < 4; r++) v[r] += in[r] ? __ldcg(src + (int64_t)z * plane + (int64_t)(8 * r) * p.N) : 0.f;
+    }
+    if (p.sk == 1) {
+        // output channels contiguous: store the row segments as they are
+#pragma unroll
+        for (int r = 0; r < 4; r++) {
+            const int m = m0 + threadIdx.y + 8 * r;
+            if (m < p.Mreal && n < p.N) {            // rows >= Mreal: zero padding of a lowered few-channel layer
+                const int tap = m / p.C, c = m - tap * p.C, rr = tap / p.S, s = tap - rr * p.S;
+                dw[c * p.sc + rr * p.sr + s * p.ss + n] = v[r];
+            }
+        }
+        return;
+    }
+#pragma unroll
+    for (int r = 0; r < 4; r++) tile[threadIdx.y + 8 * r][threadIdx.x] = v[r];
+    __syncthreads();
+    const int m = m0 + threadIdx.x;                   // lanes now run along the rows
+    if (m >= p.Mreal) return;
+    const int tap = m / p.C, c = m - tap * p.C, rr = tap / p.S, s = tap - rr * p.S;
+    float* d = dw + c * p.sc + rr * p.sr + s * p.ss;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const int nn = n0 + threadIdx.y + 8 * j;
+        if (nn < p.N) d[(int64_t)nn * p.sk] = tile[threadIdx.x][threadIdx.y + 8 * j];
     }
 }
 
@@ -1314,6 +1360,15 @@ static unsigned int* tc_sync_bank(cudaStream_t st)
     if (owners[dev] == TC_SYNC_BANKS) return nullptr;
     owner[dev][owners[dev]] = st;
     return base[dev] + (size_t)(owners[dev]++) * TC_SYNC_WORDS;
+}
+
+// Whole tiles against balanced ranges: balanced mode is taken when its cost estimate is below this share of the plain
+// one (B2C_TC_BALANCE overrides it, for experiments).
+static double tc_balance_threshold()
+{
+    static double v = -1.0;
+    if (v < 0.0) { const char* e = getenv("B2C_TC_BALANCE"); v = e ? atof(e) : 0.85; }
+    return v;
 }
 
 // Balanced mode scratch: 4 flags per CTA (padded to 4 KB) and one 128 x 128 float partial tile per CTA.
@@ -1493,7 +1548,7 @@ static int run_fwd(const FwdLaunch& f, const void* act, const void* w, const Pre
         // cost in k-block units: whole tiles take rounds x kblocks; balanced ranges take units / G plus the
         // hand-over of one partial tile (store, flag, load, add: about four k-blocks)
         const double plain = (double)rounds * (double)kblocks, balanced = (double)(tiles * kblocks) / G + 4.0;
-        if (!filters_ready && room && tiles * kblocks >= 4 * (int64_t)G && balanced < 0.85 * plain) sk = 1;
+        if (!filters_ready && room && tiles * kblocks >= 4 * (int64_t)G && balanced < tc_balance_threshold() * plain) sk = 1;
     }
     // The filter itself serves as the B operand when its layout allows a tensor map over it (the channel axis
     // that is contiguous decides K-major or MN-major); otherwise hi/lo copies in the GEMM layout are written first.
@@ -1770,9 +1825,7 @@ static int tc_wgrad_nhwc(const Geo& g, const void* x, const void* dy, void* dw, 
     int rc = dispatch_wgrad(pl.bn, ma, mb, mo, p, pl.splits, st);
     if (rc) return rc;
     WgradReduceParams rp{Krows, g.co, g.ci, g.kw, pl.splits, wsd.sk, wsd.sc, wsd.sr, wsd.ss, (int)g.K};
-    int64_t total = (int64_t)Krows * g.co;
-    int blocks = (int)((total + 255) / 256 < tc_sm_count() * 8 ? (total + 255) / 256 : tc_sm_count() * 8);
-    launch_pdl(tc_wgrad_reduce_kernel, blocks, 256, 0, st, rp, partial, (float*)dw, p.db_partial, (float*)db);
+    launch_pdl(tc_wgrad_reduce_kernel, dim3((g.co + 31) / 32, (Krows + 31) / 32), dim3(32, 8), 0, st, rp, partial, (float*)dw, p.db_partial, (float*)db);
     return check_launch("tc_wgrad_reduce_kernel");
 }
 
