@@ -56,6 +56,8 @@ class Conv2DGPU(LayerGPU, Conv2D):
         need = max(L.b2c_conv_workspace_bytes(ctypes.byref(self.desc), p) for p in
                    (_lib.PASS_FPROP, _lib.PASS_DGRAD, _lib.PASS_WGRAD))
         wsp.require(need)
+        wsp.require_side(L.b2c_conv_workspace_bytes(ctypes.byref(self.desc), _lib.PASS_WGRAD))
+        self._wgrad_done = None
         # can this layer's forward pass leave the batch sums of its output for a following batch norm?
         self.stats_bytes = int(L.b2c_conv_stats_bytes(ctypes.byref(self.desc)))
 
@@ -102,14 +104,36 @@ class Conv2DGPU(LayerGPU, Conv2D):
 
     def backward(self, dy):
         L = _lib.lib()
-        self._timed("wgrad", lambda: L.b2c_conv_wgrad(
-            ctypes.byref(self.desc), self.x.ptr, dy.ptr, self.dw.ptr, self.db.ptr if self.use_bias else None,
-            wsp.ptr(), wsp.size(), self.model.stream_handle))
+        m = self.model
+        side = m.side_stream_for_wgrad()
+        if side is None:
+            self._timed("wgrad", lambda: L.b2c_conv_wgrad(
+                ctypes.byref(self.desc), self.x.ptr, dy.ptr, self.dw.ptr, self.db.ptr if self.use_bias else None,
+                wsp.ptr(), wsp.size(), m.stream_handle))
+            if self.need_dx:
+                self._timed("dgrad", lambda: L.b2c_conv_dgrad(
+                    ctypes.byref(self.desc), dy.ptr, self.weights.ptr, self.dx.ptr, wsp.ptr(), wsp.size(), m.stream_handle))
+                return self.dx
+            return None
+        # The weight gradient only has to be there when the gradients are exchanged or applied, so it runs on a side
+        # stream next to what follows on the main stream.  The input gradient is issued first: both kernels want every
+        # SM, the one launched first gets them, and the input gradient is what the main stream's next kernels (the
+        # HBM-bound backward of the layers before this one) wait for -- those then run alongside the weight gradient.
+        # The side stream waits for dy; the model joins it before the gradients are used.
+        import torch
+        if self._wgrad_done is None:
+            self._dy_ready, self._wgrad_done = torch.cuda.Event(), torch.cuda.Event()
+        self._dy_ready.record()
         if self.need_dx:
-            self._timed("dgrad", lambda: L.b2c_conv_dgrad(
-                ctypes.byref(self.desc), dy.ptr, self.weights.ptr, self.dx.ptr, wsp.ptr(), wsp.size(),
-                self.model.stream_handle))
-            return self.dx
+            _lib.check(L.b2c_conv_dgrad(ctypes.byref(self.desc), dy.ptr, self.weights.ptr, self.dx.ptr, wsp.ptr(), wsp.size(),
+                                        m.stream_handle))
+        side.wait_event(self._dy_ready)
+        sw = wsp.side()
+        _lib.check(L.b2c_conv_wgrad(ctypes.byref(self.desc), self.x.ptr, dy.ptr, self.dw.ptr,
+                                    self.db.ptr if self.use_bias else None, sw.data_ptr(), sw.numel(), side.cuda_stream))
+        self._wgrad_done.record(side)
+        m.note_side_work(self._wgrad_done)
+        return self.dx if self.need_dx else None
 
 
 class _FusedConvInference(Conv2DGPU):

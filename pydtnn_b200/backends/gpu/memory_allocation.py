@@ -25,6 +25,24 @@ def size():
     return _buf.numel() if _buf is not None else 0
 
 
+_side = None
+
+
+def require_side(nbytes, device=None):
+    """A second workspace of the same kind for calls issued on the model's side stream (weight gradients that run
+    next to the main stream's kernels must not share scratch with them)."""
+    global _side
+    nbytes = int(nbytes)
+    if _side is None or _side.numel() < nbytes:
+        device = device or (_side.device if _side is not None else torch.device("cuda", torch.cuda.current_device()))
+        _side = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+    return _side
+
+
+def side():
+    return _side
+
+
 _red = None
 
 

@@ -62,6 +62,7 @@ class GradientBucketer:
         self._done = []
         self._built = False
         self.launch_order = []     # bucket indices in the order their all-reduce was issued (for tests)
+        self.before_launch = None  # called before an all-reduce is issued (the model joins its side stream there)
 
     def build(self):
         self.buckets, self.bucket_of = [], {}
@@ -130,6 +131,8 @@ class GradientBucketer:
             if idx in pend:
                 pend.discard(idx)
                 if not pend and self._works[b] is None:
+                    if self.before_launch is not None:
+                        self.before_launch()
                     try:
                         self._works[b] = dist.all_reduce(self._view(b), op=dist.ReduceOp.SUM, group=self.group,
                                                          async_op=True)

@@ -73,6 +73,7 @@ class Model:
         self.mode = UNSPECIFIED_MODE
         self.arena = ParamArena(self.dtype, self.device)
         self.bucketer = GradientBucketer(self.arena, self.comm, bucket_elems)
+        self.bucketer.before_launch = self.join_side_stream      # weight gradients on the side stream belong to the bucket
         self.y_batch = None
         self.loss_func = None
         self._train_fused = False
@@ -83,6 +84,9 @@ class Model:
         self.fast_update = True
         self.fuse_add_relu = True
         self.fuse_conv_bn_stats = True      # training: a Conv2D that feeds a BatchNormalization also sums its output per channel
+        self.overlap_wgrad = True           # training: weight gradients of the convolutions run on a side stream
+        self._side_stream = None
+        self._side_pending = None           # last event recorded on the side stream that the main stream has not waited for
         if model_name:
             from . import nets
             getattr(nets, f"create_{model_name}")(self)
@@ -91,6 +95,28 @@ class Model:
     @property
     def stream_handle(self):
         return torch.cuda.current_stream(self.device).cuda_stream
+
+    # -- side stream of the weight gradients ---------------------------------------------------------------
+    def side_stream_for_wgrad(self):
+        """The stream convolution weight gradients are issued on, or None when they stay on the main stream: overlap
+        switched off, per-pass timing (``conv_profile``) or per-operation tracing in progress (both bracket single
+        passes with events on the main stream)."""
+        if not self.overlap_wgrad or self.mode != TRAIN_MODE or getattr(self, "conv_profile", None) is not None \
+                or (self.tracer.enabled and self.tracer.ops):
+            return None
+        if self._side_stream is None:
+            self._side_stream = torch.cuda.Stream(device=self.device)
+        return self._side_stream
+
+    def note_side_work(self, event):
+        self._side_pending = event
+
+    def join_side_stream(self):
+        """Make the main stream wait for everything issued on the side stream so far (the side stream is in order, so
+        its latest event covers the earlier ones).  Called before gradients are exchanged, applied or read."""
+        if self._side_pending is not None:
+            torch.cuda.current_stream(self.device).wait_event(self._side_pending)
+            self._side_pending = None
 
     def add(self, layer):
         layer.set_model(self)
@@ -228,10 +254,12 @@ class Model:
             for layer in reversed(self.layers[1:]):
                 with tr.region(layer, tracer.PYDTNN_MDL_ALLREDUCE_DW):
                     layer.reduce_weights_sync()
+        self.join_side_stream()            # every gradient is ordered before whatever the caller does next on this stream
         return loss
 
     def apply_update(self, optimizer):
         tr = self.tracer
+        self.join_side_stream()
         if self.comm is not None:
             self.bucketer.wait_all()
         if self.fast_update and hasattr(optimizer, "update_arena"):
@@ -356,6 +384,10 @@ class Model:
         return missing
 
     def synchronize(self):
+        self.join_side_stream()
+        self._synchronize()
+
+    def _synchronize(self):
         """Wait for the device and raise ``B2CError`` (device timeout) if a bounded in-kernel wait ran out since the
         last check: the kernel then returned with partial results, which must not be trained on silently."""
         torch.cuda.synchronize(self.device)
