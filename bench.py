@@ -450,7 +450,7 @@ def run_ours(args):
         line["dp_check"] = dp_rec
     if world == 1 and not args.no_cpu_baseline:
         threads = _cpu_threads()
-        cpu_batch = {"resnet50": 8, "vgg16bn": 4, "alexnet": 16}[args.workload]
+        cpu_batch = {"resnet50": 8, "vgg16bn": 2, "alexnet": 16}[args.workload]
         ips, kind, times = cpu_images_per_s(args.workload, cpu_batch, 1, 0)
         what = "train step" if train else "forward pass"
         line["cpu_baseline"] = {"value": ips, "unit": UNIT, "cores": threads, "kind": kind,
