@@ -1135,6 +1135,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 // caller's filter layout.
 struct WgradReduceParams { int M, N, C, S, splits; int64_t sk, sc, sr, ss; int Mreal; };
 
+template <int ROWS>
 __global__ void __launch_bounds__(256) tc_wgrad_reduce_kernel(WgradReduceParams p, const float* __restrict__ partial, float* __restrict__ dw,
                                                               const float* __restrict__ db_partial, float* __restrict__ db)
 {
@@ -1148,40 +1149,45 @@ __global__ void __launch_bounds__(256) tc_wgrad_reduce_kernel(WgradReduceParams 
             db[n] = v;
         }
     }
-    // A block owns 32 rows (tap, ci) x 32 output channels.  Thread (x, y) adds, in split order, the partials of column
-    // n0 + x for rows y, y + 8, y + 16, y + 24 (loads of a warp cover 128 contiguous bytes; the four rows and four
-    // splits at a time are independent loads).  The sums then leave along whichever axis is contiguous in the caller's
-    // filter layout: output channels as they are, (tap, ci) rows through a transposing shared-memory tile.
-    __shared__ float tile[32][33];
-    const int m0 = blockIdx.y * 32, n0 = blockIdx.x * 32;
+    // A block owns 8 * ROWS rows (tap, ci) x 32 output channels.  Thread (x, y) adds, in split order, the partials of
+    // column n0 + x for rows y, y + 8, ... (loads of a warp cover 128 contiguous bytes; ROWS rows x 16 / ROWS splits
+    // at a time are independent loads).  ROWS = 4 for large filters; ROWS = 1 makes four times the blocks when the
+    // filter is small and the splits are many (the sum over the splits is the long loop then).  The sums leave along
+    // whichever axis is contiguous in the caller's filter layout: output channels as they are, (tap, ci) rows through
+    // a transposing shared-memory tile.
+    constexpr int TR = 8 * ROWS, U = 16 / ROWS;
+    __shared__ float tile[TR][33];
+    const int m0 = blockIdx.y * TR, n0 = blockIdx.x * 32;
     const int64_t plane = (int64_t)p.M * p.N;
     const int n = n0 + threadIdx.x;
-    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    float v[ROWS];
+#pragma unroll
+    for (int r = 0; r < ROWS; r++) v[r] = 0.f;
     if (n < p.N) {
         const float* src = partial + (int64_t)(m0 + threadIdx.y) * p.N + n;
-        bool in[4];
+        bool in[ROWS];
 #pragma unroll
-        for (int r = 0; r < 4; r++) in[r] = m0 + threadIdx.y + 8 * r < p.M;
+        for (int r = 0; r < ROWS; r++) in[r] = m0 + threadIdx.y + 8 * r < p.M;
         int z = 0;
-        for (; z + 4 <= p.splits; z += 4) {
-            float q[4][4];
+        for (; z + U <= p.splits; z += U) {
+            float q[U][ROWS];
 #pragma unroll
-            for (int u = 0; u < 4; u++)
+            for (int u = 0; u < U; u++)
 #pragma unroll
-                for (int r = 0; r < 4; r++) q[u][r] = in[r] ? __ldcg(src + (int64_t)(z + u) * plane + (int64_t)(8 * r) * p.N) : 0.f;
+                for (int r = 0; r < ROWS; r++) q[u][r] = in[r] ? __ldcg(src + (int64_t)(z + u) * plane + (int64_t)(8 * r) * p.N) : 0.f;
 #pragma unroll
-            for (int u = 0; u < 4; u++)
+            for (int u = 0; u < U; u++)
 #pragma unroll
-                for (int r = 0; r < 4; r++) v[r] += q[u][r];
+                for (int r = 0; r < ROWS; r++) v[r] += q[u][r];
         }
         for (; z < p.splits; z++)
 #pragma unroll
-            for (int r = 0; r < 4; r++) v[r] += in[r] ? __ldcg(src + (int64_t)z * plane + (int64_t)(8 * r) * p.N) : 0.f;
+            for (int r = 0; r < ROWS; r++) v[r] += in[r] ? __ldcg(src + (int64_t)z * plane + (int64_t)(8 * r) * p.N) : 0.f;
     }
     if (p.sk == 1) {
         // output channels contiguous: store the row segments as they are
 #pragma unroll
-        for (int r = 0; r < 4; r++) {
+        for (int r = 0; r < ROWS; r++) {
             const int m = m0 + threadIdx.y + 8 * r;
             if (m < p.Mreal && n < p.N) {            // rows >= Mreal: zero padding of a lowered few-channel layer
                 const int tap = m / p.C, c = m - tap * p.C, rr = tap / p.S, s = tap - rr * p.S;
@@ -1191,10 +1197,11 @@ __global__ void __launch_bounds__(256) tc_wgrad_reduce_kernel(WgradReduceParams 
         return;
     }
 #pragma unroll
-    for (int r = 0; r < 4; r++) tile[threadIdx.y + 8 * r][threadIdx.x] = v[r];
+    for (int r = 0; r < ROWS; r++) tile[threadIdx.y + 8 * r][threadIdx.x] = v[r];
     __syncthreads();
-    const int m = m0 + threadIdx.x;                   // lanes now run along the rows
-    if (m >= p.Mreal) return;
+    // lanes now run along the rows: thread (x, y) with x < TR writes row m0 + x for columns y, y + 8, y + 16, y + 24
+    const int m = m0 + threadIdx.x;
+    if (threadIdx.x >= TR || m >= p.Mreal) return;
     const int tap = m / p.C, c = m - tap * p.C, rr = tap / p.S, s = tap - rr * p.S;
     float* d = dw + c * p.sc + rr * p.sr + s * p.ss;
 #pragma unroll
@@ -1202,6 +1209,53 @@ __global__ void __launch_bounds__(256) tc_wgrad_reduce_kernel(WgradReduceParams 
         const int nn = n0 + threadIdx.y + 8 * j;
         if (nn < p.N) d[(int64_t)nn * p.sk] = tile[threadIdx.x][threadIdx.y + 8 * j];
     }
+}
+
+// The same sum for small filters cut into very many splits (a 64 x 64 filter summed over 148 pixel ranges): a block
+// owns one row x 32 output channels and its 8 thread rows share the splits (thread row y adds splits y, y + 8, ... in
+// order, then the 8 partial sums are added in thread-row order: a fixed order again).
+__global__ void __launch_bounds__(256) tc_wgrad_reduce_deep_kernel(WgradReduceParams p, const float* __restrict__ partial, float* __restrict__ dw,
+                                                                   const float* __restrict__ db_partial, float* __restrict__ db)
+{
+    pdl_prologue();
+    __shared__ float part[8][33];
+    const int n = blockIdx.x * 32 + threadIdx.x, m = blockIdx.y;
+    if (db && blockIdx.y == 0) {
+        // bias gradient: [splits * 4] row sums per channel, shared among the thread rows the same way
+        float v = 0.f;
+        if (n < p.N) for (int i = threadIdx.y; i < p.splits * 4; i += 8) v += __ldcg(db_partial + (size_t)i * p.N + n);
+        part[threadIdx.y][threadIdx.x] = v;
+        __syncthreads();
+        if (threadIdx.y == 0 && n < p.N) {
+            float t = 0.f;
+#pragma unroll
+            for (int y = 0; y < 8; y++) t += part[y][threadIdx.x];
+            db[n] = t;
+        }
+        __syncthreads();
+    }
+    const int64_t plane = (int64_t)p.M * p.N;
+    float v = 0.f;
+    if (n < p.N) {
+        const float* src = partial + (int64_t)m * p.N + n;
+        int z = threadIdx.y;
+        for (; z + 56 < p.splits; z += 64) {
+            float q[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) q[u] = __ldcg(src + (int64_t)(z + 8 * u) * plane);
+#pragma unroll
+            for (int u = 0; u < 8; u++) v += q[u];
+        }
+        for (; z < p.splits; z += 8) v += __ldcg(src + (int64_t)z * plane);
+    }
+    part[threadIdx.y][threadIdx.x] = v;
+    __syncthreads();
+    if (threadIdx.y != 0 || n >= p.N || m >= p.Mreal) return;
+    float t = 0.f;
+#pragma unroll
+    for (int y = 0; y < 8; y++) t += part[y][threadIdx.x];
+    const int tap = m / p.C, c = m - tap * p.C, rr = tap / p.S, s = tap - rr * p.S;
+    dw[(int64_t)n * p.sk + c * p.sc + rr * p.sr + s * p.ss] = t;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1825,7 +1879,12 @@ static int tc_wgrad_nhwc(const Geo& g, const void* x, const void* dy, void* dw, 
     int rc = dispatch_wgrad(pl.bn, ma, mb, mo, p, pl.splits, st);
     if (rc) return rc;
     WgradReduceParams rp{Krows, g.co, g.ci, g.kw, pl.splits, wsd.sk, wsd.sc, wsd.sr, wsd.ss, (int)g.K};
-    launch_pdl(tc_wgrad_reduce_kernel, dim3((g.co + 31) / 32, (Krows + 31) / 32), dim3(32, 8), 0, st, rp, partial, (float*)dw, p.db_partial, (float*)db);
+    if ((int64_t)((g.co + 31) / 32) * ((Krows + 31) / 32) >= 2 * (int64_t)tc_sm_count())
+        launch_pdl(tc_wgrad_reduce_kernel<4>, dim3((g.co + 31) / 32, (Krows + 31) / 32), dim3(32, 8), 0, st, rp, partial, (float*)dw, p.db_partial, (float*)db);
+    else if ((int64_t)((g.co + 31) / 32) * ((Krows + 7) / 8) >= 2 * (int64_t)tc_sm_count() || pl.splits < 16)
+        launch_pdl(tc_wgrad_reduce_kernel<1>, dim3((g.co + 31) / 32, (Krows + 7) / 8), dim3(32, 8), 0, st, rp, partial, (float*)dw, p.db_partial, (float*)db);
+    else
+        launch_pdl(tc_wgrad_reduce_deep_kernel, dim3((g.co + 31) / 32, Krows), dim3(32, 8), 0, st, rp, partial, (float*)dw, p.db_partial, (float*)db);
     return check_launch("tc_wgrad_reduce_kernel");
 }
 
