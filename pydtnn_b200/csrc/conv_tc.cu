@@ -432,6 +432,11 @@ struct TcParams {
     float* db_partial;         // WGRAD: per-(split, transform warp) channel sums of dy, [splits][4][N], or null
     int tma_store;             // output rows are dense [M][N] (or [split][M][N]): store tiles through the output tensor map
     int sk_selfclean;          // balanced mode: the owner returns a consumed flag to zero (flags in the library's bank)
+    // FWD writing one parity class of a stride-2 data gradient whose other three classes are zeros (a 1x1 filter): with
+    // zfill set, every output row also stores zeros at the pixel to its right, below it and diagonally below (offsets
+    // z_w, z_h, z_w + z_h elements) where those pixels exist (2 q + 1 < z_W, 2 p + 1 < z_H), so dx needs no clearing pass.
+    int zfill, z_W, z_H;
+    int64_t z_w, z_h;
     // FWD over several pixel classes in one launch (the parity classes of a strided data gradient): the tile list is
     // the concatenation of the classes' tile lists, class c owning tiles [cls_tile0[c], cls_tile0[c + 1]).  A class has
     // its own pixel grid, window corner, tap set, k-block count, output offset and activation tensor map; channel
@@ -1083,12 +1088,14 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             // that every store instruction writes whole 128-byte row segments (8 lanes per row, 4 rows).
             const int m = m0 + quad * 32 + lane;
             int64_t my_off = -1;
+            int zmask = 0;                       // zfill: which of the row's three neighbour pixels exist
             if (m < tg.M) {
                 if (MODE == TCM_FWD) {
                     const int img = m / (tg.P * tg.Q);
                     const int rem = m - img * (tg.P * tg.Q);
                     const int pi = rem / tg.Q, qi = rem - pi * tg.Q;
                     my_off = tg.out_off + img * p.o_sn + pi * p.o_sh + qi * p.o_sw;
+                    if (p.zfill) zmask = (2 * qi + 1 < p.z_W ? 1 : 0) | (2 * pi + 1 < p.z_H ? 2 : 0);
                 } else {
                     my_off = ((int64_t)z * p.M + m) * p.N;
                 }
@@ -1113,9 +1120,17 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         for (int i = 0; i < 8; i++) {
                             const int r = i * 4 + (lane >> 3), c4 = (lane & 7) * 4;
                             const int64_t off_r = __shfl_sync(0xffffffffu, my_off, r);
+                            const int zm = __shfl_sync(0xffffffffu, zmask, r);
                             const int n = n0 + cc * 32 + c4;
-                            if (off_r >= 0 && n < p.N)
+                            if (off_r >= 0 && n < p.N) {
                                 *reinterpret_cast<float4*>(p.out + off_r + n) = *reinterpret_cast<const float4*>(stage + r * 36 + c4);
+                                if (MODE == TCM_FWD && zm) {
+                                    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+                                    if (zm & 1) *reinterpret_cast<float4*>(p.out + off_r + p.z_w + n) = zero;
+                                    if (zm & 2) *reinterpret_cast<float4*>(p.out + off_r + p.z_h + n) = zero;
+                                    if (zm == 3) *reinterpret_cast<float4*>(p.out + off_r + p.z_h + p.z_w + n) = zero;
+                                }
+                            }
                         }
                         __syncwarp();
                     }
@@ -1567,6 +1582,8 @@ static bool make_map_out(CUtensorMap* map, const void* base, uint64_t planes, ui
 // filter kh x kw (dilation dil); output rows (n, i, j) over P x Q written at out + n*o_sn + i*o_sh + j*o_sw.
 // Where a forward pass leaves the batch statistics of its output (see TcParams::stats), or null.
 struct StatsOut { float* sums; };
+// Stride-2 data gradient of a 1x1 filter: the launch writes class (0, 0) and the zeros of the other three (TcParams::zfill).
+struct ZeroFill { int W, H; int64_t off_w, off_h; };
 
 struct FwdLaunch {
     int n, ah, aw, C, P, Q, N, kh, kw, low_h, low_w, cnt_h, cnt_w, str_h, str_w, dil_h, dil_w;
@@ -1575,7 +1592,7 @@ struct FwdLaunch {
 
 static int run_fwd(const FwdLaunch& f, const void* act, const void* w, const PrepParams& pp, const void* bias,
                    const b2c_bn_params* bn, int relu, float* out, void* ws, size_t ws_bytes, cudaStream_t st,
-                   bool filters_ready = false, const StatsOut* stats = nullptr)
+                   bool filters_ready = false, const StatsOut* stats = nullptr, const ZeroFill* zf = nullptr)
 {
     if (!load_driver_entry_points()) return B2C_ERR_UNSUPPORTED;
     const int64_t K = (int64_t)f.kh * f.kw * f.C;
@@ -1651,6 +1668,10 @@ static int run_fwd(const FwdLaunch& f, const void* act, const void* w, const Pre
     CUtensorMap mo = mbh;
     p.tma_store = 0;
     if (dense && make_map_out(&mo, out, 0, (uint64_t)p.M, (uint64_t)f.N)) p.tma_store = 1;
+    if (zf) {
+        if (p.tma_store || (f.N % 4) || ((zf->off_w | zf->off_h) & 3)) return B2C_ERR_UNSUPPORTED;
+        p.zfill = 1; p.z_W = zf->W; p.z_H = zf->H; p.z_w = zf->off_w; p.z_h = zf->off_h;
+    }
     if (stats) {
         // the statistics are taken from the staging slabs of the TMA-store epilogue
         if (!p.tma_store) return B2C_ERR_UNSUPPORTED;
@@ -1813,11 +1834,27 @@ static int tc_dgrad_nhwc(const Geo& g, const void* dy, const void* w, void* dx, 
         if (rc != 1) return rc;            // 1: not applicable, one launch per class below
     }
     bool any_empty = false;
+    int live = 0;
     for (int a = 0; a < g.vstr; a++)
         for (int b = 0; b < g.hstr; b++) {
             AxisClass ca = axis_class(a, g.vstr, g.vpad, g.kh, g.h), cb = axis_class(b, g.hstr, g.hpad, g.kw, g.w);
             if ((ca.cnt == 0 || cb.cnt == 0) && ca.out_cnt > 0 && cb.out_cnt > 0) any_empty = true;
+            if (ca.cnt > 0 && cb.cnt > 0 && ca.out_cnt > 0 && cb.out_cnt > 0) live++;
         }
+    {
+        // 2 x 2 stride, only class (0, 0) reached by a tap (a 1x1 filter without padding): the class's launch writes the
+        // other classes' zeros next to its own rows, no clearing pass over dx
+        AxisClass ca = axis_class(0, g.vstr, g.vpad, g.kh, g.h), cb = axis_class(0, g.hstr, g.hpad, g.kw, g.w);
+        if (g.vstr == 2 && g.hstr == 2 && live == 1 && ca.cnt > 0 && cb.cnt > 0 && g.ci % 4 == 0 && ((uintptr_t)dx & 15) == 0) {
+            PrepParams pp{g.ci, g.co, ca.cnt, cb.cnt, wsd.sc, wsd.sk, wsd.sr, wsd.ss, ca.r0, -g.vstr, cb.r0, -g.hstr, g.kh, g.kw};
+            FwdLaunch f{g.n, g.ho, g.wo, g.co, ca.out_cnt, cb.out_cnt, g.ci, ca.cnt, cb.cnt, ca.dmin, cb.dmin,
+                        ca.out_cnt, cb.out_cnt, 1, 1, 1, 1,
+                        (int64_t)g.h * g.w * g.ci, (int64_t)g.vstr * g.w * g.ci, (int64_t)g.hstr * g.ci};
+            ZeroFill zf{g.w, g.h, (int64_t)g.ci, (int64_t)g.w * g.ci};
+            int rc = run_fwd(f, dy, w, pp, nullptr, nullptr, 0, (float*)dx, ws, ws_bytes, st, false, nullptr, &zf);
+            if (rc != B2C_ERR_UNSUPPORTED) return rc;
+        }
+    }
     if (any_empty) {
         cudaError_t e = cudaMemsetAsync(dx, 0, (size_t)g.n * g.h * g.w * g.ci * sizeof(float), st);
         if (e != cudaSuccess) { set_cuda_error(e, "cudaMemsetAsync(dx)"); return B2C_ERR_CUDA; }
