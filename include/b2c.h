@@ -122,6 +122,17 @@ int b2c_conv_dgrad(const b2c_conv_desc *desc, const void *dy, const void *w, voi
 int b2c_conv_wgrad(const b2c_conv_desc *desc, const void *x, const void *dy, void *dw, void *db,
                    void *workspace, size_t workspace_bytes, void *stream);
 
+/* The weight gradient for a caller that kept the forward pass's lowered input, as the reference's CPU layer keeps
+ * `x_rows` from forward for backward (pydtnn/backends/cpu/layers/conv_2d_cpu.py:191-192, 373).  Few-channel NHWC layers
+ * (the network stems: ci not a multiple of 32) write the im2row matrix of x at the start of the workspace in
+ * b2c_conv_fprop and would write it again here; b2c_conv_wgrad_lowered skips that when the caller guarantees that
+ * `workspace` is the very buffer the layer's last b2c_conv_fprop (same desc, same x) ran with and nothing has written
+ * to it since -- in practice a workspace the layer owns.  b2c_conv_keeps_lowered_input(desc) says whether the layer
+ * is of that kind (1) or not (0; the call then returns B2C_ERR_UNSUPPORTED and b2c_conv_wgrad is the one to use). */
+int b2c_conv_keeps_lowered_input(const b2c_conv_desc *desc);
+int b2c_conv_wgrad_lowered(const b2c_conv_desc *desc, const void *x, const void *dy, void *dw, void *db,
+                           void *workspace, size_t workspace_bytes, void *stream);
+
 /* The integer index map of the lowering, written to DEVICE memory as int64:
  *   NHWC: map[M][K], NCHW: map[K][M]; entry = flat offset into x or -1 at a padding tap,
  * numbered exactly as pydtnn/cython_modules/im2row_nhwc_cython.pyx:85-97 and

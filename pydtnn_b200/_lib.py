@@ -53,6 +53,9 @@ PROTOTYPES = {
     "b2c_conv_dgrad": (c_int, [POINTER(ConvDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
     "b2c_conv_wgrad": (c_int, [POINTER(ConvDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t,
                                c_void_p]),
+    "b2c_conv_keeps_lowered_input": (c_int, [POINTER(ConvDesc)]),
+    "b2c_conv_wgrad_lowered": (c_int, [POINTER(ConvDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t,
+                                       c_void_p]),
     "b2c_conv_index_map": (c_int, [POINTER(ConvDesc), c_void_p, c_void_p]),
     "b2c_fc_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
     "b2c_fc_forward": (c_int, [c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

@@ -58,6 +58,13 @@ class Conv2DGPU(LayerGPU, Conv2D):
         wsp.require(need)
         wsp.require_side(L.b2c_conv_workspace_bytes(ctypes.byref(self.desc), _lib.PASS_WGRAD))
         self._wgrad_done = None
+        # A few-channel layer (the stem) lowers its input into the workspace in the forward pass; with a workspace of
+        # its own the matrix is still there for the weight gradient (the reference's CPU layer keeps x_rows the same way).
+        self._own_ws = None
+        self._lowered_valid = False
+        if L.b2c_conv_keeps_lowered_input(ctypes.byref(self.desc)):
+            import torch
+            self._own_ws = torch.empty(int(need), dtype=torch.uint8, device=self.y.ary.t.device)
         # can this layer's forward pass leave the batch sums of its output for a following batch norm?
         self.stats_bytes = int(L.b2c_conv_stats_bytes(ctypes.byref(self.desc)))
 
@@ -89,27 +96,39 @@ class Conv2DGPU(LayerGPU, Conv2D):
         L = _lib.lib()
         self.x = x          # backward reads the tensor this call saw (a fused predecessor may hand over its own buffer)
         bn = self.stats_for_bn
+        ws_ptr, ws_size = (self._own_ws.data_ptr(), self._own_ws.numel()) if self._own_ws is not None else (wsp.ptr(), wsp.size())
+        self._lowered_valid = self._own_ws is not None and self.model.mode == TRAIN_MODE
         if bn is not None and self.model.mode == TRAIN_MODE:
             # training step, a batch norm follows: the same pass also sums y and y^2 per channel while the tiles leave
             st = wsp.conv_stats()
             self._timed("fprop", lambda: L.b2c_conv_fprop_stats(
                 ctypes.byref(self.desc), x.ptr, self.weights.ptr, self.biases.ptr if self.use_bias else None,
-                self.y.ptr, st.data_ptr(), self.stats_bytes, wsp.ptr(), wsp.size(), self.model.stream_handle))
+                self.y.ptr, st.data_ptr(), self.stats_bytes, ws_ptr, ws_size, self.model.stream_handle))
             bn.prestats = (st, self.stats_bytes)
             return self.y
         self._timed("fprop", lambda: L.b2c_conv_fprop(
             ctypes.byref(self.desc), x.ptr, self.weights.ptr, self.biases.ptr if self.use_bias else None, None, 0,
-            self.y.ptr, wsp.ptr(), wsp.size(), self.model.stream_handle))
+            self.y.ptr, ws_ptr, ws_size, self.model.stream_handle))
         return self.y
+
+    def _wgrad_call(self, dy, ws_ptr, ws_size, stream):
+        """The weight-gradient call on ``stream``; a layer that still holds its forward pass's lowered input in its own
+        workspace uses that instead of lowering x again."""
+        L = _lib.lib()
+        db = self.db.ptr if self.use_bias else None
+        if self._lowered_valid:
+            self._lowered_valid = False
+            own = self._own_ws
+            return lambda: L.b2c_conv_wgrad_lowered(ctypes.byref(self.desc), self.x.ptr, dy.ptr, self.dw.ptr, db, own.data_ptr(),
+                                                    own.numel(), stream)
+        return lambda: L.b2c_conv_wgrad(ctypes.byref(self.desc), self.x.ptr, dy.ptr, self.dw.ptr, db, ws_ptr, ws_size, stream)
 
     def backward(self, dy):
         L = _lib.lib()
         m = self.model
         side = m.side_stream_for_wgrad()
         if side is None:
-            self._timed("wgrad", lambda: L.b2c_conv_wgrad(
-                ctypes.byref(self.desc), self.x.ptr, dy.ptr, self.dw.ptr, self.db.ptr if self.use_bias else None,
-                wsp.ptr(), wsp.size(), m.stream_handle))
+            self._timed("wgrad", self._wgrad_call(dy, wsp.ptr(), wsp.size(), m.stream_handle))
             if self.need_dx:
                 self._timed("dgrad", lambda: L.b2c_conv_dgrad(
                     ctypes.byref(self.desc), dy.ptr, self.weights.ptr, self.dx.ptr, wsp.ptr(), wsp.size(), m.stream_handle))
@@ -129,8 +148,7 @@ class Conv2DGPU(LayerGPU, Conv2D):
                                         m.stream_handle))
         side.wait_event(self._dy_ready)
         sw = wsp.side()
-        _lib.check(L.b2c_conv_wgrad(ctypes.byref(self.desc), self.x.ptr, dy.ptr, self.dw.ptr,
-                                    self.db.ptr if self.use_bias else None, sw.data_ptr(), sw.numel(), side.cuda_stream))
+        _lib.check(self._wgrad_call(dy, sw.data_ptr(), sw.numel(), side.cuda_stream)())
         self._wgrad_done.record(side)
         m.note_side_work(self._wgrad_done)
         return self.dx if self.need_dx else None

@@ -124,6 +124,22 @@ extern "C" int b2c_conv_dgrad(const b2c_conv_desc* desc, const void* dy, const v
     return fma_dgrad(g, dy, w, dx, ws, ws_bytes, (cudaStream_t)stream);
 }
 
+extern "C" int b2c_conv_keeps_lowered_input(const b2c_conv_desc* desc) {
+    Geo g; if (make_geo(desc, g)) return 0;
+    int e; if (pick_engine(g, B2C_PASS_WGRAD, e) || e != B2C_ENGINE_TENSOR) return 0;
+    if (pick_engine(g, B2C_PASS_FPROP, e) || e != B2C_ENGINE_TENSOR) return 0;
+    return tc_keeps_lowered(g) ? 1 : 0;
+}
+
+extern "C" int b2c_conv_wgrad_lowered(const b2c_conv_desc* desc, const void* x, const void* dy, void* dw, void* db,
+                                      void* ws, size_t ws_bytes, void* stream) {
+    Geo g; int rc = make_geo(desc, g); if (rc) return rc;
+    if (!x || !dy || !dw) return B2C_ERR_NULL_POINTER;
+    int e; rc = pick_engine(g, B2C_PASS_WGRAD, e); if (rc) return rc;
+    if (e != B2C_ENGINE_TENSOR) return B2C_ERR_UNSUPPORTED;
+    return tc_wgrad_lowered(g, x, dy, dw, db, ws, ws_bytes, (cudaStream_t)stream);
+}
+
 extern "C" int b2c_conv_wgrad(const b2c_conv_desc* desc, const void* x, const void* dy, void* dw, void* db,
                               void* ws, size_t ws_bytes, void* stream) {
     Geo g; int rc = make_geo(desc, g); if (rc) return rc;

@@ -116,6 +116,8 @@ int tc_dgrad(const Geo& g, const void* dy, const void* w, void* dx, void* ws, si
 int tc_wgrad(const Geo& g, const void* x, const void* dy, void* dw, void* db, void* ws, size_t ws_bytes,
              cudaStream_t st);
 int tc_read_status(int* out);
+bool tc_keeps_lowered(const Geo& g);
+int tc_wgrad_lowered(const Geo& g, const void* x, const void* dy, void* dw, void* db, void* ws, size_t ws_bytes, cudaStream_t st);
 size_t tc_stats_bytes(const Geo& g);
 int tc_fprop_stats(const Geo& g, const void* x, const void* w, const void* bias, void* y, void* stats, size_t stats_bytes,
                    void* ws, size_t ws_bytes, cudaStream_t st);

@@ -1874,7 +1874,8 @@ static int tc_dgrad_nhwc(const Geo& g, const void* dy, const void* w, void* dx, 
     return B2C_OK;
 }
 
-static int tc_wgrad_nhwc(const Geo& g, const void* x, const void* dy, void* dw, void* db, void* ws, size_t ws_bytes, cudaStream_t st)
+static int tc_wgrad_nhwc(const Geo& g, const void* x, const void* dy, void* dw, void* db, void* ws, size_t ws_bytes, cudaStream_t st,
+                         bool lowered_in_ws = false)
 {
     if (!load_driver_entry_points()) return B2C_ERR_UNSUPPORTED;
     const bool low = g.ci % 32 != 0;
@@ -1892,8 +1893,10 @@ static int tc_wgrad_nhwc(const Geo& g, const void* x, const void* dy, void* dw, 
     if (low) {
         // few-channel layer: gradient of the 1x1 convolution over the written-out im2row matrix
         float* rows = (float*)base;
-        int rc = launch_lower(g, x, rows, st);
-        if (rc) return rc;
+        if (!lowered_in_ws) {               // else: the forward pass of this layer left the matrix here (same offset)
+            int rc = launch_lower(g, x, rows, st);
+            if (rc) return rc;
+        }
         if (!make_map_im2col(&ma, rows, g.n, g.ho, g.wo, Krows, 0, 0, g.ho, g.wo, 1, 1, 32, CU_TENSOR_MAP_SWIZZLE_NONE))
             return B2C_ERR_UNSUPPORTED;
         p.C = Krows; p.cblocks = Krows / 32; p.S = 1;
@@ -2073,6 +2076,16 @@ int tc_dgrad(const Geo& g, const void* dy, const void* w, void* dx, void* ws, si
     rc = tc_dgrad_nhwc(as_nhwc(g), t.b, w, t.a, t.inner, t.inner_bytes, st);
     if (rc) return rc;
     return transpose_inner(t.a, dx, g.n, g.h * g.w, g.ci, st);
+}
+
+// Few-channel NHWC layers write the im2row matrix of x at the start of the workspace in their forward pass and again
+// in their weight gradient.  A caller that gives the layer a workspace of its own can say that the forward pass's
+// matrix is still there.
+bool tc_keeps_lowered(const Geo& g) { return g.layout == B2C_LAYOUT_NHWC && g.ci % 32 != 0 && tc_supported_nhwc(g, B2C_PASS_WGRAD) && tc_supported_nhwc(g, B2C_PASS_FPROP); }
+int tc_wgrad_lowered(const Geo& g, const void* x, const void* dy, void* dw, void* db, void* ws, size_t ws_bytes, cudaStream_t st)
+{
+    if (!tc_keeps_lowered(g)) return B2C_ERR_UNSUPPORTED;
+    return tc_wgrad_nhwc(g, x, dy, dw, db, ws, ws_bytes, st, true);
 }
 
 int tc_wgrad(const Geo& g, const void* x, const void* dy, void* dw, void* db, void* ws, size_t ws_bytes, cudaStream_t st)

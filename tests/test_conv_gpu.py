@@ -290,3 +290,71 @@ def test_nchw_few_channels_on_the_tensor_engine(ci, passes):
     refs = {"y": y, "dw": dw, "db": db, "dx": dx}
     for nm in ("y",) + (("dw", "db") if "wgrad" in passes else ()) + (("dx",) if "dgrad" in passes else ()):
         assert_parity(out[nm], refs[nm], np.float32, f"NCHW ci={ci} {nm}")
+
+
+def test_balanced_mode_layer_next_to_a_kernel_that_holds_most_sms():
+    """The balanced mode hands partial tiles between consecutive CTAs.  Its CTAs need not be resident together: here a
+    long weight-gradient kernel (144 persistent CTAs, each owning its SM's shared memory) is started on a second stream
+    and a balanced forward pass right behind it on the first, so only a few of the 148 CTAs can start until the other
+    kernel ends.  The result must be bit-identical to the same pass run alone, and no bounded wait may run out."""
+    L = _lib.lib()
+    big = co.Geom(64, 56, 56, 256, 256, 3, 3, 1, 1, 1, 1)          # wgrad: 36 output tiles x 4 pixel ranges = 144 CTAs, about 1 ms
+    bal = co.Geom(64, 14, 14, 256, 256, 3, 3, 1, 1, 1, 1)          # fprop: 196 tiles x 72 k-blocks on 148 CTAs -> balanced ranges
+    gen = torch.Generator(device=DEV).manual_seed(77)
+    dbig, dbal = make_desc(big, "NHWC", np.float32, "KRSC"), make_desc(bal, "NHWC", np.float32, "KRSC")
+    xb = torch.randn((big.n, big.h, big.w, big.ci), device=DEV, generator=gen)
+    dyb = torch.randn((big.n, big.ho, big.wo, big.co), device=DEV, generator=gen)
+    dwb = torch.empty((big.co, 3, 3, big.ci), device=DEV)
+    x = torch.randn((bal.n, bal.h, bal.w, bal.ci), device=DEV, generator=gen)
+    w = torch.randn((bal.co, 3, 3, bal.ci), device=DEV, generator=gen) * 0.03
+    y_alone, y_busy = torch.empty((bal.n, bal.ho, bal.wo, bal.co), device=DEV), torch.empty((bal.n, bal.ho, bal.wo, bal.co), device=DEV)
+    ws_a, ws_b = workspace(dbal), workspace(dbig)
+    main = torch.cuda.current_stream()
+    other = torch.cuda.Stream()
+
+    def fprop(out):
+        _lib.check(L.b2c_conv_fprop(ctypes.byref(dbal), x.data_ptr(), w.data_ptr(), None, None, 0, out.data_ptr(), ws_a.data_ptr(),
+                                    ws_a.numel(), main.cuda_stream))
+    fprop(y_alone)
+    torch.cuda.synchronize()
+    for _ in range(3):                                             # a few rounds: the overlap depends on launch timing
+        y_busy.fill_(float("nan"))
+        torch.cuda.synchronize()
+        _lib.check(L.b2c_conv_wgrad(ctypes.byref(dbig), xb.data_ptr(), dyb.data_ptr(), dwb.data_ptr(), None, ws_b.data_ptr(),
+                                    ws_b.numel(), other.cuda_stream))
+        fprop(y_busy)
+        torch.cuda.synchronize()
+        _lib.check(L.b2c_check_device_status(None))
+        assert torch.equal(y_busy, y_alone)
+
+
+def test_weight_gradient_from_the_forward_pass_lowered_input_is_bit_identical():
+    """A few-channel layer (network stem) writes its im2row matrix into the workspace in the forward pass; with the same
+    workspace untouched, b2c_conv_wgrad_lowered must give the bits of b2c_conv_wgrad (which lowers x again)."""
+    L = _lib.lib()
+    g = co.Geom(4, 40, 40, 3, 64, 7, 7, 3, 3, 2, 2)
+    desc = make_desc(g, "NHWC", np.float32, "KRSC")
+    assert L.b2c_conv_keeps_lowered_input(ctypes.byref(desc)) == 1
+    gen = torch.Generator(device=DEV).manual_seed(5)
+    x = torch.randn((g.n, g.h, g.w, g.ci), device=DEV, generator=gen)
+    w = torch.randn((g.co, 7, 7, g.ci), device=DEV, generator=gen) * 0.1
+    b = torch.randn((g.co,), device=DEV, generator=gen)
+    dy = torch.randn((g.n, g.ho, g.wo, g.co), device=DEV, generator=gen)
+    y = torch.empty_like(dy)
+    ws = workspace(desc)
+    out = {}
+    for name in ("plain", "lowered"):
+        dw, db = torch.full_like(w, float("nan")), torch.full_like(b, float("nan"))
+        _lib.check(L.b2c_conv_fprop(ctypes.byref(desc), x.data_ptr(), w.data_ptr(), b.data_ptr(), None, 0, y.data_ptr(), ws.data_ptr(),
+                                    ws.numel(), stream()))
+        fn = L.b2c_conv_wgrad if name == "plain" else L.b2c_conv_wgrad_lowered
+        _lib.check(fn(ctypes.byref(desc), x.data_ptr(), dy.data_ptr(), dw.data_ptr(), db.data_ptr(), ws.data_ptr(), ws.numel(), stream()))
+        torch.cuda.synchronize()
+        out[name] = (dw.cpu().numpy(), db.cpu().numpy())
+    assert np.array_equal(out["plain"][0], out["lowered"][0]) and np.array_equal(out["plain"][1], out["lowered"][1])
+    # layers with a multiple of 32 input channels never lower: the entry point refuses them
+    g2 = co.Geom(2, 8, 8, 32, 32, 3, 3, 1, 1, 1, 1)
+    d2 = make_desc(g2, "NHWC", np.float32, "KRSC")
+    assert L.b2c_conv_keeps_lowered_input(ctypes.byref(d2)) == 0
+    t = torch.zeros(64, device=DEV)
+    assert L.b2c_conv_wgrad_lowered(ctypes.byref(d2), t.data_ptr(), t.data_ptr(), t.data_ptr(), None, t.data_ptr(), 256, stream()) == -6
