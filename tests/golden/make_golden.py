@@ -3,7 +3,7 @@
 Run once, in a container where the reference checkout is mounted and ``oracle/build_oracle.py``
 has compiled its Cython kernels into ``oracle/_ref``:
 
-    python tests/golden/make_golden.py [/root/reference]
+    python tests/golden/make_golden.py [<reference checkout>]
 
 The script imports the reference package, stands up its own CPU layer classes
 (``Conv2DCPU``, ``FCCPU``, ``BatchNormalizationCPU``, pooling, ReLU, softmax, the
