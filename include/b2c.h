@@ -103,7 +103,8 @@ int b2c_conv_fprop(const b2c_conv_desc *desc, const void *x, const void *w, cons
  * pydtnn/backends/cpu/layers/batch_normalization_cpu.py:65-70): y = conv(x, w) + bias as b2c_conv_fprop writes it, and
  * in `stats` the per-channel sum and sum of squares of y, taken from the tiles on their way to memory, so that the batch
  * norm does not read y a second time for them.  `stats` is an opaque DEVICE buffer of b2c_conv_stats_bytes(desc) bytes
- * (16-byte aligned) that b2c_bn_train_forward_prestats consumes; it is rewritten by every call.
+ * (16-byte aligned) that b2c_bn_train_forward_prestats consumes; it is rewritten by every call.  The byte count says
+ * how many rows of partial sums the launch leaves, so pass the value b2c_conv_stats_bytes returned to both calls.
  * b2c_conv_stats_bytes returns 0, and b2c_conv_fprop_stats B2C_ERR_UNSUPPORTED, for shapes outside the float32 NHWC
  * tensor-core path (callers then use b2c_conv_fprop and b2c_bn_train_forward). */
 size_t b2c_conv_stats_bytes(const b2c_conv_desc *desc);
@@ -175,7 +176,8 @@ int b2c_bn_train_forward_residual(int dtype, int layout, int n, int c, int hw, c
 
 /* b2c_bn_train_forward (float32, NHWC) with the batch sums already taken by b2c_conv_fprop_stats on the convolution
  * that wrote x: mean, inverse standard deviation and the running averages come from `stats` (summed in double, in a
- * fixed order), then y = relu?(bn(x) [+ addend]) in one pass over x.  addend may be NULL (see
+ * fixed order), then y = relu?(bn(x) [+ addend]) in one pass over x.  stats_bytes: what b2c_conv_stats_bytes returned
+ * for that convolution (B2C_ERR_BAD_GEOMETRY if it is not a whole number of [2][c] float rows).  addend may be NULL (see
  * b2c_bn_train_forward_residual).  scratch: as for b2c_bn_train_forward.  Backward is b2c_bn_train_backward, unchanged. */
 int b2c_bn_train_forward_prestats(int n, int c, int hw, const void *x, const void *stats, size_t stats_bytes,
                                   const void *gamma, const void *beta, void *running_mean, void *running_var,

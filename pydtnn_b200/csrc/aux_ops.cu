@@ -434,6 +434,47 @@ __global__ void __launch_bounds__(256) bn_conv_sums_kernel(const float* __restri
     }
 }
 
+// The batch statistics from a few rows of partial sums (a convolution that kept one row per CTA group): block
+// (32 channels, 32 row lanes), one block per 32 channels.  A thread adds its rows (32 apart) in index order in double,
+// the 32 row lanes are added in lane order, then mean, inverse deviation and the running averages as
+// reduce2_final_warp_kernel (mode 0) writes them.
+__global__ void __launch_bounds__(1024) bn_rows_final_kernel(const float* __restrict__ sums, int rows, int c, double count, double momentum,
+                                                             double eps, float* __restrict__ mean_out, float* __restrict__ inv_std_out,
+                                                             float* __restrict__ run_mean, float* __restrict__ run_var)
+{
+    pdl_prologue();
+    __shared__ double s0[32][33], s1[32][33];
+    const int ch = blockIdx.x * 32 + threadIdx.x;
+    double a0 = 0.0, a1 = 0.0;
+    if (ch < c) {
+        int i = threadIdx.y;
+        for (; i + 96 < rows; i += 128) {        // four independent row pairs in flight, added in index order
+            float u0[4], u1[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                u0[u] = __ldcg(sums + ((size_t)(i + 32 * u) * 2) * c + ch);
+                u1[u] = __ldcg(sums + ((size_t)(i + 32 * u) * 2 + 1) * c + ch);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++) { a0 += (double)u0[u]; a1 += (double)u1[u]; }
+        }
+        for (; i < rows; i += 32) {
+            a0 += (double)__ldcg(sums + ((size_t)i * 2) * c + ch);
+            a1 += (double)__ldcg(sums + ((size_t)i * 2 + 1) * c + ch);
+        }
+    }
+    s0[threadIdx.y][threadIdx.x] = a0; s1[threadIdx.y][threadIdx.x] = a1;
+    __syncthreads();
+    if (threadIdx.y != 0 || ch >= c) return;
+    double t0 = 0.0, t1 = 0.0;
+    for (int i = 0; i < 32; i++) { t0 += s0[i][threadIdx.x]; t1 += s1[i][threadIdx.x]; }
+    double mean = t0 / count, var = t1 / count - mean * mean;
+    if (var < 0.0) var = 0.0;
+    mean_out[ch] = (float)mean; inv_std_out[ch] = (float)(1.0 / sqrt(var + eps));
+    run_mean[ch] = (float)(momentum * (double)run_mean[ch] + (1.0 - momentum) * mean);
+    run_var[ch] = (float)(momentum * (double)run_var[ch] + (1.0 - momentum) * var);
+}
+
 static V4Geo v4_apply_geo(int64_t rows, int c)
 {
     V4Geo g = v4_geo(rows, c, 1 << 20);
@@ -1070,11 +1111,24 @@ extern "C" int b2c_bn_train_forward_prestats(int n, int c, int hw, const void* x
     if (!x || !stats || !gamma || !beta || !running_mean || !running_var || !y || !save_mean || !save_inv_std || !scratch) return B2C_ERR_NULL_POINTER;
     if (n <= 0 || c <= 0 || hw <= 0) return B2C_ERR_BAD_GEOMETRY;
     if (!v4_ok(B2C_F32, B2C_LAYOUT_NHWC, c, x, y, addend ? addend : x)) return B2C_ERR_UNSUPPORTED;
-    const int64_t rows64 = ((int64_t)n * hw + 31) / 32;
-    if (stats_bytes < (size_t)rows64 * 2 * c * sizeof(float)) return B2C_ERR_WORKSPACE_TOO_SMALL;
+    // the convolution chose how many rows of sums to leave (one per 32 output rows, or one per CTA group and row
+    // quadrant): the byte count it reported for the buffer says which
+    const size_t row_bytes = (size_t)2 * c * sizeof(float);
+    if (stats_bytes < row_bytes || stats_bytes % row_bytes || stats_bytes / row_bytes > (size_t)(((int64_t)n * hw + 127) / 128) * 4)
+        return B2C_ERR_BAD_GEOMETRY;
     if (scratch_bytes < reduce2_bytes(c)) return B2C_ERR_WORKSPACE_TOO_SMALL;
-    const int rows = (int)rows64;
+    const int rows = (int)(stats_bytes / row_bytes);
     cudaStream_t st = (cudaStream_t)stream;
+    if (rows <= 1024) {
+        // few rows: one kernel adds them and finishes the statistics
+        launch_pdl(bn_rows_final_kernel, (c + 31) / 32, dim3(32, 32), 0, st, (const float*)stats, rows, c, (double)n * hw, momentum, eps,
+                   (float*)save_mean, (float*)save_inv_std, (float*)running_mean, (float*)running_var);
+        int rc = check_launch("bn_rows_final"); if (rc) return rc;
+        V4Geo ga = v4_apply_geo((int64_t)n * hw, c);
+        launch_pdl(bn_apply_v4_kernel, dim3(ga.gx, ga.chunks), 256, 0, st, (const float4*)x, (float4*)y, (const float*)save_mean, (const float*)save_inv_std,
+                                                                  (const float*)gamma, (const float*)beta, ga, fuse_relu, (const float4*)addend);
+        return check_launch("bn_apply_v4");
+    }
     // chunks: at least 32 rows of sums each, about two blocks per SM, no more than the scratch holds
     const int gx = (c + 31) / 32;
     int chunks = (296 + gx - 1) / gx;

@@ -24,7 +24,7 @@
 // Variants (template parameters): whole tiles or balanced (tile, k-block) ranges with a hand-over of partial
 // tiles between consecutive CTAs; 2 or 4 output slabs per drain warp; NCHW tensors run on channel-last copies.
 //
-// Warp roles (320 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer (both stay
+// Warp roles (320 threads; 448 in the variant with eight drain warps): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer (both stay
 // converged and issue through one elected lane), warps 2-5 = operand transform,
 // warps 6-9 = drain + epilogue: the tensor core's accumulate step truncates, so sums are kept in
 // tensor memory only for a chunk of 8 k-blocks (two TMEM buffers alternate) and added chunk by
@@ -243,11 +243,13 @@ enum { TC_ERR_FULL = 1, TC_ERR_XFORM = 2, TC_ERR_EMPTY = 3, TC_ERR_TFULL = 4, TC
 __device__ long long g_tc_prof[32];
 #define TC_PROF_DECL() long long _pa[16]; for (int _i = 0; _i < 16; _i++) _pa[_i] = 0
 #define TC_PROF_T0() long long _pt = clock64()
+#define TC_PROF_RESET() _pt = clock64()
 #define TC_PROF_ADD(slot) do { long long _n = clock64(); _pa[slot] += _n - _pt; _pt = _n; } while (0)
 #define TC_PROF_FLUSH() do { if (blockIdx.x == 0) for (int _i = 0; _i < 16; _i++) if (_pa[_i]) atomicAdd((unsigned long long*)&g_tc_prof[_i], (unsigned long long)_pa[_i]); } while (0)
 #else
 #define TC_PROF_DECL() do { } while (0)
 #define TC_PROF_T0() do { } while (0)
+#define TC_PROF_RESET() do { } while (0)
 #define TC_PROF_ADD(slot) do { } while (0)
 #define TC_PROF_FLUSH() do { } while (0)
 #endif
@@ -447,7 +449,10 @@ struct TcParams {
     int64_t cls_out[4];
     // FWD with batch statistics: for every block of 32 output rows, row (m / 32) of `stats` ([ceil(M/32)][2][N] floats)
     // receives the per-channel sum and sum of squares of the stored values (rows past M left out).  Null: off.
+    // stats_cta: the grid is a multiple of the column-tile count nt, so a CTA keeps one column tile; it adds the sums
+    // of all its tiles in registers and `stats` is [(grid / nt) * 4][2][N]: one row per CTA group and row quadrant.
     float* stats;
+    int stats_cta;
 };
 
 // Per-channel epilogue steps of the forward pass, decided once on the host so the drain warps branch on
@@ -507,14 +512,14 @@ __device__ __forceinline__ void tc_epilogue_math(const TcParams& p, int nbase, f
 // Shared memory per pipeline stage: the raw A tile (activations), then the hi and lo halves of the B tile.
 // Tensor memory (512 columns): two accumulator buffers of BN columns, then per stage 64 columns holding
 // the hi and lo halves of the A tile (128 rows x 32 k).
-template <int BN, int STAGES, int SLABS>
+template <int BN, int STAGES, int SLABS, int DRAIN_WARPS = 4>
 struct TcSmem {
     static constexpr int A_BYTES = 128 * 128;   // 128 rows x 32 floats (FWD) or 32 pixels x 128 rows (WGRAD)
     static constexpr int B_BYTES = BN * 128;
     static constexpr int STAGE_BYTES = A_BYTES + 2 * B_BYTES;
     static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
     static constexpr int EPI_OFFSET = BAR_OFFSET + 1024;          // barriers and flags live in the first 256 bytes
-    static constexpr int EPI_BYTES = 4 * SLABS * 4096;            // per drain warp: SLABS 32 x 32 float staging slabs
+    static constexpr int EPI_BYTES = DRAIN_WARPS * SLABS * 4096;  // per drain warp: SLABS 32 x 32 float staging slabs
     static constexpr int TOTAL = EPI_OFFSET + EPI_BYTES + 1024;   // + alignment slack
     static constexpr int TMEM_A_COL = 2 * BN;                     // first column of the A slots
     static constexpr int TMEM_COLS = 512;
@@ -563,19 +568,28 @@ __device__ __forceinline__ void st_release_gpu(int* p, int v) {
 // Registers are handed out per group of four warps, so the 10 warps are budgeted as 12: 168 registers per thread
 // is the most a launch of this shape gets (200 compiles but is refused at launch).
 // Geometry of the tile a role is working on: the launch's own, or that of the tile's pixel class (MULTI).
+// The slab column whose batch sums a lane of a drain warp ends up holding (see the statistics step of emit_slab).
+__device__ __forceinline__ int tc_stats_col(int lane) { return (lane & 7) * 4 + (lane >> 3); }
+
 struct TileGeo {
     int M, P, Q, kblocks, S, low_h, low_w, r0, s0, ltile;
     int64_t out_off;
     const CUtensorMap* ma;
 };
 
-template <int MODE, int BN, int STAGES, bool SK, int SLABS, int BSRC, bool STREAM, bool MULTI>
-__global__ void __launch_bounds__(320, 1)
+// STREAM: 0 = chunked drain, 1 = streaming epilogue, 2 = streaming epilogue with eight drain warps (448 threads: two
+// warps per tensor-memory lane quadrant, each taking half of the tile's columns).
+constexpr int TC_STREAM8 = 2;
+template <int STREAM> constexpr int tc_drain_warps() { return STREAM == TC_STREAM8 ? 8 : 4; }
+template <int STREAM> constexpr int tc_threads() { return (6 + tc_drain_warps<STREAM>()) * 32; }
+
+template <int MODE, int BN, int STAGES, bool SK, int SLABS, int BSRC, int STREAM, bool MULTI>
+__global__ void __launch_bounds__(tc_threads<STREAM>(), 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b0,
                const __grid_constant__ CUtensorMap tmap_b1, const __grid_constant__ CUtensorMap tmap_out,
                const __grid_constant__ CUtensorMap tmap_a3, TcParams p)
 {
-    static_assert(!MULTI || (MODE == TCM_FWD && !SK && !STREAM && BSRC != TCB_SPLIT), "pixel classes: whole-tile forward variant on the caller's filter");
+    static_assert(!MULTI || (MODE == TCM_FWD && !SK && STREAM == 0 && BSRC != TCB_SPLIT), "pixel classes: whole-tile forward variant on the caller's filter");
     // MULTI: the activation maps of classes 0..3 travel in the parameter slots tmap_a, tmap_b1, tmap_out, tmap_a3
     // (the split-filter map and the output map have no use there: filters are read in place, rows are scattered).
     auto tile_geo = [&](int tile) {
@@ -598,9 +612,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     // CTAs running at the same time share activation rows in L2).  The smem pipeline and the two TMEM
     // buffers keep running across tile boundaries: the producer prefetches the next tile while the
     // drain warps still store the previous one.
-    using L = TcSmem<BN, STAGES, SLABS>;
+    using L = TcSmem<BN, STAGES, SLABS, tc_drain_warps<STREAM>()>;
+    constexpr int DW = tc_drain_warps<STREAM>();
     // STREAM variants serve tiles of at most TC_CHUNK k-blocks with dense outputs (see dispatch_fwd)
-    static_assert(!STREAM || (MODE == TCM_FWD && !SK), "the streaming epilogue is a whole-tile forward variant");
+    static_assert(STREAM == 0 || (MODE == TCM_FWD && !SK), "the streaming epilogue is a whole-tile forward variant");
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* full_bar = (uint64_t*)(smem + L::BAR_OFFSET);
@@ -624,7 +639,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&xform_bar[s], 4); mbar_init(&empty_bar[s], 1); }
-        for (int b = 0; b < 2; b++) { mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], 4); }
+        for (int b = 0; b < 2; b++) { mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], DW); }
         *abort_flag = 0;
         fence_barrier_init();
         fence_proxy_async();
@@ -915,6 +930,12 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const int quad = warp & 3;                       // TMEM lane quadrant this warp may read
         bool ok = true;
         int gc = 0, ecount = 0;
+        // column slabs of a tile this warp sends out: all BN / 32, or its half of them with eight drain warps
+        constexpr int NSLAB = BN / 32 / (DW / 4);
+        const int cbeg = ((warp - 6) >> 2) * NSLAB;
+        float cs0[NSLAB], cs1[NSLAB];                    // batch statistics summed over this CTA's tiles (stats_cta)
+#pragma unroll
+        for (int i = 0; i < NSLAB; i++) cs0[i] = cs1[i] = 0.f;
         TileWalk w;
         w.init(total_tiles, p.kblocks);
         while (ok && w.template next<SK>()) {
@@ -928,12 +949,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             // columns >= N clipped; SLABS slabs per warp rotate so the warp never waits on HBM), and the slab's batch
             // statistics when asked for.
             uint8_t* ebuf = smem + L::EPI_OFFSET + (warp - 6) * (SLABS * 4096);
-            float st0[BN / 32], st1[BN / 32];                           // batch statistics of the tile's slabs
-            auto emit_slab = [&](float* a, int cc) {
+            float st0[NSLAB], st1[NSLAB];                               // batch statistics of the tile's slabs
+            TC_PROF_T0();
+            auto emit_slab = [&](float* a, int cc, int i) {      // slab cc of the tile, number i of this warp's slabs
                 uint8_t* buf = ebuf + (ecount % SLABS) * 4096;
                 if (MODE == TCM_FWD && p.epi) tc_epilogue_math(p, n0 + cc * 32, a);
+                if (threadIdx.x == 192) TC_PROF_ADD(8);     // drain: tensor-memory loads, adds, epilogue arithmetic
                 if (lane == 0) tma_store_wait_read<SLABS - 1>();     // the store that last read this slab is done
                 __syncwarp();
+                if (threadIdx.x == 192) TC_PROF_ADD(10);    // drain: waiting for a free staging slab
 #pragma unroll
                 for (int j = 0; j < 32; j += 4)
                     *reinterpret_cast<float4*>(buf + lane * 128 + ((((j >> 2) ^ (lane & 7))) << 4)) = make_float4(a[j], a[j + 1], a[j + 2], a[j + 3]);
@@ -944,73 +968,93 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     else tma_store_3d(&tmap_out, buf, n0 + cc * 32, m0 + quad * 32, z);
                     tma_store_commit();
                 }
+                if (threadIdx.x == 192) TC_PROF_ADD(9);     // drain: staging writes, fence, store issue
                 if (MODE == TCM_FWD && p.stats) {
-                    // lane j sums column j of the slab (one shared-memory row per step, no bank conflicts) over the rows
-                    // that exist.  The sums wait in registers until the tile's last slab is on its way.
-                    // All 32 slab rows are read (they exist in shared memory whatever M is) in batches of eight
-                    // independent loads; rows past M count as zeros.
+                    // Column sums of the slab over the rows that exist, read back from the staging slab: lane
+                    // (rg = lane / 8, c4 = lane % 8) takes columns 4 c4 .. 4 c4 + 3 of rows rg, rg + 4, .. (one float4 each:
+                    // the eight lanes of a row group read one whole 128-byte row, no bank conflicts), the four row groups
+                    // are added by two exchange steps that also hand every lane one column: lane keeps column
+                    // 4 c4 + rg (tc_stats_col).  The sums wait in registers until the tile's last slab is on its way.
                     const int valid = p.M - (m0 + quad * 32);
-                    float s0 = 0.f, s1 = 0.f;
-                    const uint32_t col = smem_u32(buf) + (lane & 3) * 4;
+                    const int rg = lane >> 3, c4 = lane & 7;
+                    float4 q[8];
 #pragma unroll
-                    for (int r8 = 0; r8 < 32; r8 += 8) {
-                        float v[8];
-#pragma unroll
-                        for (int r = 0; r < 8; r++)
-                            asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v[r]) : "r"(col + (r8 + r) * 128 + ((((lane >> 2) ^ r)) << 4)));
-#pragma unroll
-                        for (int r = 0; r < 8; r++) {
-                            const float u = r8 + r < valid ? v[r] : 0.f;
-                            s0 += u; s1 = fmaf(u, u, s1);
-                        }
+                    for (int r = 0; r < 8; r++) {
+                        const int row = rg + 4 * r;
+                        const uint32_t addr = smem_u32(buf) + row * 128 + ((c4 ^ (row & 7)) << 4);
+                        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(q[r].x), "=f"(q[r].y), "=f"(q[r].z), "=f"(q[r].w) : "r"(addr));
                     }
-                    st0[cc] = s0; st1[cc] = s1;
+                    float4 t0 = make_float4(0.f, 0.f, 0.f, 0.f), t1 = t0;
+#pragma unroll
+                    for (int r = 0; r < 8; r++) {
+                        float4 u = q[r];
+                        if (rg + 4 * r >= valid) u = make_float4(0.f, 0.f, 0.f, 0.f);       // rows past M count as zeros
+                        t0.x += u.x; t0.y += u.y; t0.z += u.z; t0.w += u.w;
+                        t1.x = fmaf(u.x, u.x, t1.x); t1.y = fmaf(u.y, u.y, t1.y); t1.z = fmaf(u.z, u.z, t1.z); t1.w = fmaf(u.w, u.w, t1.w);
+                    }
+                    const bool up = (lane & 16) != 0, odd = (lane & 8) != 0;
+                    // step 1 (partner lane ^ 16): the lower lane keeps columns 0, 1 of the four, the upper one 2, 3
+                    float k0 = up ? t0.z : t0.x, k1 = up ? t0.w : t0.y, g0 = up ? t0.x : t0.z, g1 = up ? t0.y : t0.w;
+                    float m0s = up ? t1.z : t1.x, m1s = up ? t1.w : t1.y, h0 = up ? t1.x : t1.z, h1 = up ? t1.y : t1.w;
+                    k0 += __shfl_xor_sync(0xffffffffu, g0, 16); k1 += __shfl_xor_sync(0xffffffffu, g1, 16);
+                    m0s += __shfl_xor_sync(0xffffffffu, h0, 16); m1s += __shfl_xor_sync(0xffffffffu, h1, 16);
+                    // step 2 (partner lane ^ 8): one column each
+                    float s0 = odd ? k1 : k0, e0 = odd ? k0 : k1, s1 = odd ? m1s : m0s, e1 = odd ? m0s : m1s;
+                    s0 += __shfl_xor_sync(0xffffffffu, e0, 8); s1 += __shfl_xor_sync(0xffffffffu, e1, 8);
+                    st0[i] = s0; st1[i] = s1;
+                    if (threadIdx.x == 192) TC_PROF_ADD(11);    // drain: batch statistics
                 }
                 ecount++;
             };
             auto store_stats = [&]() {
-                if (MODE == TCM_FWD && p.stats && m0 + quad * 32 < p.M) {
-                    // row (m / 32) of the statistics: the block's two rows of sums, 128 contiguous bytes per slab
-                    float* srow = p.stats + ((size_t)((m0 >> 5) + quad) * 2) * p.N + n0 + lane;
+                if (MODE == TCM_FWD && p.stats && p.stats_cta && m0 + quad * 32 < p.M) {
+                    // the grid is a multiple of the column-tile count, so every tile of this CTA has the same n0
 #pragma unroll
-                    for (int cc = 0; cc < BN / 32; cc++)
-                        if (n0 + cc * 32 + lane < p.N) { __stcg(srow + cc * 32, st0[cc]); __stcg(srow + cc * 32 + p.N, st1[cc]); }
+                    for (int i = 0; i < NSLAB; i++)
+                        if (n0 + (cbeg + i) * 32 < p.N) { cs0[i] += st0[i]; cs1[i] += st1[i]; }
+                } else if (MODE == TCM_FWD && p.stats && m0 + quad * 32 < p.M) {
+                    // row (m / 32) of the statistics: the block's two rows of sums, 128 contiguous bytes per slab
+                    const int col = tc_stats_col(lane);
+                    float* srow = p.stats + ((size_t)((m0 >> 5) + quad) * 2) * p.N + n0 + cbeg * 32 + col;
+#pragma unroll
+                    for (int i = 0; i < NSLAB; i++)
+                        if (n0 + (cbeg + i) * 32 + col < p.N) { __stcg(srow + i * 32, st0[i]); __stcg(srow + i * 32 + p.N, st1[i]); }
                 }
             };
-            if constexpr (STREAM) {
+            if constexpr (STREAM != 0) {
                 // Short K loops: the tile is one chunk in tensor memory and the epilogue, not the tensor pipe, sets the
                 // pace.  The drain warp takes 32 columns at a time straight from tensor memory (the next 32 already in
                 // flight) and sends them out, so it never holds a whole row of the tile in registers.
                 const int b = gc & 1;
-                TC_PROF_T0();
+                TC_PROF_RESET();
                 ok = mbar_wait(&tfull_bar[b], (gc >> 1) & 1, abort_flag, &g_tc_status, TC_ERR_TFULL);
                 if (threadIdx.x == 192) TC_PROF_ADD(7);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t tsrc = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(b * BN);
                 float a[2][32];
-                tmem_ld_32x32_f(tsrc, a[0]);
+                tmem_ld_32x32_f(tsrc + (uint32_t)(cbeg * 32), a[0]);
 #pragma unroll
-                for (int cc = 0; cc < BN / 32; cc++) {
+                for (int i = 0; i < NSLAB; i++) {
+                    const int cc = cbeg + i;
                     tmem_ld_wait();
-                    if (cc + 1 < BN / 32) tmem_ld_32x32_f(tsrc + (uint32_t)((cc + 1) * 32), a[(cc + 1) & 1]);
+                    if (i + 1 < NSLAB) tmem_ld_32x32_f(tsrc + (uint32_t)((cc + 1) * 32), a[(i + 1) & 1]);
                     else {
-                        // every column of the buffer is in registers: the tensor core may have it back
+                        // every column this warp takes is in registers: the tensor core may have the buffer back
                         tc_fence_before();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&tempty_bar[b]);
                     }
-                    if (n0 + cc * 32 < p.N && m0 + quad * 32 < p.M) emit_slab(a[cc & 1], cc);
+                    if (n0 + cc * 32 < p.N && m0 + quad * 32 < p.M) emit_slab(a[i & 1], cc, i);
                 }
                 gc++;
                 store_stats();
-                continue;
-            }
+            } else {
             const int nchunks = (w.kb_e - w.kb_b + TC_CHUNK - 1) / TC_CHUNK;
             float acc[BN];
             for (int c = 0; c < nchunks && ok; c++, gc++) {
                 const int b = gc & 1;
-                TC_PROF_T0();
+                TC_PROF_RESET();
                 ok = mbar_wait(&tfull_bar[b], (gc >> 1) & 1, abort_flag, &g_tc_status, TC_ERR_TFULL);
                 if (threadIdx.x == 192) TC_PROF_ADD(7);    // drain: waiting for a finished chunk
                 if (!ok) break;
@@ -1082,7 +1126,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     }
                 }
             }
-            TC_PROF_T0();
+            TC_PROF_RESET();
             // Epilogue. A thread owns one output row, but a warp writing 32 different rows per store would
             // touch 32 cache lines with 16 bytes each; the values go through a per-warp smem tile instead so
             // that every store instruction writes whole 128-byte row segments (8 lanes per row, 4 rows).
@@ -1103,7 +1147,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             if (ok && p.tma_store) {
 #pragma unroll
                 for (int cc = 0; cc < BN / 32; cc++)
-                    if (n0 + cc * 32 < p.N && m0 + quad * 32 < p.M) emit_slab(&acc[cc * 32], cc);     // slabs wholly outside the output are skipped
+                    if (n0 + cc * 32 < p.N && m0 + quad * 32 < p.M) emit_slab(&acc[cc * 32], cc, cc);     // slabs wholly outside the output are skipped
                 store_stats();
             } else if (ok) {
                 float* stage = (float*)(smem + L::EPI_OFFSET) + (warp - 6) * (SLABS * 4096 / 4);
@@ -1137,6 +1181,16 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 }
             }
             if (threadIdx.x == 192) TC_PROF_ADD(9);        // drain: epilogue
+            }   // chunked drain
+        }
+        if (MODE == TCM_FWD && !SK && !MULTI && p.stats && p.stats_cta && ok) {
+            // One row of sums per (group of nt CTAs, row quadrant): the nt CTAs of a group hold the nt column tiles.
+            const int n0 = (int)(blockIdx.x % nt) * BN;
+            const int col = tc_stats_col(lane);
+            float* srow = p.stats + ((size_t)((blockIdx.x / nt) * 4 + quad) * 2) * p.N + n0 + cbeg * 32 + col;
+#pragma unroll
+            for (int i = 0; i < NSLAB; i++)
+                if (n0 + (cbeg + i) * 32 + col < p.N) { __stcg(srow + i * 32, cs0[i]); __stcg(srow + i * 32 + p.N, cs1[i]); }
         }
         if (p.tma_store && lane == 0) tma_store_wait_read<0>();   // the slabs stay allocated until the last store has read them
     }
@@ -1490,11 +1544,11 @@ static size_t tc_workspace_bytes_nhwc(const Geo& g, int pass)
            align_up((size_t)pl.splits * 4 * g.co * sizeof(float), 1024);
 }
 
-template <int MODE, int BN, int STAGES, bool SK, int SLABS, int BSRC, bool STREAM = false, bool MULTI = false>
+template <int MODE, int BN, int STAGES, bool SK, int SLABS, int BSRC, int STREAM = 0, bool MULTI = false>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb0, const CUtensorMap& mb1, const CUtensorMap& mo, const TcParams& p, int splits, cudaStream_t st,
                      const CUtensorMap* ma3 = nullptr)
 {
-    using L = TcSmem<BN, STAGES, SLABS>;
+    using L = TcSmem<BN, STAGES, SLABS, tc_drain_warps<STREAM>()>;
     static PerDeviceOnce attr;
     {
         cudaError_t e = attr.run([] { return cudaFuncSetAttribute(conv_tc_kernel<MODE, BN, STAGES, SK, SLABS, BSRC, STREAM, MULTI>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL); });
@@ -1508,8 +1562,9 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb0, const CUtens
 #ifdef B2C_TC_DEV
     { const char* e = getenv("B2C_TC_DBG"); q.dbg = e ? atoi(e) : 0; }
 #endif
-    const int grid = q.sk ? sm_count : (int)(tiles < sm_count ? tiles : sm_count);     // one persistent CTA per SM
-    launch_pdl(conv_tc_kernel<MODE, BN, STAGES, SK, SLABS, BSRC, STREAM, MULTI>, grid, 320, L::TOTAL, st, ma, mb0, mb1, mo, ma3 ? *ma3 : ma, q);
+    int grid = q.sk ? sm_count : (int)(tiles < sm_count ? tiles : sm_count);     // one persistent CTA per SM
+    if (q.stats && q.stats_cta) grid -= grid % ((p.N + BN - 1) / BN);               // a CTA keeps its column tile
+    launch_pdl(conv_tc_kernel<MODE, BN, STAGES, SK, SLABS, BSRC, STREAM, MULTI>, grid, tc_threads<STREAM>(), L::TOTAL, st, ma, mb0, mb1, mo, ma3 ? *ma3 : ma, q);
     return check_launch("conv_tc_kernel");
 }
 
@@ -1524,12 +1579,12 @@ static int dispatch_fwd(int bn, const CUtensorMap& ma, const CUtensorMap& mb0, c
     // streaming epilogue (32 columns at a time straight from tensor memory); up to four k-blocks per tile a shallower
     // operand pipeline also leaves room for four output slabs per drain warp, so a whole tile's stores are in flight.
     if (p.kblocks <= 4 && p.tma_store) {
-        if (bn == 64) return launch_tc<TCM_FWD, 64, 4, false, 4, BSRC, true>(ma, mb0, mb1, mo, p, 1, st);
-        return launch_tc<TCM_FWD, 128, 3, false, 4, BSRC, true>(ma, mb0, mb1, mo, p, 1, st);
+        if (bn == 64) return launch_tc<TCM_FWD, 64, 4, false, 2, BSRC, TC_STREAM8>(ma, mb0, mb1, mo, p, 1, st);
+        return launch_tc<TCM_FWD, 128, 3, false, 2, BSRC, TC_STREAM8>(ma, mb0, mb1, mo, p, 1, st);
     }
     if (p.kblocks <= TC_CHUNK && p.tma_store) {
-        if (bn == 64) return launch_tc<TCM_FWD, 64, 6, false, 2, BSRC, true>(ma, mb0, mb1, mo, p, 1, st);
-        return launch_tc<TCM_FWD, 128, 4, false, 2, BSRC, true>(ma, mb0, mb1, mo, p, 1, st);
+        if (bn == 64) return launch_tc<TCM_FWD, 64, 6, false, 2, BSRC, 1>(ma, mb0, mb1, mo, p, 1, st);
+        return launch_tc<TCM_FWD, 128, 4, false, 2, BSRC, 1>(ma, mb0, mb1, mo, p, 1, st);
     }
     if (bn == 64) return launch_tc<TCM_FWD, 64, 6, false, 2, BSRC>(ma, mb0, mb1, mo, p, 1, st);
     return launch_tc<TCM_FWD, 128, 4, false, 2, BSRC>(ma, mb0, mb1, mo, p, 1, st);
@@ -1582,6 +1637,32 @@ static bool make_map_out(CUtensorMap* map, const void* base, uint64_t planes, ui
 // filter kh x kw (dilation dil); output rows (n, i, j) over P x Q written at out + n*o_sn + i*o_sh + j*o_sw.
 // Where a forward pass leaves the batch statistics of its output (see TcParams::stats), or null.
 struct StatsOut { float* sums; };
+
+// Whole tiles or balanced k-block ranges for a forward launch (cost in k-block units: whole tiles take
+// rounds x kblocks; balanced ranges take units / G plus the hand-over of one partial tile: store, flag, load, add,
+// about four k-blocks).
+static bool fwd_prefers_balanced(int64_t M, int N, int64_t kblocks)
+{
+    const int G = tc_sm_count();
+    const int BN = N <= 64 ? 64 : 128;
+    const int64_t tiles = ((M + 127) / 128) * ((N + BN - 1) / BN);
+    const int64_t rounds = (tiles + G - 1) / G;
+    const double plain = (double)rounds * (double)kblocks, balanced = (double)(tiles * kblocks) / G + 4.0;
+    return tiles * kblocks >= 4 * (int64_t)G && balanced < tc_balance_threshold() * plain;
+}
+
+// Rows of the statistics buffer a forward launch with batch sums writes: one per CTA group and row quadrant when the
+// launch takes whole tiles (a CTA then keeps its column tile and sums over all its tiles), else one per 32 output rows.
+static int64_t fwd_stats_rows(int64_t M, int N, int64_t kblocks, bool may_balance, bool* by_cta)
+{
+    const int G = tc_sm_count();
+    const int BN = N <= 64 ? 64 : 128;
+    const int64_t nt = (N + BN - 1) / BN, tiles = ((M + 127) / 128) * nt;
+    const int64_t grid = tiles < G ? tiles : G;
+    const bool cta = nt <= grid && !(may_balance && fwd_prefers_balanced(M, N, kblocks));
+    if (by_cta) *by_cta = cta;
+    return cta ? (grid / nt) * 4 : (M + 31) / 32;
+}
 // Stride-2 data gradient of a 1x1 filter: the launch writes class (0, 0) and the zeros of the other three (TcParams::zfill).
 struct ZeroFill { int W, H; int64_t off_w, off_h; };
 
@@ -1611,15 +1692,9 @@ static int run_fwd(const FwdLaunch& f, const void* act, const void* w, const Pre
     unsigned int* sk_bank = tc_sm_count() * 4 <= TC_SYNC_FLAGS ? tc_sync_bank(st) : nullptr;
     if (sk_bank) sk_flags = (int*)sk_bank;
     {
-        const int G = tc_sm_count();
-        const int64_t tiles = (((int64_t)f.n * f.P * f.Q + 127) / 128) * ((f.N + BN - 1) / BN);
         const int64_t kblocks = (int64_t)f.kh * f.kw * (f.C / 32);
-        const int64_t rounds = (tiles + G - 1) / G;
         const bool room = base + 2 * fbytes + sk_bytes() <= (uintptr_t)ws + ws_bytes;
-        // cost in k-block units: whole tiles take rounds x kblocks; balanced ranges take units / G plus the
-        // hand-over of one partial tile (store, flag, load, add: about four k-blocks)
-        const double plain = (double)rounds * (double)kblocks, balanced = (double)(tiles * kblocks) / G + 4.0;
-        if (!filters_ready && room && tiles * kblocks >= 4 * (int64_t)G && balanced < tc_balance_threshold() * plain) sk = 1;
+        if (!filters_ready && room && fwd_prefers_balanced((int64_t)f.n * f.P * f.Q, f.N, kblocks)) sk = 1;
     }
     // The filter itself serves as the B operand when its layout allows a tensor map over it (the channel axis
     // that is contiguous decides K-major or MN-major); otherwise hi/lo copies in the GEMM layout are written first.
@@ -1676,6 +1751,9 @@ static int run_fwd(const FwdLaunch& f, const void* act, const void* w, const Pre
         // the statistics are taken from the staging slabs of the TMA-store epilogue
         if (!p.tma_store) return B2C_ERR_UNSUPPORTED;
         p.stats = stats->sums;
+        bool by_cta = false;
+        fwd_stats_rows(p.M, p.N, p.kblocks, !filters_ready, &by_cta);
+        p.stats_cta = by_cta ? 1 : 0;       // by_cta implies sk == 0: balanced ranges are only taken when preferred
     }
     if (bsrc == TCB_RAW_K) return dispatch_fwd<TCB_RAW_K>(BN, ma, mbh, mbl, mo, p, st);
     if (bsrc == TCB_RAW_MN) return dispatch_fwd<TCB_RAW_MN>(BN, ma, mbh, mbl, mo, p, st);
@@ -1808,11 +1886,11 @@ static int tc_dgrad_classes_one_launch(const Geo& g, const WStride& wsd, const v
     // launch-wide fields the kernel still reads
     p.M = p.cls_M[0]; p.P = p.cls_P[0]; p.Q = p.cls_Q[0]; p.kblocks = p.cls_kblocks[0]; p.S = p.cls_S[0];
     if (bsrc == TCB_RAW_K) {
-        if (BN == 64) return launch_tc<TCM_FWD, 64, 6, false, 2, TCB_RAW_K, false, true>(ma[0], mb, ma[1], ma[2], p, 1, st, &ma[3]);
-        return launch_tc<TCM_FWD, 128, 4, false, 2, TCB_RAW_K, false, true>(ma[0], mb, ma[1], ma[2], p, 1, st, &ma[3]);
+        if (BN == 64) return launch_tc<TCM_FWD, 64, 6, false, 2, TCB_RAW_K, 0, true>(ma[0], mb, ma[1], ma[2], p, 1, st, &ma[3]);
+        return launch_tc<TCM_FWD, 128, 4, false, 2, TCB_RAW_K, 0, true>(ma[0], mb, ma[1], ma[2], p, 1, st, &ma[3]);
     }
-    if (BN == 64) return launch_tc<TCM_FWD, 64, 6, false, 2, TCB_RAW_MN, false, true>(ma[0], mb, ma[1], ma[2], p, 1, st, &ma[3]);
-    return launch_tc<TCM_FWD, 128, 4, false, 2, TCB_RAW_MN, false, true>(ma[0], mb, ma[1], ma[2], p, 1, st, &ma[3]);
+    if (BN == 64) return launch_tc<TCM_FWD, 64, 6, false, 2, TCB_RAW_MN, 0, true>(ma[0], mb, ma[1], ma[2], p, 1, st, &ma[3]);
+    return launch_tc<TCM_FWD, 128, 4, false, 2, TCB_RAW_MN, 0, true>(ma[0], mb, ma[1], ma[2], p, 1, st, &ma[3]);
 }
 
 static int tc_dgrad_nhwc(const Geo& g, const void* dy, const void* w, void* dx, void* ws, size_t ws_bytes, cudaStream_t st)
@@ -2035,11 +2113,13 @@ static bool nchw_ws(const Geo& g, void* ws, size_t ws_bytes, NchwWs& o)
 }
 
 // Forward pass that also leaves the per-channel sums of its output for a training-mode batch norm (NHWC float32 on this
-// engine only).  Buffer: [ceil(M / 32)][2][co] floats.
+// engine only).  Buffer: [rows][2][co] floats, rows as fwd_stats_rows says.
 size_t tc_stats_bytes(const Geo& g)
 {
     if (g.layout != B2C_LAYOUT_NHWC || !tc_supported_nhwc(g, B2C_PASS_FPROP) || g.co % 4) return 0;
-    return (size_t)((g.M + 31) / 32) * 2 * g.co * sizeof(float);
+    const bool lowered = g.ci % 32 != 0;        // few-channel layers run as a 1x1 convolution over the lowered matrix
+    const int64_t kblocks = lowered ? lowered_kp(g) / 32 : (int64_t)g.kh * g.kw * (g.ci / 32);
+    return (size_t)fwd_stats_rows(g.M, g.co, kblocks, !lowered, nullptr) * 2 * g.co * sizeof(float);
 }
 
 int tc_fprop_stats(const Geo& g, const void* x, const void* w, const void* bias, void* y, void* stats, size_t stats_bytes,

@@ -14,7 +14,9 @@ sys.path.insert(0, ROOT)
 
 SLOTS = {0: "producer: waits for a free stage", 14: "producer: issues TMA", 1: "MMA: waits for a drained accumulator",
          3: "MMA: waits for the transform", 4: "MMA: issues", 5: "transform: waits for TMA data", 6: "transform: works",
-         7: "drain: waits for a finished chunk", 8: "drain: tensor-memory loads and adds", 9: "drain: epilogue"}
+         7: "drain: waits for a finished chunk", 8: "drain: tensor-memory loads, adds, epilogue arithmetic",
+         10: "drain: waits for a free staging slab", 9: "drain: staging writes, fence, store issue (or the scattered-store epilogue)",
+         11: "drain: batch statistics"}
 
 
 def main():
