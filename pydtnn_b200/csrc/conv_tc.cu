@@ -512,18 +512,23 @@ __device__ __forceinline__ void tc_epilogue_math(const TcParams& p, int nbase, f
 // Shared memory per pipeline stage: the raw A tile (activations), then the hi and lo halves of the B tile.
 // Tensor memory (512 columns): two accumulator buffers of BN columns, then per stage 64 columns holding
 // the hi and lo halves of the A tile (128 rows x 32 k).
-template <int BN, int STAGES, int SLABS, int DRAIN_WARPS = 4>
+// RESKB > 0 (resident filters): the B tiles of all k-blocks (at most RESKB) stay in shared memory for the whole launch,
+// a stage holds the A tile only, and the A slots in tensor memory (TSLOTS of them) cycle separately from the STAGES
+// shared-memory stages.
+template <int BN, int STAGES, int SLABS, int DRAIN_WARPS = 4, int RESKB = 0>
 struct TcSmem {
     static constexpr int A_BYTES = 128 * 128;   // 128 rows x 32 floats (FWD) or 32 pixels x 128 rows (WGRAD)
     static constexpr int B_BYTES = BN * 128;
-    static constexpr int STAGE_BYTES = A_BYTES + 2 * B_BYTES;
-    static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-    static constexpr int EPI_OFFSET = BAR_OFFSET + 1024;          // barriers and flags live in the first 256 bytes
+    static constexpr int STAGE_BYTES = RESKB ? A_BYTES : A_BYTES + 2 * B_BYTES;
+    static constexpr int RES_OFFSET = STAGES * STAGE_BYTES;         // resident B tiles: per k-block the raw tile, then its lo half
+    static constexpr int BAR_OFFSET = RES_OFFSET + RESKB * 2 * B_BYTES;
+    static constexpr int TSLOTS = RESKB ? (512 - 2 * BN) / 64 : STAGES;
+    static constexpr int EPI_OFFSET = BAR_OFFSET + 1024;          // barriers and flags live in the first 512 bytes
     static constexpr int EPI_BYTES = DRAIN_WARPS * SLABS * 4096;  // per drain warp: SLABS 32 x 32 float staging slabs
     static constexpr int TOTAL = EPI_OFFSET + EPI_BYTES + 1024;   // + alignment slack
     static constexpr int TMEM_A_COL = 2 * BN;                     // first column of the A slots
     static constexpr int TMEM_COLS = 512;
-    static_assert(2 * BN + STAGES * 64 <= TMEM_COLS, "tensor memory budget");
+    static_assert(2 * BN + TSLOTS * 64 <= TMEM_COLS, "tensor memory budget");
     static_assert(TOTAL <= 232448, "shared memory budget");
 };
 
@@ -583,7 +588,7 @@ constexpr int TC_STREAM8 = 2;
 template <int STREAM> constexpr int tc_drain_warps() { return STREAM == TC_STREAM8 ? 8 : 4; }
 template <int STREAM> constexpr int tc_threads() { return (6 + tc_drain_warps<STREAM>()) * 32; }
 
-template <int MODE, int BN, int STAGES, bool SK, int SLABS, int BSRC, int STREAM, bool MULTI>
+template <int MODE, int BN, int STAGES, bool SK, int SLABS, int BSRC, int STREAM, bool MULTI, int RESKB = 0>
 __global__ void __launch_bounds__(tc_threads<STREAM>(), 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b0,
                const __grid_constant__ CUtensorMap tmap_b1, const __grid_constant__ CUtensorMap tmap_out,
@@ -612,18 +617,22 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     // CTAs running at the same time share activation rows in L2).  The smem pipeline and the two TMEM
     // buffers keep running across tile boundaries: the producer prefetches the next tile while the
     // drain warps still store the previous one.
-    using L = TcSmem<BN, STAGES, SLABS, tc_drain_warps<STREAM>()>;
+    using L = TcSmem<BN, STAGES, SLABS, tc_drain_warps<STREAM>(), RESKB>;
     constexpr int DW = tc_drain_warps<STREAM>();
+    constexpr int TSLOTS = L::TSLOTS;
+    static_assert(RESKB == 0 || (STREAM == TC_STREAM8 && BSRC != TCB_SPLIT), "resident filters: short-K streaming variant on the caller's filter");
     // STREAM variants serve tiles of at most TC_CHUNK k-blocks with dense outputs (see dispatch_fwd)
     static_assert(STREAM == 0 || (MODE == TCM_FWD && !SK), "the streaming epilogue is a whole-tile forward variant");
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* full_bar = (uint64_t*)(smem + L::BAR_OFFSET);
     uint64_t* xform_bar = full_bar + STAGES;
-    uint64_t* empty_bar = xform_bar + STAGES;
-    uint64_t* tfull_bar = empty_bar + STAGES;
+    uint64_t* empty_bar = xform_bar + TSLOTS;
+    uint64_t* tfull_bar = empty_bar + TSLOTS;
     uint64_t* tempty_bar = tfull_bar + 2;
-    uint32_t* tmem_slot = (uint32_t*)(tempty_bar + 2);
+    uint64_t* afree_bar = tempty_bar + 2;              // RESKB: the transform warps have read the stage's A tile
+    uint64_t* bres_bar = afree_bar + STAGES;           // RESKB: the resident B tiles have landed
+    uint32_t* tmem_slot = (uint32_t*)(bres_bar + 1);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -638,7 +647,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if (MULTI) { if (p.ncls > 1) tma_prefetch_map(&tmap_b1); if (p.ncls > 2) tma_prefetch_map(&tmap_out); if (p.ncls > 3) tma_prefetch_map(&tmap_a3); }
     }
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&xform_bar[s], 4); mbar_init(&empty_bar[s], 1); }
+        for (int s = 0; s < STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&afree_bar[s], 4); }
+        for (int s = 0; s < TSLOTS; s++) { mbar_init(&xform_bar[s], 4); mbar_init(&empty_bar[s], 1); }
+        mbar_init(bres_bar, 1);
         for (int b = 0; b < 2; b++) { mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], DW); }
         *abort_flag = 0;
         fence_barrier_init();
@@ -659,6 +670,28 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         // the barrier and issues the boxes of the k-block.
         int it = 0;
         bool ok = true;
+        if (RESKB) {
+            // The grid is a multiple of the column-tile count: this CTA only meets column tile blockIdx.x % nt, whose
+            // filter tiles (all k-blocks) are fetched once.
+            const int n0r = (int)(blockIdx.x % nt) * BN;
+            if (elect_one_sync()) {
+                mbar_expect_tx(bres_bar, (uint32_t)(p.kblocks * L::B_BYTES));
+                for (int kb = 0; kb < p.kblocks; kb++) {
+                    const int tap = kb / p.cblocks, cb = kb - tap * p.cblocks;
+                    const int r = tap / p.S, sx = tap - r * p.S;
+                    const int tap_real = (p.tap_r0 + p.tap_rstep * r) * p.tap_sreal + p.tap_s0 + p.tap_sstep * sx;
+                    uint8_t* dst = smem + L::RES_OFFSET + kb * 2 * L::B_BYTES;
+                    if (BSRC == TCB_RAW_K) {
+                        tma_load_3d(dst, &tmap_b0, bres_bar, cb * 32, tap_real, n0r);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BN / 32; j++)       // boxes past N are zero-filled by the TMA unit
+                            tma_load_3d(dst + j * 4096, &tmap_b0, bres_bar, n0r + 32 * j, tap_real, cb * 32);
+                    }
+                }
+            }
+            __syncwarp();
+        }
         TileWalk w;
         w.init(total_tiles, p.kblocks);
         while (ok && w.template next<SK>()) {
@@ -698,7 +731,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 const int s = it % STAGES, use = it / STAGES;
                 TC_PROF_T0();
                 bool good = true;
-                if (use > 0) good = mbar_wait(&empty_bar[s], (use - 1) & 1, abort_flag, &g_tc_status, TC_ERR_EMPTY);
+                // a stage is free when the MMAs that read it have completed; with resident filters, as soon as the
+                // transform warps have copied its A tile to tensor memory
+                if (use > 0) good = mbar_wait(RESKB ? &afree_bar[s] : &empty_bar[s], (use - 1) & 1, abort_flag, &g_tc_status, TC_ERR_EMPTY);
                 good = __all_sync(0xffffffffu, good);
                 if (lane == 0) TC_PROF_ADD(0);    // producer: waiting for a free stage
                 if (!good) { ok = false; break; }
@@ -712,10 +747,12 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         else
 #endif
                         {
-                            mbar_expect_tx(&full_bar[s], (uint32_t)(BSRC == TCB_SPLIT ? L::STAGE_BYTES : L::A_BYTES + L::B_BYTES));
+                            mbar_expect_tx(&full_bar[s], (uint32_t)(RESKB ? L::A_BYTES : BSRC == TCB_SPLIT ? L::STAGE_BYTES : L::A_BYTES + L::B_BYTES));
                             tma_load_im2col_4d(st, tg.ma, &full_bar[s], cb * 32, base_w, base_h, img,
                                                (uint16_t)(sx * p.dil_w), (uint16_t)(r * p.dil_h));
-                            if (BSRC == TCB_SPLIT) {
+                            if (RESKB) {
+                                // the filter tiles are resident
+                            } else if (BSRC == TCB_SPLIT) {
                                 tma_load_2d(st + L::A_BYTES, &tmap_b0, &full_bar[s], kb * 32, n0);
                                 tma_load_2d(st + L::A_BYTES + L::B_BYTES, &tmap_b1, &full_bar[s], kb * 32, n0);
                             } else {
@@ -779,7 +816,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             while (ok && w.template next<SK>()) {
                 if (MULTI) w.kb_e = tile_geo(w.tile).kblocks;
                 for (int kb = w.kb_b; kb < w.kb_e && ok; kb++, it++) {
-                    const int s = it % STAGES, use = it / STAGES;
+                    const int s = it % TSLOTS, use = it / TSLOTS;        // A slot in tensor memory (= the stage, unless the filters are resident)
                     const int b = gc & 1;
                     const bool chunk_start = ((kb - w.kb_b) % TC_CHUNK) == 0;
                     const bool chunk_end = ((kb - w.kb_b) % TC_CHUNK) == TC_CHUNK - 1 || kb == w.kb_e - 1;
@@ -793,9 +830,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     if (lane == 0) TC_PROF_ADD(3);    // MMA: waiting for the transform
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t sa = smem_u32(smem + s * L::STAGE_BYTES);
-                    const uint64_t b_hi = make_smem_desc(sa + L::A_BYTES, LBO, SBO, LAYOUT);
-                    const uint64_t b_lo = make_smem_desc(sa + L::A_BYTES + L::B_BYTES, LBO, SBO, LAYOUT);
+                    const uint32_t sb = RESKB ? smem_u32(smem + L::RES_OFFSET + kb * 2 * L::B_BYTES) : smem_u32(smem + s * L::STAGE_BYTES) + L::A_BYTES;
+                    const uint64_t b_hi = make_smem_desc(sb, LBO, SBO, LAYOUT);
+                    const uint64_t b_lo = make_smem_desc(sb + L::B_BYTES, LBO, SBO, LAYOUT);
                     const uint32_t a_hi = tmem_base + (uint32_t)(L::TMEM_A_COL + s * 64);
                     const uint32_t a_lo = a_hi + 32;
                     const uint32_t d = tmem_base + (uint32_t)(b * BN);
@@ -837,6 +874,27 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const int t = threadIdx.x - 64;              // 0..127
         int it = 0;
         bool ok = true;
+        if (RESKB) {
+            // the lo halves of the resident filter tiles, once per launch
+            ok = mbar_wait(bres_bar, 0, abort_flag, &g_tc_status, TC_ERR_FULL);
+            if (ok) {
+                for (int kb = 0; kb < p.kblocks; kb++) {
+                    const float4* b_hi = (const float4*)(smem + L::RES_OFFSET + kb * 2 * L::B_BYTES);
+                    float4* b_lo = (float4*)(smem + L::RES_OFFSET + kb * 2 * L::B_BYTES + L::B_BYTES);
+#pragma unroll
+                    for (int i = 0; i < L::B_BYTES / 16 / 128; i++) {
+                        const float4 q = b_hi[t + i * 128];
+                        float4 l;
+                        l.x = q.x - __uint_as_float(__float_as_uint(q.x) & 0xFFFFE000u);
+                        l.y = q.y - __uint_as_float(__float_as_uint(q.y) & 0xFFFFE000u);
+                        l.z = q.z - __uint_as_float(__float_as_uint(q.z) & 0xFFFFE000u);
+                        l.w = q.w - __uint_as_float(__float_as_uint(q.w) & 0xFFFFE000u);
+                        b_lo[t + i * 128] = l;
+                    }
+                }
+                fence_proxy_async();
+            }
+        }
         TileWalk w;
         w.init(total_tiles, p.kblocks);
         while (ok && w.template next<SK>()) {
@@ -853,8 +911,12 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 if (!mbar_wait(&full_bar[s], use & 1, abort_flag, &g_tc_status, TC_ERR_FULL)) { ok = false; break; }
                 if (t == 0) TC_PROF_ADD(5);    // transform: waiting for TMA data
                 const uint8_t* st = smem + s * L::STAGE_BYTES;
+                // the A slot in tensor memory: the stage's own, or (resident filters) the next of a separate ring that
+                // is free once the MMAs that read it have completed
+                const int ts = it % TSLOTS, tuse = it / TSLOTS;
+                if (RESKB && tuse > 0 && !mbar_wait(&empty_bar[ts], (tuse - 1) & 1, abort_flag, &g_tc_status, TC_ERR_EMPTY)) { ok = false; break; }
 #ifdef B2C_TC_DEV
-                if (p.dbg & 4) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(&xform_bar[s]); continue; }
+                if (p.dbg & 4) { tc_fence_before(); __syncwarp(); if (lane == 0) { if (RESKB) mbar_arrive(&afree_bar[s]); mbar_arrive(&xform_bar[ts]); } continue; }
 #endif
                 uint32_t v[32], h[32];
                 if (MODE == TCM_FWD) {
@@ -871,14 +933,19 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll
                     for (int k = 0; k < 32; k++) v[k] = a_col[k * 32];
                 }
+                if (RESKB) {
+                    // the A tile is in registers: the producer may refill the stage
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&afree_bar[s]);
+                }
 #pragma unroll
                 for (int j = 0; j < 32; j++) h[j] = v[j] & 0xFFFFE000u;
-                const uint32_t slot = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(L::TMEM_A_COL + s * 64);
+                const uint32_t slot = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(L::TMEM_A_COL + ts * 64);
                 tmem_st_32x32(slot, h);
 #pragma unroll
                 for (int j = 0; j < 32; j++) v[j] = __float_as_uint(__uint_as_float(v[j]) - __uint_as_float(h[j]));
                 tmem_st_32x32(slot + 32, v);
-                if (SPLIT_B) {
+                if (SPLIT_B && RESKB == 0) {
                     const float4* b_hi = (const float4*)(st + L::A_BYTES);
                     float4* b_lo = (float4*)(smem + s * L::STAGE_BYTES + L::A_BYTES + L::B_BYTES);
 #pragma unroll
@@ -897,7 +964,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 tmem_st_wait();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&xform_bar[s]);
+                if (lane == 0) mbar_arrive(&xform_bar[ts]);
                 if (t == 0) TC_PROF_ADD(6);    // transform: work
             }
             if (MODE == TCM_WGRAD && do_db && ok) {
@@ -1544,14 +1611,14 @@ static size_t tc_workspace_bytes_nhwc(const Geo& g, int pass)
            align_up((size_t)pl.splits * 4 * g.co * sizeof(float), 1024);
 }
 
-template <int MODE, int BN, int STAGES, bool SK, int SLABS, int BSRC, int STREAM = 0, bool MULTI = false>
+template <int MODE, int BN, int STAGES, bool SK, int SLABS, int BSRC, int STREAM = 0, bool MULTI = false, int RESKB = 0>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb0, const CUtensorMap& mb1, const CUtensorMap& mo, const TcParams& p, int splits, cudaStream_t st,
                      const CUtensorMap* ma3 = nullptr)
 {
-    using L = TcSmem<BN, STAGES, SLABS, tc_drain_warps<STREAM>()>;
+    using L = TcSmem<BN, STAGES, SLABS, tc_drain_warps<STREAM>(), RESKB>;
     static PerDeviceOnce attr;
     {
-        cudaError_t e = attr.run([] { return cudaFuncSetAttribute(conv_tc_kernel<MODE, BN, STAGES, SK, SLABS, BSRC, STREAM, MULTI>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL); });
+        cudaError_t e = attr.run([] { return cudaFuncSetAttribute(conv_tc_kernel<MODE, BN, STAGES, SK, SLABS, BSRC, STREAM, MULTI, RESKB>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL); });
         if (e != cudaSuccess) { set_cuda_error(e, "cudaFuncSetAttribute(conv_tc_kernel)"); return B2C_ERR_CUDA; }
     }
     const int sm_count = tc_sm_count();
@@ -1563,8 +1630,8 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb0, const CUtens
     { const char* e = getenv("B2C_TC_DBG"); q.dbg = e ? atoi(e) : 0; }
 #endif
     int grid = q.sk ? sm_count : (int)(tiles < sm_count ? tiles : sm_count);     // one persistent CTA per SM
-    if (q.stats && q.stats_cta) grid -= grid % ((p.N + BN - 1) / BN);               // a CTA keeps its column tile
-    launch_pdl(conv_tc_kernel<MODE, BN, STAGES, SK, SLABS, BSRC, STREAM, MULTI>, grid, tc_threads<STREAM>(), L::TOTAL, st, ma, mb0, mb1, mo, ma3 ? *ma3 : ma, q);
+    if ((q.stats && q.stats_cta) || RESKB) grid -= grid % ((p.N + BN - 1) / BN);    // a CTA keeps its column tile
+    launch_pdl(conv_tc_kernel<MODE, BN, STAGES, SK, SLABS, BSRC, STREAM, MULTI, RESKB>, grid, tc_threads<STREAM>(), L::TOTAL, st, ma, mb0, mb1, mo, ma3 ? *ma3 : ma, q);
     return check_launch("conv_tc_kernel");
 }
 
@@ -1579,6 +1646,17 @@ static int dispatch_fwd(int bn, const CUtensorMap& ma, const CUtensorMap& mb0, c
     // streaming epilogue (32 columns at a time straight from tensor memory); up to four k-blocks per tile a shallower
     // operand pipeline also leaves room for four output slabs per drain warp, so a whole tile's stores are in flight.
     if (p.kblocks <= 4 && p.tma_store) {
+        if constexpr (BSRC != TCB_SPLIT) {
+            // The filter tiles of a column tile are a few tens of KB: they stay in shared memory for the whole launch
+            // (a CTA keeps one column tile), the ring holds activations only and runs further ahead.
+            const int nt = (p.N + bn - 1) / bn;
+            const int64_t tiles = (int64_t)((p.M + 127) / 128) * nt;
+            if (tiles >= nt && nt <= tc_sm_count()) {
+                if (bn == 64) return launch_tc<TCM_FWD, 64, 6, false, 2, BSRC, TC_STREAM8, false, 4>(ma, mb0, mb1, mo, p, 1, st);
+                if (p.kblocks <= 2) return launch_tc<TCM_FWD, 128, 6, false, 2, BSRC, TC_STREAM8, false, 2>(ma, mb0, mb1, mo, p, 1, st);
+                return launch_tc<TCM_FWD, 128, 4, false, 1, BSRC, TC_STREAM8, false, 4>(ma, mb0, mb1, mo, p, 1, st);
+            }
+        }
         if (bn == 64) return launch_tc<TCM_FWD, 64, 4, false, 2, BSRC, TC_STREAM8>(ma, mb0, mb1, mo, p, 1, st);
         return launch_tc<TCM_FWD, 128, 3, false, 2, BSRC, TC_STREAM8>(ma, mb0, mb1, mo, p, 1, st);
     }
