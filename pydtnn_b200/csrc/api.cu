@@ -163,6 +163,10 @@ extern "C" size_t b2c_fc_workspace_bytes(int dtype, int batch, int in_f, int out
         size_t b = e == B2C_ENGINE_TENSOR ? tc_workspace_bytes(g, pass) : fma_workspace_bytes(g, pass);
         if (b > m) m = b;
     }
+    if (tc_fc_small_batch(dtype, engine, batch, in_f, out_f)) {
+        size_t b = tc_fc_small_batch_bytes(batch, in_f, out_f);
+        if (b > m) m = b;
+    }
     return m;
 }
 
@@ -170,6 +174,8 @@ extern "C" int b2c_fc_forward(int dtype, int engine, int batch, int in_f, int ou
                               const void* bias, void* y, void* ws, size_t ws_bytes, void* stream) {
     Geo g; int rc = fc_geo(dtype, engine, batch, in_f, out_f, g); if (rc) return rc;
     if (!x || !w || !y) return B2C_ERR_NULL_POINTER;
+    if (tc_fc_small_batch(dtype, engine, batch, in_f, out_f))
+        return tc_fc_forward_small_batch(batch, in_f, out_f, x, w, bias, y, ws, ws_bytes, (cudaStream_t)stream);
     int e; rc = pick_engine(g, B2C_PASS_FPROP, e); if (rc) return rc;
     if (e == B2C_ENGINE_TENSOR) return tc_fprop(g, x, w, bias, nullptr, 0, y, ws, ws_bytes, (cudaStream_t)stream);
     return fma_fprop(g, x, w, bias, nullptr, 0, y, ws, ws_bytes, (cudaStream_t)stream);
@@ -180,6 +186,20 @@ extern "C" int b2c_fc_backward(int dtype, int engine, int batch, int in_f, int o
     Geo g; int rc = fc_geo(dtype, engine, batch, in_f, out_f, g); if (rc) return rc;
     if (!dy) return B2C_ERR_NULL_POINTER;
     cudaStream_t st = (cudaStream_t)stream;
+    if (tc_fc_small_batch(dtype, engine, batch, in_f, out_f)) {
+        if (dw) {
+            if (!x) return B2C_ERR_NULL_POINTER;
+            rc = tc_fc_wgrad_small_batch(batch, in_f, out_f, x, dy, dw, db, ws, ws_bytes, st); if (rc) return rc;
+        } else if (db) {
+            if (!ws || ws_bytes < channel_sum_workspace_bytes(batch, out_f, 1)) return B2C_ERR_WORKSPACE_TOO_SMALL;
+            rc = channel_sum(dtype, B2C_LAYOUT_NHWC, batch, out_f, 1, dy, db, ws, ws_bytes, st); if (rc) return rc;
+        }
+        if (dx) {
+            if (!w) return B2C_ERR_NULL_POINTER;
+            rc = tc_fc_dgrad_small_batch(batch, in_f, out_f, dy, w, dx, ws, ws_bytes, st);
+        }
+        return rc;
+    }
     if (dw) {
         if (!x) return B2C_ERR_NULL_POINTER;
         int e; rc = pick_engine(g, B2C_PASS_WGRAD, e); if (rc) return rc;

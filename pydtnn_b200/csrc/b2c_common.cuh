@@ -118,6 +118,13 @@ int tc_wgrad(const Geo& g, const void* x, const void* dy, void* dw, void* db, vo
 int tc_read_status(int* out);
 bool tc_keeps_lowered(const Geo& g);
 int tc_wgrad_lowered(const Geo& g, const void* x, const void* dy, void* dw, void* db, void* ws, size_t ws_bytes, cudaStream_t st);
+bool tc_fc_small_batch(int dtype, int engine, int batch, int in_f, int out_f);
+size_t tc_fc_small_batch_bytes(int batch, int in_f, int out_f);
+int tc_fc_forward_small_batch(int batch, int in_f, int out_f, const void* x, const void* w, const void* bias, void* y,
+                              void* ws, size_t ws_bytes, cudaStream_t st);
+int tc_fc_dgrad_small_batch(int batch, int in_f, int out_f, const void* dy, const void* w, void* dx, void* ws, size_t ws_bytes, cudaStream_t st);
+int tc_fc_wgrad_small_batch(int batch, int in_f, int out_f, const void* x, const void* dy, void* dw, void* db, void* ws, size_t ws_bytes,
+                            cudaStream_t st);
 size_t tc_stats_bytes(const Geo& g);
 int tc_fprop_stats(const Geo& g, const void* x, const void* w, const void* bias, void* y, void* stats, size_t stats_bytes,
                    void* ws, size_t ws_bytes, cudaStream_t st);

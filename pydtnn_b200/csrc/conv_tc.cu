@@ -2258,6 +2258,110 @@ int tc_wgrad(const Geo& g, const void* x, const void* dy, void* dw, void* db, vo
     return tc_wgrad_nhwc(as_nhwc(g), t.a, t.b, dw, db, t.inner, t.inner_bytes, st);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Fully connected layers with a small batch (pydtnn/backends/gpu/layers/fc_gpu.py:54-94: y = x w + b, dw = x^T dy,
+// dx = dy w^T, w stored (in, out))
+// ---------------------------------------------------------------------------------------------
+// With 32-128 rows in x every pass is a stream over the (in, out) weight matrix.  As a 1x1 convolution over `batch`
+// pixels the batch is the GEMM row axis and fills a fraction of each 128-row MMA; here the weight matrix takes that
+// axis instead: it is read as an activation tensor of `in` pixels with `out` channels, and the batch becomes the
+// narrow column axis.
+//   forward   y (batch, out)  = weight-gradient form: "x" = w (in pixels x out channels), "dy" = x^T (in x batch),
+//                               result in (co = batch, ci = out) filter layout = y; then the bias.
+//   dx        dx^T (in, batch) = forward form over w with dy (batch, out) as the (co, ci) filter; then transposed.
+//   dw        dw (in, out)    = forward form over x^T (in pixels x batch channels) with dy as the (ci, co) filter.
+// x^T and dx^T are batch x in floats: small copies beside one pass over the weights.
+static Geo fc_pixels_view(int pixels, int ci, int co, int w_layout)
+{
+    Geo q{};
+    q.layout = B2C_LAYOUT_NHWC; q.dtype = B2C_F32; q.w_layout = w_layout; q.engine = B2C_ENGINE_TENSOR;
+    q.n = 1; q.h = pixels; q.w = 1; q.ci = ci; q.co = co; q.kh = q.kw = 1;
+    q.vstr = q.hstr = q.vdil = q.hdil = 1;
+    q.ho = pixels; q.wo = 1; q.M = pixels; q.K = ci;
+    return q;
+}
+
+bool tc_fc_small_batch(int dtype, int engine, int batch, int in_f, int out_f)
+{
+    if (dtype != B2C_F32 || engine == B2C_ENGINE_FMA) return false;
+    if (batch > 128 || batch % 32 || out_f % 32 || in_f % 4) return false;
+    return (int64_t)in_f * out_f >= (1 << 22);          // a weight matrix of at least 16 MB
+}
+
+__global__ void fc_add_bias_kernel(float4* __restrict__ y, const float4* __restrict__ bias, int rows, int cols4)
+{
+    pdl_prologue();
+    const int64_t total = (int64_t)rows * cols4;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        float4 v = y[i];
+        const float4 b = bias[i % cols4];
+        v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+        y[i] = v;
+    }
+}
+
+size_t tc_fc_small_batch_bytes(int batch, int in_f, int out_f)
+{
+    const size_t copy = act_bytes(1, in_f, 1, batch);               // x^T or dx^T
+    size_t inner = tc_workspace_bytes_nhwc(fc_pixels_view(in_f, out_f, batch, B2C_W_KRSC), B2C_PASS_WGRAD);
+    size_t b = tc_workspace_bytes_nhwc(fc_pixels_view(in_f, out_f, batch, B2C_W_KRSC), B2C_PASS_FPROP);
+    if (b > inner) inner = b;
+    b = tc_workspace_bytes_nhwc(fc_pixels_view(in_f, batch, out_f, B2C_W_CRSK), B2C_PASS_FPROP);
+    if (b > inner) inner = b;
+    b = channel_sum_workspace_bytes(batch, out_f, 1);
+    if (b > inner) inner = b;
+    return copy + inner + 2048;
+}
+
+// Splits the caller's workspace into the transposed copy and the rest.
+static bool fc_ws(int batch, int in_f, void* ws, size_t ws_bytes, float** copy, void** inner, size_t* inner_bytes)
+{
+    if (!ws) return false;
+    const uintptr_t base = align_up((uintptr_t)ws, 1024);
+    const size_t cb = act_bytes(1, in_f, 1, batch);
+    if (base + cb > (uintptr_t)ws + ws_bytes) return false;
+    *copy = (float*)base; *inner = (void*)(base + cb); *inner_bytes = (uintptr_t)ws + ws_bytes - (base + cb);
+    return true;
+}
+
+int tc_fc_forward_small_batch(int batch, int in_f, int out_f, const void* x, const void* w, const void* bias, void* y,
+                              void* ws, size_t ws_bytes, cudaStream_t st)
+{
+    float* xt; void* inner; size_t inner_bytes;
+    if (!fc_ws(batch, in_f, ws, ws_bytes, &xt, &inner, &inner_bytes)) return B2C_ERR_WORKSPACE_TOO_SMALL;
+    if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)y | (uintptr_t)bias) & 15) return B2C_ERR_MISALIGNED;
+    int rc = transpose_inner(x, xt, 1, batch, in_f, st);                        // (batch, in) -> (in, batch)
+    if (rc) return rc;
+    rc = tc_wgrad_nhwc(fc_pixels_view(in_f, out_f, batch, B2C_W_KRSC), w, xt, y, nullptr, inner, inner_bytes, st);
+    if (rc || !bias) return rc;
+    const int64_t total4 = (int64_t)batch * out_f / 4;
+    launch_pdl(fc_add_bias_kernel, (int)((total4 + 255) / 256 < 1184 ? (total4 + 255) / 256 : 1184), 256, 0, st, (float4*)y, (const float4*)bias, batch, out_f / 4);
+    return check_launch("fc_add_bias_kernel");
+}
+
+int tc_fc_dgrad_small_batch(int batch, int in_f, int out_f, const void* dy, const void* w, void* dx, void* ws, size_t ws_bytes, cudaStream_t st)
+{
+    float* dxt; void* inner; size_t inner_bytes;
+    if (!fc_ws(batch, in_f, ws, ws_bytes, &dxt, &inner, &inner_bytes)) return B2C_ERR_WORKSPACE_TOO_SMALL;
+    if (((uintptr_t)dy | (uintptr_t)w | (uintptr_t)dx) & 15) return B2C_ERR_MISALIGNED;
+    int rc = tc_fprop_nhwc(fc_pixels_view(in_f, out_f, batch, B2C_W_KRSC), w, dy, nullptr, nullptr, 0, dxt, inner, inner_bytes, st);
+    if (rc) return rc;
+    return transpose_inner(dxt, dx, 1, in_f, batch, st);                        // (in, batch) -> (batch, in)
+}
+
+int tc_fc_wgrad_small_batch(int batch, int in_f, int out_f, const void* x, const void* dy, void* dw, void* db, void* ws, size_t ws_bytes,
+                            cudaStream_t st)
+{
+    float* xt; void* inner; size_t inner_bytes;
+    if (!fc_ws(batch, in_f, ws, ws_bytes, &xt, &inner, &inner_bytes)) return B2C_ERR_WORKSPACE_TOO_SMALL;
+    if (((uintptr_t)x | (uintptr_t)dy | (uintptr_t)dw) & 15) return B2C_ERR_MISALIGNED;
+    int rc = transpose_inner(x, xt, 1, batch, in_f, st);
+    if (rc) return rc;
+    rc = tc_fprop_nhwc(fc_pixels_view(in_f, batch, out_f, B2C_W_CRSK), xt, dy, nullptr, nullptr, 0, dw, inner, inner_bytes, st);
+    if (rc || !db) return rc;
+    return channel_sum(B2C_F32, B2C_LAYOUT_NHWC, batch, out_f, 1, dy, db, inner, inner_bytes, st);
+}
+
 #ifdef B2C_TC_PROFILE
 extern "C" int b2c_debug_prof(long long* out, int reset)
 {

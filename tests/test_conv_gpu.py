@@ -163,8 +163,11 @@ def test_fc_against_reference_golden_and_oracle(dtype):
     ref = np.load(os.path.join(GOLD, "fc_ref.npz"))
     cases = [tuple(ref[f"f{i}_{dtype}_{n}"] for n in ("x", "w", "b", "dy", "y", "dw", "db", "dx")) for i in range(3)]
     rng = np.random.Generator(np.random.PCG64(3))
-    # the last two: tensor-core forward and input gradient; partial tiles and a ragged batch in the dense dw kernel
-    for (bsz, fin, fout) in ((64, 2048, 1000), (32, 1000, 4096), (5, 7, 3), (64, 4096, 2048), (21, 200, 132)):
+    # tensor-core forward and input gradient; partial tiles and a ragged batch in the dense dw kernel; the last three take
+    # the small-batch route (the weight matrix on the GEMM row axis): whole tiles, an input count that is not a multiple
+    # of a k-block, an output count that is not a multiple of a tile, batches of 32 / 64 / 96
+    for (bsz, fin, fout) in ((64, 2048, 1000), (32, 1000, 4096), (5, 7, 3), (21, 200, 132),
+                             (64, 4096, 2048), (32, 2052, 4096), (96, 2048, 2080)):
         x = rng.standard_normal((bsz, fin)).astype(dtype)
         w = (rng.standard_normal((fin, fout)) / np.sqrt(fin)).astype(dtype)
         b = rng.standard_normal((fout,)).astype(dtype)
