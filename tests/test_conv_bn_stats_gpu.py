@@ -19,7 +19,12 @@ pytestmark = pytest.mark.gpu
 # 64- and 128-wide column tiles, the balanced mode (14x14x256 3x3 at batch 64) and a few-channel stem
 SHAPES = [(3, 10, 10, 32, 64, 3, 1, 1), (4, 16, 16, 64, 256, 1, 1, 0), (8, 28, 28, 128, 128, 3, 2, 1),
           (64, 14, 14, 256, 256, 3, 1, 1), (16, 56, 56, 64, 256, 1, 1, 0), (2, 9, 9, 32, 2048, 1, 1, 0),
-          (4, 40, 40, 3, 64, 7, 2, 3)]
+          (4, 40, 40, 3, 64, 7, 2, 3),
+          # sums kept per CTA over many tiles (more row tiles than SMs), a half-empty column tile, ragged rows, six column
+          # tiles (a grid of 144 CTAs); the batch norm's fast path takes channel counts 4..128, 256 and multiples of 256
+          (3, 91, 91, 64, 32, 1, 1, 0), (2, 29, 31, 96, 128, 1, 1, 0), (2, 40, 40, 128, 768, 1, 1, 0),
+          # long K with whole tiles: the chunked drain's per-CTA sums (25 row tiles x 2 column tiles)
+          (4, 28, 28, 256, 256, 3, 1, 1)]
 
 
 def _conv_and_bn(g, x, w_krsc, b, gamma, beta, fused, relu, addend):

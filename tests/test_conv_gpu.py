@@ -88,6 +88,13 @@ PARITY_SHAPES = {
     # the CTAs and tiles are shared by 2 (first case) or about 6 (second case) consecutive CTAs
     "balanced_160_tiles_9_kblocks": co.Geom(5, 64, 64, 32, 128, 3, 3, 1, 1, 1, 1),
     "balanced_50_tiles_72_kblocks": co.Geom(16, 14, 14, 256, 256, 3, 3, 1, 1, 1, 1),
+    # short K loops (1-4 k-blocks: eight drain warps, filter tiles resident in shared memory, a grid that is a multiple
+    # of the column-tile count): a ragged last row tile, a half-empty last column tile (192 = 128 + 64), three and one
+    # k-blocks, a 64-wide and a 96-wide output; more row tiles than SMs in the first (every CTA walks several tiles)
+    "short_k_2kb_ragged_rows_192_cols": co.Geom(3, 91, 91, 64, 192, 1, 1, 0, 0, 1, 1),
+    "short_k_3kb_96_cols": co.Geom(2, 29, 31, 96, 96, 1, 1, 0, 0, 1, 1),
+    "short_k_1kb_64_cols": co.Geom(5, 20, 20, 32, 64, 1, 1, 0, 0, 1, 1),
+    "short_k_4kb_5_column_tiles": co.Geom(2, 40, 40, 128, 640, 1, 1, 0, 0, 1, 1),
 }
 
 
