@@ -413,6 +413,7 @@ struct TcParams {
     int str_h, str_w, dil_h, dil_w;
     int low_h, low_w;          // lower corner of the im2col window (= -padding for a plain convolution)
     int Mpix;                  // WGRAD: total pixels
+    int a_box_log2;            // WGRAD: log2 of the channels per x box (32, 64 or 128: the widest that divides C)
     int splits;                // WGRAD: pixel ranges (1 for FWD)
     // FWD epilogue
     const float *bias, *mean, *inv_std, *gamma, *beta;
@@ -707,24 +708,25 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 const int p0 = rem / tg.Q, q0 = rem - p0 * tg.Q;
                 base_w = q0 * p.str_w + tg.low_w; base_h = p0 * p.str_h + tg.low_h;
             }
-            // WGRAD: the tile's boxes are fixed: up to four x boxes (32 rows of (tap, ci) each) and BN/32 dy
-            // boxes (32 output channels each)
+            // WGRAD: the tile's boxes are fixed: up to four x boxes (32, 64 or 128 rows of (tap, ci) each: a box stays
+            // inside one tap because its width divides C) and BN/32 dy boxes (32 output channels each)
             int box_c0[4] = {0, 0, 0, 0}, box_offw[4] = {0, 0, 0, 0}, box_offh[4] = {0, 0, 0, 0};
-            int boxes = 0;
+            uint32_t tx_bytes = 0;
+            const int a_box = 1 << p.a_box_log2;
             if (MODE == TCM_WGRAD) {
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
-                    const int mrow = m0 + 32 * j;
-                    if (mrow < p.M) {
+                    const int mrow = m0 + a_box * j;
+                    if (a_box * j < 128 && mrow < p.M) {
                         const int tap = mrow / p.C;
                         box_c0[j] = mrow - tap * p.C;
                         const int r = tap / p.S, sx = tap - r * p.S;
                         box_offw[j] = sx * p.dil_w; box_offh[j] = r * p.dil_h;
-                        boxes++;
+                        tx_bytes += (uint32_t)a_box * 128u;
                     }
                 }
 #pragma unroll
-                for (int j = 0; j < BN / 32; j++) if (n0 + 32 * j < p.N) boxes++;
+                for (int j = 0; j < BN / 32; j++) if (n0 + 32 * j < p.N) tx_bytes += 4096u;
             }
             const int pix_begin = (MODE == TCM_WGRAD) ? z * p.kblocks * 32 : 0;
             for (int kb = w.kb_b; kb < w.kb_e; kb++, it++) {
@@ -779,11 +781,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         else
 #endif
                         {
-                        mbar_expect_tx(&full_bar[s], (uint32_t)(boxes * 4096));
+                        mbar_expect_tx(&full_bar[s], tx_bytes);
 #pragma unroll
                         for (int j = 0; j < 4; j++)
-                            if (m0 + 32 * j < p.M)
-                                tma_load_im2col_4d(st + j * 4096, &tmap_a, &full_bar[s], box_c0[j], cw, chh, im,
+                            if (a_box * j < 128 && m0 + a_box * j < p.M)
+                                tma_load_im2col_4d(st + j * (a_box * 128), &tmap_a, &full_bar[s], box_c0[j], cw, chh, im,
                                                    (uint16_t)box_offw[j], (uint16_t)box_offh[j]);
 #pragma unroll
                         for (int j = 0; j < BN / 32; j++)
@@ -928,10 +930,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         v[4 * c] = q.x; v[4 * c + 1] = q.y; v[4 * c + 2] = q.z; v[4 * c + 3] = q.w;
                     }
                 } else {
-                    // unswizzled boxes of [32 pixels][32 rows]: this thread's row is column `lane` of box `quad`
-                    const uint32_t* a_col = reinterpret_cast<const uint32_t*>(st + quad * 4096) + lane;
+                    // unswizzled boxes of [32 pixels][a_box rows]: this thread's row is a column of its box
+                    const int a_box = 1 << p.a_box_log2;
+                    const uint32_t* a_col = reinterpret_cast<const uint32_t*>(st + (row >> p.a_box_log2) * (a_box * 128)) + (row & (a_box - 1));
 #pragma unroll
-                    for (int k = 0; k < 32; k++) v[k] = a_col[k * 32];
+                    for (int k = 0; k < 32; k++) v[k] = a_col[k * a_box];
                 }
                 if (RESKB) {
                     // the A tile is in registers: the producer may refill the stage
@@ -1437,7 +1440,7 @@ static bool make_map_2d(CUtensorMap* map, const void* base, uint64_t rows, uint6
 // `cnt_h` x `cnt_w` positions per image before the traversal stride is applied. Corners in (w, h) order.
 static bool make_map_im2col(CUtensorMap* map, const void* base, int n, int h, int w, int c, int low_h, int low_w,
                             int cnt_h, int cnt_w, int str_h, int str_w, uint32_t pixels,
-                            CUtensorMapSwizzle swz = CU_TENSOR_MAP_SWIZZLE_128B)
+                            CUtensorMapSwizzle swz = CU_TENSOR_MAP_SWIZZLE_128B, uint32_t channels = 32)
 {
     cuuint64_t dims[4] = {(cuuint64_t)c, (cuuint64_t)w, (cuuint64_t)h, (cuuint64_t)n};
     cuuint64_t strides[3] = {(cuuint64_t)c * 4, (cuuint64_t)w * c * 4, (cuuint64_t)h * w * c * 4};
@@ -1446,7 +1449,7 @@ static bool make_map_im2col(CUtensorMap* map, const void* base, int n, int h, in
     for (int i = 0; i < 2; i++) if (lower[i] < -128 || lower[i] > 127 || upper[i] < -128 || upper[i] > 127) return false;
     cuuint32_t estr[4] = {1, (cuuint32_t)str_w, (cuuint32_t)str_h, 1};
     return g_encode_im2col(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void*>(base), dims, strides, lower, upper,
-                           32, pixels, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                           channels, pixels, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
                            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -2053,14 +2056,20 @@ static int tc_wgrad_nhwc(const Geo& g, const void* x, const void* dy, void* dw, 
             int rc = launch_lower(g, x, rows, st);
             if (rc) return rc;
         }
-        if (!make_map_im2col(&ma, rows, g.n, g.ho, g.wo, Krows, 0, 0, g.ho, g.wo, 1, 1, 32, CU_TENSOR_MAP_SWIZZLE_NONE))
-            return B2C_ERR_UNSUPPORTED;
+        int lg = Krows % 128 == 0 ? 7 : Krows % 64 == 0 ? 6 : 5;       // widest box first, narrower if the encoder refuses
+        while (lg >= 5 && !make_map_im2col(&ma, rows, g.n, g.ho, g.wo, Krows, 0, 0, g.ho, g.wo, 1, 1, 32, CU_TENSOR_MAP_SWIZZLE_NONE, 1u << lg)) lg--;
+        if (lg < 5) return B2C_ERR_UNSUPPORTED;
+        p.a_box_log2 = lg;
         p.C = Krows; p.cblocks = Krows / 32; p.S = 1;
         p.str_h = 1; p.str_w = 1; p.dil_h = 1; p.dil_w = 1; p.low_h = 0; p.low_w = 0;
     } else {
-        if (!make_map_im2col(&ma, x, g.n, g.h, g.w, g.ci, -g.vpad, -g.hpad, g.h + 2 * g.vpad - (g.kh - 1) * g.vdil,
-                             g.w + 2 * g.hpad - (g.kw - 1) * g.hdil, g.vstr, g.hstr, 32, CU_TENSOR_MAP_SWIZZLE_NONE))
-            return B2C_ERR_UNSUPPORTED;
+        // x boxes as wide as the channel count allows (fewer TMA instructions per k-block: the producer's issue
+        // time was 36-63 % of the kernel's on the weight gradients of the step)
+        int lg = g.ci % 128 == 0 ? 7 : g.ci % 64 == 0 ? 6 : 5;
+        while (lg >= 5 && !make_map_im2col(&ma, x, g.n, g.h, g.w, g.ci, -g.vpad, -g.hpad, g.h + 2 * g.vpad - (g.kh - 1) * g.vdil,
+                                           g.w + 2 * g.hpad - (g.kw - 1) * g.hdil, g.vstr, g.hstr, 32, CU_TENSOR_MAP_SWIZZLE_NONE, 1u << lg)) lg--;
+        if (lg < 5) return B2C_ERR_UNSUPPORTED;
+        p.a_box_log2 = lg;
         p.C = g.ci; p.cblocks = g.ci / 32; p.S = g.kw;
         p.str_h = g.vstr; p.str_w = g.hstr; p.dil_h = g.vdil; p.dil_w = g.hdil; p.low_h = -g.vpad; p.low_w = -g.hpad;
     }
