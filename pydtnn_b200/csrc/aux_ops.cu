@@ -349,16 +349,27 @@ __global__ void __launch_bounds__(256) bn_apply_v4_kernel(const float4* __restri
     const float4 ga = *reinterpret_cast<const float4*>(gamma + grp * 4), be = *reinterpret_cast<const float4*>(beta + grp * 4);
     const int64_t per = (g.rows + gridDim.y - 1) / gridDim.y;
     const int64_t r0 = (int64_t)blockIdx.y * per, r1 = r0 + per < g.rows ? r0 + per : g.rows;
-    for (int64_t r = r0 + rxi; r < r1; r += g.rx) {
-        float4 v = x[r * g.c4 + grp], o;
+    auto one = [&](float4 v, float4 a) {
+        float4 o;
         o.x = bn_affine(v.x, m.x, is.x, ga.x, be.x); o.y = bn_affine(v.y, m.y, is.y, ga.y, be.y);
         o.z = bn_affine(v.z, m.z, is.z, ga.z, be.z); o.w = bn_affine(v.w, m.w, is.w, ga.w, be.w);
         if (addend) {        // residual sum on the rounded BN output, as the separate add kernel would do
-            const float4 a = addend[r * g.c4 + grp];
             o.x = __fadd_rn(o.x, a.x); o.y = __fadd_rn(o.y, a.y); o.z = __fadd_rn(o.z, a.z); o.w = __fadd_rn(o.w, a.w);
         }
         if (relu) { o.x = fmaxf(o.x, 0.f); o.y = fmaxf(o.y, 0.f); o.z = fmaxf(o.z, 0.f); o.w = fmaxf(o.w, 0.f); }
-        y[r * g.c4 + grp] = o;
+        return o;
+    };
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+    int64_t r = r0 + rxi;
+    for (; r + g.rx < r1; r += 2 * g.rx) {          // two rows per trip: their loads are in flight together
+        const int64_t j0 = r * g.c4 + grp, j1 = (r + g.rx) * g.c4 + grp;
+        const float4 v0 = x[j0], v1 = x[j1];
+        const float4 a0 = addend ? addend[j0] : zero, a1 = addend ? addend[j1] : zero;
+        y[j0] = one(v0, a0); y[j1] = one(v1, a1);
+    }
+    if (r < r1) {
+        const int64_t j = r * g.c4 + grp;
+        y[j] = one(x[j], addend ? addend[j] : zero);
     }
 }
 
@@ -377,11 +388,10 @@ __global__ void __launch_bounds__(256) bn_bwd_dx_v4_kernel(const float4* __restr
     const float4 sc = make_float4(ga.x * is.x / count, ga.y * is.y / count, ga.z * is.z / count, ga.w * is.w / count);
     const int64_t per = (g.rows + gridDim.y - 1) / gridDim.y;
     const int64_t r0 = (int64_t)blockIdx.y * per, r1 = r0 + per < g.rows ? r0 + per : g.rows;
-    for (int64_t r = r0 + rxi; r < r1; r += g.rx) {
-        const int64_t j = r * g.c4 + grp;
-        float4 xv = x[j], gd = dy[j], o;
+    const float4 be = (relu && beta) ? *reinterpret_cast<const float4*>(beta + grp * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+    auto one = [&](int64_t j, float4 xv, float4 gd) {
+        float4 o;
         if (relu && beta) {       // ReLU mask recomputed from x (see bn_affine)
-            const float4 be = *reinterpret_cast<const float4*>(beta + grp * 4);
             if (!(bn_affine(xv.x, m.x, is.x, ga.x, be.x) > 0.f)) gd.x = 0.f;
             if (!(bn_affine(xv.y, m.y, is.y, ga.y, be.y) > 0.f)) gd.y = 0.f;
             if (!(bn_affine(xv.z, m.z, is.z, ga.z, be.z) > 0.f)) gd.z = 0.f;
@@ -391,7 +401,17 @@ __global__ void __launch_bounds__(256) bn_bwd_dx_v4_kernel(const float4* __restr
         o.y = sc.y * (count * gd.y - ((xv.y - m.y) * is.y) * dg.y - db.y);
         o.z = sc.z * (count * gd.z - ((xv.z - m.z) * is.z) * dg.z - db.z);
         o.w = sc.w * (count * gd.w - ((xv.w - m.w) * is.w) * dg.w - db.w);
-        dx[j] = o;
+        return o;
+    };
+    int64_t r = r0 + rxi;
+    for (; r + g.rx < r1; r += 2 * g.rx) {          // two rows per trip: their loads are in flight together
+        const int64_t j0 = r * g.c4 + grp, j1 = (r + g.rx) * g.c4 + grp;
+        const float4 x0 = x[j0], g0 = dy[j0], x1 = x[j1], g1 = dy[j1];
+        dx[j0] = one(j0, x0, g0); dx[j1] = one(j1, x1, g1);
+    }
+    if (r < r1) {
+        const int64_t j = r * g.c4 + grp;
+        dx[j] = one(j, x[j], dy[j]);
     }
 }
 

@@ -22,11 +22,15 @@
 // contiguous channel axis use hi/lo copies written once per call by a small kernel instead.
 //
 // Variants (template parameters): whole tiles or balanced (tile, k-block) ranges with a hand-over of partial
-// tiles between consecutive CTAs; 2 or 4 output slabs per drain warp; NCHW tensors run on channel-last copies.
+// tiles between consecutive CTAs; the filter from split copies or read in place (K-major or MN-major); a chunked
+// drain, or for tiles of one chunk a streaming epilogue (32 columns at a time straight from tensor memory) with four
+// or eight drain warps; for tiles of at most four k-blocks the filter tiles of the CTA's column tile resident in
+// shared memory for the whole launch; several pixel classes (a strided data gradient) in one launch.  NCHW tensors
+// run on channel-last copies.
 //
-// Warp roles (320 threads; 448 in the variant with eight drain warps): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer (both stay
-// converged and issue through one elected lane), warps 2-5 = operand transform,
-// warps 6-9 = drain + epilogue: the tensor core's accumulate step truncates, so sums are kept in
+// Warp roles (320 threads; 448 with eight drain warps): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer
+// (both stay converged and issue through one elected lane), warps 2-5 = operand transform,
+// warps 6-9 (6-13) = drain + epilogue: the tensor core's accumulate step truncates, so sums are kept in
 // tensor memory only for a chunk of 8 k-blocks (two TMEM buffers alternate) and added chunk by
 // chunk into float32 registers with round-to-nearest, then bias / BN-scale / ReLU -> global.
 // Every mbarrier wait is bounded: when a wait runs out the CTA raises an abort flag, records a

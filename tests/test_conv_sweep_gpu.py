@@ -173,8 +173,11 @@ def _vgg16_convs():
 
 _ALEXNET_CONVS = [(227, 3, 96, 11, 4, 0), (27, 96, 256, 5, 1, 2), (13, 256, 384, 3, 1, 1), (13, 384, 384, 3, 1, 1),
                   (13, 384, 256, 3, 1, 1)]
+# not a network: short K loops (2 and 4 k-blocks per tile) on launches long enough to take split filter copies
+# instead of the filter in place (more than 30000 tile x k-block units), a combination none of the networks has
+_SHORT_K_LONG_LAUNCH = [(112, 64, 1024, 1, 1, 0), (112, 128, 640, 1, 1, 0)]
 _NETWORKS = {"resnet50": (64, "NHWC", _resnet50_convs()), "vgg16": (32, "NHWC", _vgg16_convs()),
-             "alexnet": (64, "NCHW", _ALEXNET_CONVS)}
+             "alexnet": (64, "NCHW", _ALEXNET_CONVS), "short_k_long_launch": (20, "NHWC", _SHORT_K_LONG_LAUNCH)}
 
 
 @pytest.mark.parametrize("net", sorted(_NETWORKS))
