@@ -1606,8 +1606,31 @@ static WgradPlan wgrad_plan(const Geo& g)
     return pl;
 }
 
+// A 1x1 stride-1 weight gradient whose (tap, ci) rows fill at most half of a 128-row MMA (ci <= 64) while co would fill
+// it: the roles of x and dy are exchanged (dw^T = dy^T x, computed as the weight gradient of the layer with ci and co
+// exchanged, x in the place of dy), and the second stage writes dw through exchanged filter strides.  The bias
+// gradient comes out of the B-operand path, which then holds x: layers that ask for it keep the plain form.
+static bool wgrad_swap_ok(const Geo& g)
+{
+    return g.kh == 1 && g.kw == 1 && g.vstr == 1 && g.hstr == 1 && g.vpad == 0 && g.hpad == 0 &&
+           g.ci % 32 == 0 && g.ci <= 64 && g.co % 32 == 0 && g.co >= 128;
+}
+static Geo wgrad_swapped(const Geo& g)
+{
+    Geo q = g;
+    q.ci = g.co; q.co = g.ci; q.K = q.ci;
+    return q;
+}
+
 static size_t tc_workspace_bytes_nhwc(const Geo& g, int pass)
 {
+    if (pass == B2C_PASS_WGRAD && wgrad_swap_ok(g)) {
+        // either form may run (the bias gradient decides at the call): room for both
+        const size_t a = tc_workspace_bytes_nhwc(wgrad_swapped(g), pass);      // not exchanged again: its co is at most 64
+        const WgradPlan pl = wgrad_plan(g);
+        const size_t b = align_up((size_t)pl.splits * g.K * g.co * sizeof(float), 1024) + 2048 + align_up((size_t)pl.splits * 4 * g.co * sizeof(float), 1024);
+        return a > b ? a : b;
+    }
     const bool low = g.ci % 32 != 0;
     const size_t lowered = low ? align_up((size_t)g.M * lowered_kp(g) * sizeof(float), 1024) : 0;
     if (pass == B2C_PASS_FPROP && low) return lowered + 2 * align_up((size_t)g.co * lowered_kp(g) * sizeof(float), 1024) + 2048;
@@ -2038,9 +2061,11 @@ static int tc_dgrad_nhwc(const Geo& g, const void* dy, const void* w, void* dx, 
 }
 
 static int tc_wgrad_nhwc(const Geo& g, const void* x, const void* dy, void* dw, void* db, void* ws, size_t ws_bytes, cudaStream_t st,
-                         bool lowered_in_ws = false)
+                         bool lowered_in_ws = false, bool exchanged = false)
 {
     if (!load_driver_entry_points()) return B2C_ERR_UNSUPPORTED;
+    if (!exchanged && !db && !lowered_in_ws && wgrad_swap_ok(g))
+        return tc_wgrad_nhwc(wgrad_swapped(g), dy, x, dw, nullptr, ws, ws_bytes, st, false, true);
     const bool low = g.ci % 32 != 0;
     const int Krows = low ? lowered_kp(g) : (int)g.K;
     WgradPlan pl = wgrad_plan(g);
@@ -2085,6 +2110,11 @@ static int tc_wgrad_nhwc(const Geo& g, const void* x, const void* dy, void* dw, 
     CUtensorMap mo = mb;
     p.tma_store = make_map_out(&mo, partial, (uint64_t)pl.splits, (uint64_t)Krows, (uint64_t)g.co) ? 1 : 0;
     WStride wsd = w_stride(g.w_layout, g.ci, g.co, g.kh, g.kw);
+    if (exchanged) {
+        // g is the layer with ci and co exchanged: the caller's filter has g.co input and g.ci output channels
+        wsd = w_stride(g.w_layout, g.co, g.ci, 1, 1);
+        const int64_t t = wsd.sk; wsd.sk = wsd.sc; wsd.sc = t;
+    }
     int rc = dispatch_wgrad(pl.bn, ma, mb, mo, p, pl.splits, st);
     if (rc) return rc;
     WgradReduceParams rp{Krows, g.co, g.ci, g.kw, pl.splits, wsd.sk, wsd.sc, wsd.sr, wsd.ss, (int)g.K};

@@ -127,6 +127,24 @@ def test_float32_nhwc_against_oracle(name, engine):
         assert_parity(out[nm], ref, np.float32, f"{name} {nm}")
 
 
+@pytest.mark.parametrize("w_layout", ["KRSC", "CRSK"])
+@pytest.mark.parametrize("shape", [(4, 56, 56, 64, 256), (3, 27, 29, 32, 128), (2, 28, 28, 64, 160)])
+def test_1x1_weight_gradient_without_bias_on_few_input_channels(shape, w_layout):
+    """Without a bias gradient to take, a 1x1 weight gradient with at most 64 input channels runs with x and dy
+    exchanged (co on the GEMM row axis) and writes dw through exchanged filter strides: same dw, both filter layouts,
+    and the same as the plain form that a bias gradient request selects."""
+    n, h, w_, ci, cout = shape
+    g = co.Geom(n, h, w_, ci, cout, 1, 1, 0, 0, 1, 1)
+    x, w, b, dy = _inputs(g, np.float32, seed=5)
+    dw, db, _ = co.conv2d_backward(x, dy, w, g, "NHWC")
+    exchanged = run_conv(g, "NHWC", np.float32, x, w, None, dy, w_layout=w_layout, passes=("wgrad",))
+    plain = run_conv(g, "NHWC", np.float32, x, w, b, dy, w_layout=w_layout, passes=("wgrad",))
+    assert exchanged["db"] is None
+    assert_parity(exchanged["dw"], dw, np.float32, f"{shape} {w_layout} dw, exchanged operands")
+    assert_parity(plain["dw"], dw, np.float32, f"{shape} {w_layout} dw")
+    assert_parity(plain["db"], db, np.float32, f"{shape} {w_layout} db")
+
+
 @pytest.mark.parametrize("layout,dtype", [("NCHW", "float32"), ("NHWC", "float64"), ("NCHW", "float64")])
 @pytest.mark.parametrize("name", ["cfg1_3x3_64_64_n64", "resnet_3x3s2_128", "resnet_1x1_64_256", "sweep_5x5s2_14",
                                   "dilated_3x3", "ragged_everything", "alexnet_conv1_11x11s4", "resnet_1x1s2_256_512",
