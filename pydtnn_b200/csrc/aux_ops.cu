@@ -885,6 +885,43 @@ __global__ void __launch_bounds__(256) pool_bwd_v4_kernel(PoolP p, const float4*
     }
 }
 
+// Max pooling backward for the 3x3 window with stride 2 and dilation 1 (the pool after a network's stem), NHWC float4:
+// the same gather as pool_bwd_v4_kernel with the window arithmetic in constants.  An element (ih, iw) is reached by
+// tap ii = (ih + vpad) % 2 (and ii + 2 when that is 0) of window row (ih + vpad) / 2 (and the row before it); the same
+// along w.  Grid (blocks over iw x channel groups, n x h): one division per thread.  Taps are visited in ascending
+// order, as the general kernel does, so the sums are the same bits.
+__global__ void __launch_bounds__(256) pool_bwd_max_k3s2_kernel(PoolP p, const float4* __restrict__ dy, const int4* __restrict__ idx_max,
+                                                                float4* __restrict__ dx)
+{
+    pdl_prologue();
+    const int c4 = p.c / 4;
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= p.w * c4) return;
+    const int iw = e / c4, cg = e - iw * c4;
+    const int nn = blockIdx.y / p.h, ih = blockIdx.y - nn * p.h;
+    const int th = ih + p.vpad, tw = iw + p.hpad;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int ka = 0; ka < 2; ka++) {
+        const int ii = (th & 1) + 2 * ka, xx = (th >> 1) - ka;
+        if (ii > 2 || xx < 0 || xx >= p.ho) continue;
+#pragma unroll
+        for (int kb = 0; kb < 2; kb++) {
+            const int jj = (tw & 1) + 2 * kb, yy = (tw >> 1) - kb;
+            if (jj > 2 || yy < 0 || yy >= p.wo) continue;
+            const int64_t o = (((int64_t)nn * p.ho + xx) * p.wo + yy) * c4 + cg;
+            const float4 g = dy[o];
+            const int4 id = idx_max[o];
+            const int tap = ii * 3 + jj;
+            if (id.x == tap) acc.x += g.x;
+            if (id.y == tap) acc.y += g.y;
+            if (id.z == tap) acc.z += g.z;
+            if (id.w == tap) acc.w += g.w;
+        }
+    }
+    dx[((int64_t)blockIdx.y * p.w + iw) * c4 + cg] = acc;
+}
+
 // out = max(a + b, 0)  (residual sum followed by ReLU in one pass)
 __global__ void add_relu_f4_kernel(const float4* __restrict__ a, const float4* __restrict__ b, float4* __restrict__ out, int64_t n4)
 {
@@ -1374,6 +1411,12 @@ extern "C" int b2c_pool_backward(int dtype, int layout, int is_max, int n, int h
             if (unit) launch_pdl(pool_bwd_v4_kernel<MAXF, IDXT, true>, ew_blocks(total / 4), 256, 0, st, p, (const float4*)dy, (const int4*)idx_max, (float4*)dx);  \
             else launch_pdl(pool_bwd_v4_kernel<MAXF, IDXT, false>, ew_blocks(total / 4), 256, 0, st, p, (const float4*)dy, (const int4*)idx_max, (float4*)dx);     \
         } while (0)
+        if (is_max && unit && p.kh == 3 && p.kw == 3 && p.vstr == 2 && p.hstr == 2 && (int64_t)p.n * p.h <= 65535 &&
+            (int64_t)p.w * (p.c / 4) < 0x7fffffffLL) {
+            launch_pdl(pool_bwd_max_k3s2_kernel, dim3((unsigned)((p.w * (p.c / 4) + 255) / 256), (unsigned)(p.n * p.h)), 256, 0, st, p,
+                       (const float4*)dy, (const int4*)idx_max, (float4*)dx);
+            return check_launch("pool_bwd_max_k3s2");
+        }
         if (is_max && small) B2C_POOL_BWD_V4(true, int);
         else if (is_max) B2C_POOL_BWD_V4(true, int64_t);
         else if (small) B2C_POOL_BWD_V4(false, int);
