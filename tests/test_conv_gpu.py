@@ -163,10 +163,19 @@ def test_other_layouts_and_float64_against_oracle(name, layout, dtype):
         assert_parity(out[nm], ref, dtype, f"{name} {layout} {dtype} {nm}")
 
 
-@pytest.mark.parametrize("layout", ["NHWC", "NCHW"])
+# the fused epilogue on every drain path of the tensor-core kernel: the chunked drain (3x3, nine k-blocks), the
+# streaming epilogue with eight drain warps and resident filter tiles (1x1 on 64 and on 128 channels: 128- and 64-wide
+# column tiles), the streaming epilogue with four drain warps (1x1 on 256 channels, a partial last column tile)
+_EPILOGUE_GEOMS = {"3x3_32_48": co.Geom(4, 14, 14, 32, 48, 3, 3, 1, 1, 1, 1),
+                   "1x1_64_256": co.Geom(4, 28, 28, 64, 256, 1, 1, 0, 0, 1, 1),
+                   "1x1_128_64": co.Geom(2, 28, 28, 128, 64, 1, 1, 0, 0, 1, 1),
+                   "1x1_256_192": co.Geom(2, 14, 14, 256, 192, 1, 1, 0, 0, 1, 1)}
+
+
 @pytest.mark.parametrize("mode", ["relu", "bn", "bn_relu", "nobias_bn_relu"])
-def test_fused_inference_epilogue(layout, mode):
-    g = co.Geom(4, 14, 14, 32, 48, 3, 3, 1, 1, 1, 1)
+@pytest.mark.parametrize("layout,geom", [("NHWC", k) for k in _EPILOGUE_GEOMS] + [("NCHW", "3x3_32_48")])
+def test_fused_inference_epilogue(layout, geom, mode):
+    g = _EPILOGUE_GEOMS[geom]
     x, w, b, dy = _inputs(g, np.float32, seed=2)
     xl, wl, _ = _to_layout(x, w, dy, layout)
     rng = np.random.Generator(np.random.PCG64(5))
@@ -179,7 +188,7 @@ def test_fused_inference_epilogue(layout, mode):
     ref = co.conv2d_fused_inference(xl, wl, bias, g, layout, bn if use_bn else None, use_relu)
     out = run_conv(g, layout, np.float32, xl, wl, bias, None, bn=bn if use_bn else None, relu=use_relu,
                    passes=("fprop",))
-    assert_parity(out["y"], ref, np.float32, f"fused {mode} {layout}")
+    assert_parity(out["y"], ref, np.float32, f"fused {mode} {layout} {geom}")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "float64"])
