@@ -24,7 +24,9 @@ SHAPES = [(3, 10, 10, 32, 64, 3, 1, 1), (4, 16, 16, 64, 256, 1, 1, 0), (8, 28, 2
           # tiles (a grid of 144 CTAs); the batch norm's fast path takes channel counts 4..128, 256 and multiples of 256
           (3, 91, 91, 64, 32, 1, 1, 0), (2, 29, 31, 96, 128, 1, 1, 0), (2, 40, 40, 128, 768, 1, 1, 0),
           # long K with whole tiles: the chunked drain's per-CTA sums (25 row tiles x 2 column tiles)
-          (4, 28, 28, 256, 256, 3, 1, 1)]
+          (4, 28, 28, 256, 256, 3, 1, 1),
+          # eight k-blocks: the streaming epilogue with four drain warps; 32 k-blocks of a 1x1 filter
+          (4, 14, 14, 256, 128, 1, 1, 0), (4, 14, 14, 1024, 256, 1, 1, 0)]
 
 
 def _conv_and_bn(g, x, w_krsc, b, gamma, beta, fused, relu, addend):
