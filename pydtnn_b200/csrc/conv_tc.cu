@@ -347,12 +347,16 @@ __global__ void tc_lower_rows_kernel(LowerParams p, const float* __restrict__ x,
     extern __shared__ float patch[];                      // [kh][wp][c], column j is input column j - hpad
     const int nn = blockIdx.x / p.ho, oh = blockIdx.x - nn * p.ho;
     const int rowlen = wp * p.c;
+    // one patch pixel per thread and trip (its few channels in an inner loop: no division per element)
     for (int r = 0; r < p.kh; r++) {
         const int ih = oh * p.vstr - p.vpad + r * p.vdil;
+        const bool row_in = (unsigned)ih < (unsigned)p.h;
         const float* src = x + ((int64_t)nn * p.h + ih) * p.w * p.c;
-        for (int j = threadIdx.x; j < rowlen; j += blockDim.x) {
-            const int iw = j / p.c - p.hpad;
-            patch[r * rowlen + j] = ((unsigned)ih < (unsigned)p.h && (unsigned)iw < (unsigned)p.w) ? __ldg(src + j - p.hpad * p.c) : 0.f;
+        for (int j = threadIdx.x; j < wp; j += blockDim.x) {
+            const int iw = j - p.hpad;
+            const bool in = row_in && (unsigned)iw < (unsigned)p.w;
+            float* dst = patch + r * rowlen + j * p.c;
+            for (int c = 0; c < p.c; c++) dst[c] = in ? __ldg(src + (int64_t)iw * p.c + c) : 0.f;
         }
     }
     __syncthreads();
